@@ -1,0 +1,156 @@
+/*
+ * ormi_b200 — C ABI of the B200 (sm_100a) backend for the realize path of Ormi's lazy
+ * tensor graph.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns 0 on success
+ * and a non-zero code on failure (the text is available from ormi_b200_last_error()), and
+ * never throws.  The C++ seams of ormi-core (IAllocator, cuda::execute_jit, cuda::compile,
+ * cuda::matmul, cuda::sum, execute_graph) translate a non-zero return into
+ * std::runtime_error, which is the reference's own error convention
+ * (ormi-core/csrc/utils/macros.h:8-19).
+ *
+ * Each declaration cites the reference interface it replaces, by path inside the Ormi
+ * project.
+ */
+#ifndef ORMI_B200_H
+#define ORMI_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ORMI_B200_MAX_DIMS 8
+
+/* Operation codes: same order and values as ormi::ops::OpEnum (ormi-core/csrc/core/ops.h:4-10). */
+enum ormi_b200_op {
+    ORMI_OP_LEAF = 0, ORMI_OP_CONST = 1,
+    ORMI_OP_NEG = 2, ORMI_OP_EXP = 3, ORMI_OP_LOG = 4, ORMI_OP_SIN = 5, ORMI_OP_COS = 6,
+    ORMI_OP_ADD = 7, ORMI_OP_SUB = 8, ORMI_OP_MUL = 9, ORMI_OP_DIV = 10, ORMI_OP_POW = 11,
+    ORMI_OP_MATMUL = 12,
+    ORMI_OP_SUM = 13, ORMI_OP_TRANSPOSE = 14, ORMI_OP_RESHAPE = 15, ORMI_OP_EXPAND = 16,
+    ORMI_OP_FRAC_DERIV = 17
+};
+
+/* Node flags (in). */
+#define ORMI_NODE_KEEP   1u  /* somebody outside the graph holds this node: it must own a buffer after realize */
+/* Node flags (out, set by ormi_b200_realize). */
+#define ORMI_NODE_OWNED  2u  /* `data` is a fresh pool buffer now owned by the caller (free with ormi_b200_free) */
+#define ORMI_NODE_ALIAS  4u  /* `data` aliases the buffer of the node's view base (ormi-core/csrc/backend/runtime.cpp:20-23) */
+
+/*
+ * One node of the lazy graph, flattened: the fields of ormi::Node that the realize path
+ * reads (ormi-core/csrc/core/node.h:12-37) — op, parents, view {shape, strides}, the
+ * ReduceAttrs of a SUM (ormi-core/csrc/core/attributes.h:8-11) and the realized buffer.
+ * Nodes are stored in topological order: a parent's index is lower than its child's.
+ */
+typedef struct ormi_b200_node {
+    int32_t  op;                           /* enum ormi_b200_op */
+    int32_t  n_parents;                    /* 0, 1 or 2 */
+    int32_t  parents[2];                   /* indices into the node array */
+    int32_t  ndim;
+    int32_t  shape[ORMI_B200_MAX_DIMS];    /* node->view.shape */
+    int32_t  strides[ORMI_B200_MAX_DIMS];  /* node->view.strides, in elements */
+    int32_t  n_axes;                       /* SUM: number of reduced axes; 0 = reduce every axis */
+    int32_t  axes[ORMI_B200_MAX_DIMS];
+    int32_t  keepdims;
+    uint32_t flags;
+    void*    data;                         /* device pointer of node->data->ptr, NULL when not realized */
+    int64_t  data_bytes;                   /* node->data->bytes */
+} ormi_b200_node;
+
+typedef struct ormi_b200_ctx ormi_b200_ctx;
+
+/* ------------------------------------------------------------------ context, memory ---- */
+
+/* Binds device `device`, creates the compute stream and the buffer pool.
+ * Replaces the CUDAAllocator constructor (ormi-core/csrc/backend/cuda/allocator.cu:20-25) and the
+ * per-call cuInit/context retain of execute_jit (ormi-core/csrc/backend/cuda/jit.cu:16-19).
+ * Fails (non-zero) when no CUDA device is present; the reference's tests use exactly that failure to
+ * detect CUDA (ormi-core/csrc/tests/test_utils.h:17-21). */
+int ormi_b200_init(int device, ormi_b200_ctx** out_ctx);
+int ormi_b200_shutdown(ormi_b200_ctx* ctx);
+
+/* Text of the last error raised on the calling thread. */
+const char* ormi_b200_last_error(void);
+
+/* Exact-size caching pool: a freed block is handed back for the next request of the same byte size
+ * (contract pinned by ormi-core/csrc/tests/core/test_allocator.cpp:12-47).
+ * Replaces CUDAAllocator::allocate / free (allocator.cu:36-55). */
+int ormi_b200_alloc(ormi_b200_ctx* ctx, size_t bytes, void** out_ptr);
+int ormi_b200_free(ormi_b200_ctx* ctx, void* ptr, size_t bytes);
+/* Returns every cached block to the driver (the reference never does; additive). */
+int ormi_b200_trim(ormi_b200_ctx* ctx);
+
+/* CUDAAllocator::memset / memcpy / fill_n / copy_* (allocator.cu:57-95).  The host copies are complete
+ * on return; device-side work is ordered on the context's stream. */
+int ormi_b200_memset(ormi_b200_ctx* ctx, void* ptr, int value, size_t bytes);
+int ormi_b200_memcpy_d2d(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes);
+int ormi_b200_memcpy_h2d(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes);
+int ormi_b200_memcpy_d2h(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes);
+int ormi_b200_fill_u32(ormi_b200_ctx* ctx, void* dst, uint32_t pattern, size_t count);
+int ormi_b200_fill_u8(ormi_b200_ctx* ctx, void* dst, uint8_t pattern, size_t count);
+/* Waits for everything queued on the context's stream. */
+int ormi_b200_sync(ormi_b200_ctx* ctx);
+/* The context's compute stream as a cudaStream_t, for callers that time with CUDA events. */
+void* ormi_b200_stream(ormi_b200_ctx* ctx);
+
+/* ------------------------------------------------------------------ realize path ------- */
+
+/* Realizes `roots` (and every KEEP-flagged ancestor) of a flattened graph.
+ * Replaces ormi::execute_graph for DeviceEnum::CUDA (ormi-core/csrc/backend/runtime.cpp:13-39),
+ * cuda::execute_jit (ormi-core/csrc/backend/cuda/jit.cu:13-44) and the CUDA graph breakers
+ * (kernels/blas/matmul.cu:114-124, kernels/reduce/sum.cu:86-97), with a fusion scheduler in front:
+ * pointwise chains, their trailing row / column / global sums and reduce-then-broadcast groups run as
+ * single generated sm_100a kernels.  On return every root, every KEEP node and every node the scheduler
+ * had to materialize has `data`/`data_bytes` set and ORMI_NODE_OWNED (or ORMI_NODE_ALIAS for a view). */
+int ormi_b200_realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots);
+
+/* The schedule of the same call as text (JSON): buffers, kernel launches with their generated CUDA C
+ * source, GEMM steps.  Needs no device; ctx may be NULL.  Writes at most `cap` bytes (NUL-terminated)
+ * and stores the full length in *out_len.  Counterpart of cuda::compile's `kernel_code`
+ * (ormi-core/csrc/backend/cuda/compiler.cuh:8-16) for a whole graph. */
+int ormi_b200_plan_json(const ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots,
+                        char* buf, size_t cap, size_t* out_len);
+
+/* cuda::compile (ormi-core/csrc/backend/cuda/compiler.cu:53-112): CUDA C source of the guarded scalar
+ * `fused_kernel` for the un-realized pointwise sub-graph under `root`, with the leaves in argument order.
+ * `leaf_index[i]` receives the node index of LEAF_i. */
+int ormi_b200_compile_source(const ormi_b200_node* nodes, int n_nodes, int root,
+                             char* buf, size_t cap, size_t* out_len,
+                             int* leaf_index, int leaf_cap, int* n_leaves);
+
+/* compile_ptx (ormi-core/csrc/backend/cuda/utils.cu:6-27): NVRTC, but straight to an sm_100a cubin.
+ * Needs no device.  The image is written to `buf` when it fits; *out_len is its size. */
+int ormi_b200_compile_cubin(const char* source, char* buf, size_t cap, size_t* out_len);
+
+/* cuda::sum (ormi-core/csrc/backend/cuda/kernels/reduce/sum.cu:12-84) on raw buffers: deterministic
+ * reduction of `in` (shape/strides of in_view) over `axes` (n_axes == 0: all) into the contiguous `out`. */
+int ormi_b200_sum(ormi_b200_ctx* ctx, const float* in, int ndim, const int32_t* shape, const int32_t* strides,
+                  const int32_t* axes, int n_axes, float* out);
+
+/* cuda::matmul (ormi-core/csrc/backend/cuda/kernels/blas/matmul.cu:19-112) on raw buffers and views:
+ * C[b] = op(A[b]) op(B[b]); transposition from the last-dimension stride, leading dimensions broadcast.
+ * `out` is the contiguous [batch..., M, N] result. */
+int ormi_b200_matmul(ormi_b200_ctx* ctx,
+                     const float* A, int ndim_a, const int32_t* shape_a, const int32_t* strides_a,
+                     const float* B, int ndim_b, const int32_t* shape_b, const int32_t* strides_b,
+                     float* out, int ndim_out, const int32_t* shape_out);
+
+/* ------------------------------------------------------------------ options, counters -- */
+
+/* Matmul arithmetic used by ormi_b200_realize / ormi_b200_matmul (additive knob; the reference has none):
+ * "fp32" (SIMT FFMA, default), "bf16" (tcgen05, fp32 accumulate), "tf32", "3xtf32". Key "matmul".
+ * Key "fusion": "on" (default) / "off" (one kernel per node, like the reference scheduler). */
+int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value);
+
+/* Counters since init: "kernels_compiled", "kernel_cache_hits", "plan_cache_hits", "launches",
+ * "gemm_launches", "bytes_allocated", "pool_hits". */
+int ormi_b200_get_counter(ormi_b200_ctx* ctx, const char* name, int64_t* out_value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ORMI_B200_H */
