@@ -139,6 +139,11 @@ static int eval_sum(const ormi_b200_node* nodes, slot_t* slots, int i) {
             if (!reduced) { out_flat += coord * ostr[out_d]; out_d++; }
             else if (n->keepdims) out_d++;
         }
+        if (out_flat >= out_elems) {
+            free(out);
+            snprintf(g_err, sizeof g_err, "the reference SUM writes out of bounds here (un-broadcast of a middle dimension, adjoint.cpp:22-31)");
+            return 1;
+        }
         out[out_flat] += is->ptr[e];
     }
     slots[i].ptr = out; slots[i].elems = out_elems; slots[i].owned = 1;

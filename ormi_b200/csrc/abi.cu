@@ -1,0 +1,251 @@
+// extern "C" surface of the backend (include/ormi_b200.h): argument checking, exception -> error code.
+#include <cstring>
+
+#include "context.h"
+#include "ormi_b200.h"
+
+using namespace ormi_b200;
+
+static thread_local std::string g_last_error;
+
+template <typename F>
+static int guarded(F&& f) {
+    try { f(); return 0; }
+    catch (const std::exception& e) { g_last_error = e.what(); return 1; }
+    catch (...) { g_last_error = "unknown error"; return 1; }
+}
+
+static void need(bool cond, const char* msg) { if (!cond) throw Error(msg); }
+
+namespace ormi_b200 {
+void gemm_bf16(ormi_b200_ctx* ctx, const GemmArgs& g);
+void gemm_dispatch(ormi_b200_ctx* ctx, const GemmArgs& g) {
+    if (ctx->matmul_mode == MatmulMode::BF16) gemm_bf16(ctx, g);
+    else gemm_ffma(ctx, g);
+}
+}  // namespace ormi_b200
+
+extern "C" {
+
+const char* ormi_b200_last_error(void) { return g_last_error.c_str(); }
+
+int ormi_b200_init(int device, ormi_b200_ctx** out_ctx) {
+    return guarded([&] {
+        need(out_ctx != nullptr, "ormi_b200_init: out_ctx is NULL");
+        int count = 0;
+        cudaError_t e = cudaGetDeviceCount(&count);
+        if (e != cudaSuccess) { cudaGetLastError(); throw Error(std::string("CUDA Error: ") + cudaGetErrorString(e)); }
+        if (device < 0 || device >= count) throw Error("CUDA Error: no such device " + std::to_string(device));
+        ORMI_CUDA(cudaSetDevice(device));
+        cudaDeviceProp prop;
+        ORMI_CUDA(cudaGetDeviceProperties(&prop, device));
+        if (prop.major != 10) throw Error("ormi_b200 is built for sm_100a only; device is sm_" + std::to_string(prop.major) + std::to_string(prop.minor));
+        auto ctx = std::make_unique<ormi_b200_ctx>();
+        ctx->device = device;
+        ctx->num_sms = prop.multiProcessorCount;
+        ORMI_CUDA(cudaFree(0));
+        ctx->drv.load();
+        ORMI_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+        *out_ctx = ctx.release();
+    });
+}
+
+int ormi_b200_shutdown(ormi_b200_ctx* ctx) {
+    return guarded([&] {
+        if (!ctx) return;
+        cudaSetDevice(ctx->device);
+        cudaStreamSynchronize(ctx->stream);
+        for (auto& kv : ctx->kernel_cache) if (kv.second.module) ctx->drv.ModuleUnload(kv.second.module);
+        for (auto& kv : ctx->free_blocks) for (void* p : kv.second) cudaFree(p);
+        for (int i = 0; i < 2; ++i) if (ctx->stage[i]) cudaFree(ctx->stage[i]);
+        cudaStreamDestroy(ctx->stream);
+        delete ctx;
+    });
+}
+
+int ormi_b200_alloc(ormi_b200_ctx* ctx, size_t bytes, void** out_ptr) {
+    return guarded([&] { need(ctx && out_ptr, "ormi_b200_alloc: NULL argument"); ORMI_CUDA(cudaSetDevice(ctx->device)); *out_ptr = pool_alloc(ctx, bytes); });
+}
+
+int ormi_b200_free(ormi_b200_ctx* ctx, void* ptr, size_t bytes) {
+    return guarded([&] { need(ctx != nullptr, "ormi_b200_free: ctx is NULL"); pool_free(ctx, ptr, bytes); });
+}
+
+int ormi_b200_trim(ormi_b200_ctx* ctx) {
+    return guarded([&] {
+        need(ctx != nullptr, "ormi_b200_trim: ctx is NULL");
+        ORMI_CUDA(cudaSetDevice(ctx->device));
+        ORMI_CUDA(cudaStreamSynchronize(ctx->stream));
+        std::lock_guard<std::mutex> lock(ctx->pool_mutex);
+        for (auto& kv : ctx->free_blocks) for (void* p : kv.second) cudaFree(p);
+        ctx->free_blocks.clear();
+    });
+}
+
+int ormi_b200_memset(ormi_b200_ctx* ctx, void* ptr, int value, size_t bytes) {
+    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); ORMI_CUDA(cudaMemsetAsync(ptr, value, bytes, ctx->stream)); });
+}
+
+int ormi_b200_memcpy_d2d(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream)); });
+}
+
+int ormi_b200_memcpy_h2d(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    return guarded([&] {
+        need(ctx != nullptr, "ctx is NULL");
+        ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+        ORMI_CUDA(cudaStreamSynchronize(ctx->stream));   // the host buffer may be reused on return
+    });
+}
+
+int ormi_b200_memcpy_d2h(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    return guarded([&] {
+        need(ctx != nullptr, "ctx is NULL");
+        ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        ORMI_CUDA(cudaStreamSynchronize(ctx->stream));
+    });
+}
+
+__global__ void fill_u32_kernel(uint32_t* dst, uint32_t v, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) dst[i] = v;
+}
+
+int ormi_b200_fill_u32(ormi_b200_ctx* ctx, void* dst, uint32_t pattern, size_t count) {
+    return guarded([&] {
+        need(ctx != nullptr, "ctx is NULL");
+        if (count == 0) return;
+        int grid = (int)std::min<size_t>((count + 255) / 256, (size_t)ctx->num_sms * 8);
+        fill_u32_kernel<<<grid, 256, 0, ctx->stream>>>((uint32_t*)dst, pattern, count);
+        ORMI_CUDA(cudaGetLastError());
+    });
+}
+
+int ormi_b200_fill_u8(ormi_b200_ctx* ctx, void* dst, uint8_t pattern, size_t count) {
+    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); ORMI_CUDA(cudaMemsetAsync(dst, pattern, count, ctx->stream)); });
+}
+
+int ormi_b200_sync(ormi_b200_ctx* ctx) {
+    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); ORMI_CUDA(cudaStreamSynchronize(ctx->stream)); });
+}
+
+void* ormi_b200_stream(ormi_b200_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+int ormi_b200_realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots) {
+    return guarded([&] {
+        need(ctx && nodes && roots && n_nodes > 0 && n_roots > 0, "ormi_b200_realize: bad arguments");
+        realize(ctx, nodes, n_nodes, roots, n_roots);
+    });
+}
+
+int ormi_b200_plan_json(const ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots,
+                        char* buf, size_t cap, size_t* out_len) {
+    return guarded([&] {
+        need(nodes && roots && n_nodes > 0 && n_roots > 0, "ormi_b200_plan_json: bad arguments");
+        Plan p = build_plan(nodes, n_nodes, roots, n_roots, SchedOptions());
+        std::string js = plan_to_json(p);
+        if (out_len) *out_len = js.size();
+        if (buf && cap) { size_t c = std::min(cap - 1, js.size()); std::memcpy(buf, js.data(), c); buf[c] = 0; }
+    });
+}
+
+int ormi_b200_compile_source(const ormi_b200_node* nodes, int n_nodes, int root, char* buf, size_t cap, size_t* out_len,
+                             int* leaf_index, int leaf_cap, int* n_leaves) {
+    return guarded([&] {
+        need(nodes && n_nodes > 0, "ormi_b200_compile_source: bad arguments");
+        SimpleKernel k = compile_simple(nodes, n_nodes, root);
+        if (!k.error.empty()) throw Error(k.error);
+        if (out_len) *out_len = k.source.size();
+        if (buf && cap) { size_t c = std::min(cap - 1, k.source.size()); std::memcpy(buf, k.source.data(), c); buf[c] = 0; }
+        if (n_leaves) *n_leaves = (int)k.leaves.size();
+        for (int i = 0; leaf_index && i < leaf_cap && i < (int)k.leaves.size(); ++i) leaf_index[i] = k.leaves[i];
+    });
+}
+
+int ormi_b200_compile_cubin(const char* source, char* buf, size_t cap, size_t* out_len) {
+    return guarded([&] {
+        need(source != nullptr, "ormi_b200_compile_cubin: source is NULL");
+        std::vector<char> cubin = compile_cubin(source);
+        if (out_len) *out_len = cubin.size();
+        if (buf && cap >= cubin.size()) std::memcpy(buf, cubin.data(), cubin.size());
+    });
+}
+
+static void fill_node(ormi_b200_node& nd, int op, int ndim, const int32_t* shape, const int32_t* strides, void* data) {
+    std::memset(&nd, 0, sizeof nd);
+    nd.op = op; nd.ndim = ndim;
+    int64_t elems = 1;
+    for (int d = 0; d < ndim; ++d) { nd.shape[d] = shape[d]; elems *= shape[d]; }
+    if (strides) for (int d = 0; d < ndim; ++d) nd.strides[d] = strides[d];
+    else { int acc = 1; for (int d = ndim - 1; d >= 0; --d) { nd.strides[d] = acc; acc *= shape[d]; } }
+    nd.data = data;
+    // extent of the buffer behind the view (for the "one float" rule only the value 4 matters)
+    int64_t extent = 1;
+    for (int d = 0; d < ndim; ++d) extent += (int64_t)(nd.shape[d] - 1) * (nd.strides[d] < 0 ? -nd.strides[d] : nd.strides[d]);
+    nd.data_bytes = data ? extent * 4 : 0;
+}
+
+int ormi_b200_sum(ormi_b200_ctx* ctx, const float* in, int ndim, const int32_t* shape, const int32_t* strides,
+                  const int32_t* axes, int n_axes, float* out) {
+    return guarded([&] {
+        need(ctx && in && out && ndim >= 0 && ndim <= ORMI_B200_MAX_DIMS, "ormi_b200_sum: bad arguments");
+        ormi_b200_node g[2];
+        fill_node(g[0], ORMI_OP_LEAF, ndim, shape, strides, (void*)in);
+        int32_t oshape[ORMI_B200_MAX_DIMS]; int ond = 0;
+        for (int d = 0; d < ndim; ++d) {
+            bool red = n_axes == 0;
+            for (int a = 0; a < n_axes; ++a) red |= (axes[a] == d);
+            if (!red) oshape[ond++] = shape[d];
+        }
+        fill_node(g[1], ORMI_OP_SUM, ond, oshape, nullptr, nullptr);
+        g[1].n_parents = 1; g[1].parents[0] = 0; g[1].n_axes = n_axes;
+        for (int a = 0; a < n_axes; ++a) g[1].axes[a] = axes[a];
+        int root = 1;
+        std::vector<std::pair<int, void*>> pre{{1, (void*)out}};
+        realize(ctx, g, 2, &root, 1, &pre);
+    });
+}
+
+int ormi_b200_matmul(ormi_b200_ctx* ctx,
+                     const float* A, int ndim_a, const int32_t* shape_a, const int32_t* strides_a,
+                     const float* B, int ndim_b, const int32_t* shape_b, const int32_t* strides_b,
+                     float* out, int ndim_out, const int32_t* shape_out) {
+    return guarded([&] {
+        need(ctx && A && B && out, "ormi_b200_matmul: NULL argument");
+        need(ndim_a >= 2 && ndim_b >= 2 && ndim_a <= ORMI_B200_MAX_DIMS && ndim_b <= ORMI_B200_MAX_DIMS && ndim_out <= ORMI_B200_MAX_DIMS,
+             "MATMUL requires operands to have at least 2 dimensions.");
+        ormi_b200_node g[3];
+        fill_node(g[0], ORMI_OP_LEAF, ndim_a, shape_a, strides_a, (void*)A);
+        fill_node(g[1], ORMI_OP_LEAF, ndim_b, shape_b, strides_b, (void*)B);
+        if (g[0].data_bytes == 4) g[0].data_bytes = 8;   // a 1x1 operand is still a matrix, not a broadcast scalar
+        if (g[1].data_bytes == 4) g[1].data_bytes = 8;
+        fill_node(g[2], ORMI_OP_MATMUL, ndim_out, shape_out, nullptr, nullptr);
+        g[2].n_parents = 2; g[2].parents[0] = 0; g[2].parents[1] = 1;
+        int root = 2;
+        std::vector<std::pair<int, void*>> pre{{2, (void*)out}};
+        realize(ctx, g, 3, &root, 1, &pre);
+    });
+}
+
+int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value) {
+    return guarded([&] {
+        need(ctx && key && value, "ormi_b200_set_option: NULL argument");
+        std::string k = key, v = value;
+        if (k == "matmul") {
+            if (v == "fp32") ctx->matmul_mode = MatmulMode::FP32;
+            else if (v == "bf16") ctx->matmul_mode = MatmulMode::BF16;
+            else throw Error("unknown matmul mode: " + v);
+        } else if (k == "fusion") {
+            if (v == "on") ctx->fusion = true; else if (v == "off") ctx->fusion = false; else throw Error("fusion must be on or off");
+        } else throw Error("unknown option: " + k);
+    });
+}
+
+int ormi_b200_get_counter(ormi_b200_ctx* ctx, const char* name, int64_t* out_value) {
+    return guarded([&] {
+        need(ctx && name && out_value, "ormi_b200_get_counter: NULL argument");
+        auto it = ctx->counters.find(name);
+        *out_value = it == ctx->counters.end() ? 0 : it->second;
+    });
+}
+
+}  // extern "C"

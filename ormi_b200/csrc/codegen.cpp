@@ -1,0 +1,609 @@
+// CUDA C code generation for fused kernels (NVRTC input, compiled for sm_100a).
+//
+// Replaces ormi::cuda::compile (ormi-core/csrc/backend/cuda/compiler.cu:53-112), which emits one scalar,
+// one-element-per-thread kernel per node with a div/mod chain per leaf, and the NVRTC `sum_kernel` of
+// ormi::cuda::sum (ormi-core/csrc/backend/cuda/kernels/reduce/sum.cu:29-66), which issues one atomicAdd per
+// input element.
+//
+// Two templates:
+//   flat  — pointwise domains (optionally with global sums): grid-stride loop, 128-bit loads/stores,
+//           broadcast operands addressed with strides baked in as literals, scalars hoisted.
+//   rows  — domains split into rows x columns: a group of T threads owns a row, keeps its VPT elements in
+//           registers, and evaluates the expression level by level; a row SUM is a register sum + warp
+//           shuffles + (T > 32) one shared-memory exchange, in a fixed order (deterministic, no atomics).
+//           Column sums and global sums accumulate in registers across the rows of a persistent block and
+//           leave one partial per block; a finalize kernel adds the partials in block order.
+//
+// Arithmetic follows the reference CPU backend op for op: every + - * / is a separately rounded IEEE fp32
+// operation (__fadd_rn etc. forbid FMA contraction, which the CPU interpreter cannot do either:
+// ormi-core/csrc/backend/cpu/lowerings/pointwise.cpp:5-15), and exp/log/sin/cos are the accurate CUDA
+// functions, never the fast intrinsics.
+#include <algorithm>
+#include <functional>
+#include <map>
+#include <sstream>
+
+#include "kernel_ir.h"
+
+namespace ormi_b200 {
+
+std::string device_prelude() {
+    return R"PRE(
+#ifndef ORMI_PRELUDE
+#define ORMI_PRELUDE
+// x ** y with the exponents the graphs actually use (0.5, 2, 3, 1, -1) evaluated the way a correctly
+// rounded powf would come out; anything else is powf.
+__device__ __forceinline__ float ormi_pow(float x, float y) {
+    if (y == 0.5f) return sqrtf(x);
+    if (y == 2.0f) return __fmul_rn(x, x);
+    if (y == 3.0f) return (float)((double)x * (double)x * (double)x);
+    if (y == 1.0f) return x;
+    if (y == -1.0f) return __fdiv_rn(1.0f, x);
+    return powf(x, y);
+}
+__device__ __forceinline__ float ormi_warp_sum(float v, int width) {
+    for (int o = width >> 1; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+#endif
+)PRE";
+}
+
+namespace {
+
+int64_t prod(const std::vector<int>& v, size_t a, size_t b) { int64_t p = 1; for (size_t i = a; i < b; ++i) p *= v[i]; return p; }
+
+std::string op_expr(int op, const std::string& a, const std::string& b) {
+    switch (op) {
+        case ORMI_OP_ADD: return "__fadd_rn(" + a + ", " + b + ")";
+        case ORMI_OP_SUB: return "__fsub_rn(" + a + ", " + b + ")";
+        case ORMI_OP_MUL: return "__fmul_rn(" + a + ", " + b + ")";
+        case ORMI_OP_DIV: return "__fdiv_rn(" + a + ", " + b + ")";
+        case ORMI_OP_POW: return "ormi_pow(" + a + ", " + b + ")";
+        case ORMI_OP_NEG: return "-" + a;
+        case ORMI_OP_EXP: return "expf(" + a + ")";
+        case ORMI_OP_LOG: return "logf(" + a + ")";
+        case ORMI_OP_SIN: return "sinf(" + a + ")";
+        case ORMI_OP_COS: return "cosf(" + a + ")";
+        case KNode::OP_ID: return a;
+    }
+    return "0.0f /* unknown op */";
+}
+
+int ceil_pow2(int64_t v) { int p = 1; while (p < v) p <<= 1; return p; }
+
+struct LoadInfo {
+    bool scalar = true;          // every stride 0
+    // rows template
+    bool row_var = false;        // depends on the row
+    bool elem = false;           // depends on the column
+    int64_t sc = 0;              // column stride after collapsing D[k:]
+    bool row_collapsed = true;   // row offset = r * sr
+    int64_t sr = 0;
+};
+
+int64_t touched_bytes(const KLoad& l, const std::vector<int>& D) {
+    int64_t e = 1;
+    for (size_t d = 0; d < D.size(); ++d) if (l.st[d] != 0) e *= D[d];
+    return e * 4;
+}
+
+// ---------------------------------------------------------------------------------------- flat template
+GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
+    GeneratedKernel out;
+    const size_t nd = spec.D.size();
+    // collapse adjacent dims that every load walks contiguously
+    std::vector<int64_t> cs;                     // collapsed sizes
+    std::vector<std::vector<int64_t>> lst(spec.loads.size());   // per load, per collapsed dim
+    for (size_t d = 0; d < nd; ++d) {
+        bool merge = !cs.empty();
+        if (merge) for (size_t l = 0; l < spec.loads.size(); ++l) if (lst[l].back() != spec.loads[l].st[d] * spec.D[d]) merge = false;
+        if (merge) { cs.back() *= spec.D[d]; for (size_t l = 0; l < spec.loads.size(); ++l) lst[l].back() = spec.loads[l].st[d]; }
+        else { cs.push_back(spec.D[d]); for (size_t l = 0; l < spec.loads.size(); ++l) lst[l].push_back(spec.loads[l].st[d]); }
+    }
+    const size_t cd = cs.size();
+    int64_t total = 1; for (int v : spec.D) total *= v;
+    int V = 4;
+    if (cd == 0 || cs.back() % 4 != 0) V = 1;
+    for (size_t l = 0; l < spec.loads.size() && V == 4; ++l) {
+        int64_t inner = lst[l].back();
+        if (inner != 0 && inner != 1) V = 1;
+        if (inner == 1) for (size_t d = 0; d + 1 < cd; ++d) if (lst[l][d] % 4 != 0) V = 1;
+    }
+    const int NT = 256;
+    const int64_t nvec = total / V;
+    int grid = (int)std::min<int64_t>((nvec + NT - 1) / NT, (int64_t)spec.num_sms * 8);
+    if (grid < 1) grid = 1;
+    int n_global = 0;
+    for (auto& o : spec.outputs) n_global += (o.kind == KOutput::GLOBALSUM);
+
+    std::ostringstream s;
+    s << device_prelude();
+    s << "extern \"C\" __global__ void __launch_bounds__(" << NT << ") " << name << "(";
+    for (size_t l = 0; l < spec.loads.size(); ++l) s << (l ? ", " : "") << "const float* __restrict__ in" << l;
+    for (size_t o = 0; o < spec.outputs.size(); ++o) s << ((spec.loads.size() + o) ? ", " : "") << "float* __restrict__ out" << o;
+    s << ") {\n";
+    std::vector<bool> scalar(spec.loads.size());
+    for (size_t l = 0; l < spec.loads.size(); ++l) {
+        scalar[l] = std::all_of(lst[l].begin(), lst[l].end(), [](int64_t v) { return v == 0; });
+        if (scalar[l]) s << "    const float S" << l << " = in" << l << "[0];\n";
+    }
+    for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) s << "    float gacc" << o << " = 0.0f;\n";
+    s << "    for (int i = blockIdx.x * " << NT << " + threadIdx.x; i < " << nvec << "; i += gridDim.x * " << NT << ") {\n";
+    s << "        const int e0 = i * " << V << ";\n";
+    if (cd > 1) {
+        s << "        int rem = e0;\n";
+        for (size_t d = cd; d-- > 1;) s << "        const int c" << d << " = rem % " << cs[d] << "; rem /= " << cs[d] << ";\n";
+        s << "        const int c0 = rem;\n";
+    } else if (cd == 1) {
+        s << "        const int c0 = e0;\n";
+    }
+    auto ref = [&](const KRef& r) {
+        if (r.t == KRef::LOAD) return scalar[r.id] ? "S" + std::to_string(r.id) : "L" + std::to_string(r.id) + "[j]";
+        return "v" + std::to_string(r.id) + "[j]";
+    };
+    for (size_t l = 0; l < spec.loads.size(); ++l) {
+        if (scalar[l]) continue;
+        s << "        float L" << l << "[" << V << "];\n        {\n            const int off = 0";
+        for (size_t d = 0; d < cd; ++d) if (lst[l][d] != 0) s << " + c" << d << " * " << lst[l][d];
+        s << ";\n";
+        int64_t inner = lst[l].back();
+        if (V == 4 && inner == 1) {
+            s << "            const float4 t = *reinterpret_cast<const float4*>(in" << l << " + off);\n"
+              << "            L" << l << "[0] = t.x; L" << l << "[1] = t.y; L" << l << "[2] = t.z; L" << l << "[3] = t.w;\n";
+        } else if (V == 4) {
+            s << "            const float t = in" << l << "[off];\n            L" << l << "[0] = t; L" << l << "[1] = t; L" << l << "[2] = t; L" << l << "[3] = t;\n";
+        } else {
+            s << "            L" << l << "[0] = in" << l << "[off];\n";
+        }
+        s << "        }\n";
+    }
+    for (const KNode& kn : spec.nodes) s << "        float v" << kn.node << "[" << V << "];\n";
+    s << "        #pragma unroll\n        for (int j = 0; j < " << V << "; ++j) {\n";
+    for (const KNode& kn : spec.nodes) {
+        std::string a = ref(kn.operands[0]);
+        std::string b = kn.operands.size() > 1 ? ref(kn.operands[1]) : "";
+        s << "            v" << kn.node << "[j] = " << op_expr(kn.op, a, b) << ";\n";
+    }
+    s << "        }\n";
+    for (size_t o = 0; o < spec.outputs.size(); ++o) {
+        const KOutput& ko = spec.outputs[o];
+        auto val = [&](int j) {
+            if (ko.value.t == KRef::LOAD) return scalar[ko.value.id] ? "S" + std::to_string(ko.value.id) : "L" + std::to_string(ko.value.id) + "[" + std::to_string(j) + "]";
+            return "v" + std::to_string(ko.value.id) + "[" + std::to_string(j) + "]";
+        };
+        if (ko.kind == KOutput::GLOBALSUM) {
+            for (int j = 0; j < V; ++j) s << "        gacc" << o << " = __fadd_rn(gacc" << o << ", " << val(j) << ");\n";
+        } else if (V == 4) {
+            s << "        *reinterpret_cast<float4*>(out" << o << " + e0) = make_float4(" << val(0) << ", " << val(1) << ", " << val(2) << ", " << val(3) << ");\n";
+        } else {
+            s << "        out" << o << "[e0] = " << val(0) << ";\n";
+        }
+    }
+    s << "    }\n";
+    if (n_global) {
+        s << "    __shared__ float gsm[" << n_global << "][" << NT / 32 << "];\n";
+        int gi = 0;
+        for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) {
+            s << "    gacc" << o << " = ormi_warp_sum(gacc" << o << ", 32);\n";
+            s << "    if ((threadIdx.x & 31) == 0) gsm[" << gi << "][threadIdx.x >> 5] = gacc" << o << ";\n";
+            ++gi;
+        }
+        s << "    __syncthreads();\n    if (threadIdx.x == 0) {\n";
+        gi = 0;
+        for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) {
+            s << "        { float a = 0.0f; for (int w = 0; w < " << NT / 32 << "; ++w) a = __fadd_rn(a, gsm[" << gi << "][w]); out" << o << "[blockIdx.x] = a; }\n";
+            ++gi;
+        }
+        s << "    }\n";
+    }
+    s << "}\n";
+
+    out.step.name = name;
+    out.step.source = s.str();
+    out.step.grid = grid;
+    out.step.block = NT;
+    out.cols = 1;
+    std::ostringstream w;
+    w << "flat[total=" << total << ",V=" << V << ",dims=" << cd << "] nodes=" << spec.nodes.size() << " loads=" << spec.loads.size() << " outs=" << spec.outputs.size();
+    out.step.what = w.str();
+    for (auto& l : spec.loads) out.step.bytes_read += touched_bytes(l, spec.D);
+    for (auto& o : spec.outputs) out.step.bytes_written += (o.kind == KOutput::GLOBALSUM) ? 4 * (int64_t)grid : total * 4;
+    return out;
+}
+
+// ---------------------------------------------------------------------------------------- rows template
+GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
+    GeneratedKernel out;
+    const size_t nd = spec.D.size();
+    const int k = spec.k;
+    auto unsupported = [&](const std::string& why) { out.error = "row template: " + why; out.unsupported_sums = true; return out; };
+    if (k < 1 || k >= (int)nd) return unsupported("no row/column split");
+    const int64_t R = prod(spec.D, 0, k), C = prod(spec.D, k, nd);
+
+    std::vector<LoadInfo> li(spec.loads.size());
+    bool need_row_coords = false;
+    for (size_t l = 0; l < spec.loads.size(); ++l) {
+        const auto& st = spec.loads[l].st;
+        LoadInfo& I = li[l];
+        for (size_t d = k; d + 1 < nd; ++d) if (st[d] != st[d + 1] * spec.D[d + 1]) return unsupported("operand columns are not uniformly strided");
+        I.sc = st[nd - 1];
+        I.elem = false;
+        for (size_t d = k; d < nd; ++d) if (st[d] != 0) I.elem = true;
+        if (!I.elem) I.sc = 0;
+        I.row_var = false;
+        for (int d = 0; d < k; ++d) if (st[d] != 0) I.row_var = true;
+        I.scalar = !I.elem && !I.row_var;
+        I.row_collapsed = true;
+        for (int d = 0; d + 1 < k; ++d) if (st[d] != st[d + 1] * spec.D[d + 1]) I.row_collapsed = false;
+        I.sr = st[k - 1];
+        if (I.row_var && !I.row_collapsed) need_row_coords = true;
+    }
+    int V = (C % 4 == 0) ? 4 : 1;
+    for (size_t l = 0; l < spec.loads.size() && V == 4; ++l) {
+        if (!li[l].elem) continue;
+        if (li[l].sc != 1) V = 1;
+        for (int d = 0; d < k; ++d) if (spec.loads[l].st[d] % 4 != 0) V = 1;
+    }
+    const int target = (V == 4) ? 16 : 8;
+    int T = std::min(1024, std::max(32, ceil_pow2((C + target - 1) / target)));
+    int64_t VPT = (C + T - 1) / T;
+    VPT = (VPT + V - 1) / V * V;
+    if (VPT > 32) return unsupported("row of " + std::to_string(C) + " elements does not fit in registers");
+    const int NT = std::max(T, 256), G = NT / T, NV = (int)VPT / V, NW = T / 32;
+    const bool col_pred = (VPT * T != C);
+    const bool row_pred = (R % G != 0);
+    int grid = (int)std::min<int64_t>((R + G - 1) / G, (int64_t)spec.num_sms * (NT <= 256 ? 4 : (NT <= 512 ? 2 : 1)));
+    if (grid < 1) grid = 1;
+
+    // levels
+    std::map<int, int> level;       // node -> level
+    std::map<int, const KNode*> by_id;
+    auto ref_level = [&](const KRef& r) { return r.t == KRef::LOAD ? 0 : level[r.id]; };
+    int max_level = 0, max_sums_per_level = 0;
+    std::map<int, int> sums_at;
+    for (const KNode& kn : spec.nodes) {
+        by_id[kn.node] = &kn;
+        int lv = 0;
+        for (auto& r : kn.operands) lv = std::max(lv, ref_level(r));
+        if (kn.op == KNode::OP_ROWSUM) { lv += 1; max_sums_per_level = std::max(max_sums_per_level, ++sums_at[lv]); }
+        level[kn.node] = lv;
+        max_level = std::max(max_level, lv);
+    }
+    auto rowv = [&](const KNode* kn) { return kn->row || kn->scalar; };
+    auto is_elem = [&](const KRef& r) { return r.t == KRef::LOAD ? li[r.id].elem : !rowv(by_id[r.id]); };
+    auto ref = [&](const KRef& r, const std::string& j) {
+        if (r.t == KRef::LOAD) return "L" + std::to_string(r.id) + (li[r.id].elem ? "[" + j + "]" : "");
+        return "v" + std::to_string(r.id) + (rowv(by_id[r.id]) ? "" : "[" + j + "]");
+    };
+    int n_col = 0, n_glob = 0;
+    for (auto& o : spec.outputs) { n_col += (o.kind == KOutput::COLSUM); n_glob += (o.kind == KOutput::GLOBALSUM); }
+
+    std::ostringstream s;
+    s << device_prelude();
+    s << "extern \"C\" __global__ void __launch_bounds__(" << NT << ") " << name << "(";
+    for (size_t l = 0; l < spec.loads.size(); ++l) s << (l ? ", " : "") << "const float* __restrict__ in" << l;
+    for (size_t o = 0; o < spec.outputs.size(); ++o) s << ((spec.loads.size() + o) ? ", " : "") << "float* __restrict__ out" << o;
+    s << ") {\n";
+    s << "    // rows=" << R << " cols=" << C << " threads/row=" << T << " rows/block=" << G << " elems/thread=" << VPT << " vec=" << V << "\n";
+    s << "    const int tid = threadIdx.x % " << T << ";\n    const int grp = threadIdx.x / " << T << ";\n";
+    if (max_sums_per_level && NW > 1) s << "    __shared__ float red[" << max_sums_per_level << "][" << G << "][" << NW << "];\n";
+    auto col_of = [&](const std::string& q, const std::string& e) { return "((" + q + ") * " + std::to_string(T) + " + tid) * " + std::to_string(V) + " + (" + e + ")"; };
+    auto emit_array_load = [&](size_t l, const std::string& ro, const std::string& ind, bool rowp) {
+        std::string L = "L" + std::to_string(l), P = "in" + std::to_string(l);
+        s << ind << "float " << L << "[" << VPT << "];\n";
+        s << ind << "#pragma unroll\n" << ind << "for (int q = 0; q < " << NV << "; ++q) {\n";
+        s << ind << "    const int col = " << col_of("q", "0") << ";\n";
+        std::string pred;
+        if (rowp) pred = "rok";
+        if (col_pred) pred += std::string(pred.empty() ? "" : " && ") + "col < " + std::to_string(C);
+        if (V == 4) {
+            s << ind << "    float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);\n";
+            s << ind << "    " << (pred.empty() ? "" : "if (" + pred + ") ") << "t = *reinterpret_cast<const float4*>(" << P << " + " << ro << " + col);\n";
+            s << ind << "    " << L << "[4 * q] = t.x; " << L << "[4 * q + 1] = t.y; " << L << "[4 * q + 2] = t.z; " << L << "[4 * q + 3] = t.w;\n";
+        } else {
+            s << ind << "    " << L << "[q] = " << (pred.empty() ? "" : "(" + pred + ") ? ") << P << "[" << ro << " + col * " << li[l].sc << "]" << (pred.empty() ? "" : " : 0.0f") << ";\n";
+        }
+        s << ind << "}\n";
+    };
+    // hoisted loads: row-invariant
+    for (size_t l = 0; l < spec.loads.size(); ++l) {
+        if (li[l].row_var) continue;
+        if (li[l].scalar) s << "    const float L" << l << " = in" << l << "[0];\n";
+        else emit_array_load(l, "0", "    ", false);
+    }
+    for (size_t o = 0; o < spec.outputs.size(); ++o) {
+        if (spec.outputs[o].kind == KOutput::COLSUM) { s << "    float cacc" << o << "[" << VPT << "];\n    #pragma unroll\n    for (int j = 0; j < " << VPT << "; ++j) cacc" << o << "[j] = 0.0f;\n"; }
+        if (spec.outputs[o].kind == KOutput::GLOBALSUM) s << "    float gacc" << o << " = 0.0f;\n";
+    }
+    s << "    for (int rb = blockIdx.x * " << G << "; rb < " << R << "; rb += gridDim.x * " << G << ") {\n";
+    s << "        const int r = rb + grp;\n";
+    if (row_pred) s << "        const bool rok = r < " << R << ";\n";
+    if (need_row_coords) {
+        s << "        int rrem = " << (row_pred ? "rok ? r : 0" : "r") << ";\n";
+        for (int d = k - 1; d >= 1; --d) s << "        const int rc" << d << " = rrem % " << spec.D[d] << "; rrem /= " << spec.D[d] << ";\n";
+        s << "        const int rc0 = rrem;\n";
+    }
+    for (size_t l = 0; l < spec.loads.size(); ++l) {
+        if (!li[l].row_var) continue;
+        std::string ro = "ro" + std::to_string(l);
+        if (li[l].row_collapsed) s << "        const int " << ro << " = r * " << li[l].sr << ";\n";
+        else {
+            s << "        const int " << ro << " = 0";
+            for (int d = 0; d < k; ++d) if (spec.loads[l].st[d] != 0) s << " + rc" << d << " * " << spec.loads[l].st[d];
+            s << ";\n";
+        }
+        if (li[l].elem) emit_array_load(l, ro, "        ", row_pred);
+        else s << "        const float L" << l << " = " << (row_pred ? "rok ? " : "") << "in" << l << "[" << ro << "]" << (row_pred ? " : 0.0f" : "") << ";\n";
+    }
+    for (const KNode& kn : spec.nodes) if (!rowv(&kn)) s << "        float v" << kn.node << "[" << VPT << "];\n";
+
+    auto ok_expr = [&](const std::string& j) {
+        std::string p;
+        if (row_pred) p = "rok";
+        if (col_pred) p += std::string(p.empty() ? "" : " && ") + "(" + col_of(j + " / " + std::to_string(V), j + " % " + std::to_string(V)) + ") < " + std::to_string(C);
+        return p;
+    };
+    for (int lv = 0; lv <= max_level; ++lv) {
+        // (a) per-row scalars of this level
+        for (const KNode& kn : spec.nodes) {
+            if (!rowv(&kn) || kn.op == KNode::OP_ROWSUM || level[kn.node] != lv) continue;
+            std::string a = ref(kn.operands[0], "0"), b = kn.operands.size() > 1 ? ref(kn.operands[1], "0") : "";
+            s << "        const float v" << kn.node << " = " << op_expr(kn.op, a, b) << ";\n";
+        }
+        // (b) per-element values of this level
+        bool any = false;
+        for (const KNode& kn : spec.nodes) if (!rowv(&kn) && level[kn.node] == lv) any = true;
+        if (any) {
+            s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) {\n";
+            for (const KNode& kn : spec.nodes) {
+                if (rowv(&kn) || level[kn.node] != lv) continue;
+                std::string a = ref(kn.operands[0], "j"), b = kn.operands.size() > 1 ? ref(kn.operands[1], "j") : "";
+                s << "            v" << kn.node << "[j] = " << op_expr(kn.op, a, b) << ";\n";
+            }
+            s << "        }\n";
+        }
+        // (c) row sums that become available after this level
+        std::vector<const KNode*> sums;
+        for (const KNode& kn : spec.nodes) if (kn.op == KNode::OP_ROWSUM && level[kn.node] == lv + 1) sums.push_back(&kn);
+        if (!sums.empty()) {
+            for (auto* kn : sums) s << "        float v" << kn->node << " = 0.0f;\n";
+            s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) {\n";
+            std::string ok = ok_expr("j");
+            if (!ok.empty()) s << "            const bool ok = " << ok << ";\n";
+            for (auto* kn : sums) {
+                std::string val = ref(kn->operands[0], "j");
+                s << "            v" << kn->node << " = __fadd_rn(v" << kn->node << ", " << (ok.empty() ? val : "ok ? " + val + " : 0.0f") << ");\n";
+            }
+            s << "        }\n";
+            for (auto* kn : sums) s << "        v" << kn->node << " = ormi_warp_sum(v" << kn->node << ", " << std::min(T, 32) << ");\n";
+            if (NW > 1) {
+                s << "        if ((threadIdx.x & 31) == 0) {";
+                for (size_t i = 0; i < sums.size(); ++i) s << " red[" << i << "][grp][tid >> 5] = v" << sums[i]->node << ";";
+                s << " }\n        __syncthreads();\n";
+                for (size_t i = 0; i < sums.size(); ++i)
+                    s << "        { float a = 0.0f; for (int w = 0; w < " << NW << "; ++w) a = __fadd_rn(a, red[" << i << "][grp][w]); v" << sums[i]->node << " = a; }\n";
+                s << "        __syncthreads();\n";
+            }
+        }
+    }
+    // outputs
+    for (size_t o = 0; o < spec.outputs.size(); ++o) {
+        const KOutput& ko = spec.outputs[o];
+        bool elem = is_elem(ko.value);
+        if (ko.kind == KOutput::FULL) {
+            s << "        #pragma unroll\n        for (int q = 0; q < " << NV << "; ++q) {\n            const int col = " << col_of("q", "0") << ";\n";
+            std::string pred;
+            if (row_pred) pred = "rok";
+            if (col_pred) pred += std::string(pred.empty() ? "" : " && ") + "col < " + std::to_string(C);
+            auto v = [&](int e) { return elem ? ref(ko.value, std::to_string(V) + " * q + " + std::to_string(e)) : ref(ko.value, "0"); };
+            s << "            " << (pred.empty() ? "" : "if (" + pred + ") ");
+            if (V == 4) s << "*reinterpret_cast<float4*>(out" << o << " + r * " << C << " + col) = make_float4(" << v(0) << ", " << v(1) << ", " << v(2) << ", " << v(3) << ");\n";
+            else s << "out" << o << "[r * " << C << " + col] = " << v(0) << ";\n";
+            s << "        }\n";
+        } else if (ko.kind == KOutput::ROW) {
+            s << "        if (tid == 0" << (row_pred ? " && rok" : "") << ") out" << o << "[r] = " << ref(ko.value, "0") << ";\n";
+        } else if (ko.kind == KOutput::COLSUM) {
+            s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) cacc" << o << "[j] = __fadd_rn(cacc" << o << "[j], "
+              << (row_pred ? "rok ? " + ref(ko.value, "j") + " : 0.0f" : ref(ko.value, "j")) << ");\n";
+        } else {
+            s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) {\n";
+            std::string ok = ok_expr("j");
+            s << "            gacc" << o << " = __fadd_rn(gacc" << o << ", " << (ok.empty() ? ref(ko.value, "j") : "(" + ok + ") ? " + ref(ko.value, "j") + " : 0.0f") << ");\n        }\n";
+        }
+    }
+    s << "    }\n";
+    // epilogue: one partial per block
+    if (n_col) {
+        if (G > 1) s << "    __shared__ float csm[" << G << "][" << T * VPT << "];\n";
+        for (size_t o = 0; o < spec.outputs.size(); ++o) {
+            if (spec.outputs[o].kind != KOutput::COLSUM) continue;
+            if (G > 1) {
+                s << "    #pragma unroll\n    for (int j = 0; j < " << VPT << "; ++j) csm[grp][j * " << T << " + tid] = cacc" << o << "[j];\n    __syncthreads();\n";
+                s << "    if (grp == 0) {\n        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) { float a = 0.0f; for (int g = 0; g < " << G << "; ++g) a = __fadd_rn(a, csm[g][j * " << T << " + tid]); cacc" << o << "[j] = a; }\n    }\n    __syncthreads();\n";
+            }
+            s << "    if (grp == 0) {\n        #pragma unroll\n        for (int q = 0; q < " << NV << "; ++q) {\n            const int col = " << col_of("q", "0") << ";\n";
+            s << "            " << (col_pred ? "if (col < " + std::to_string(C) + ") " : "");
+            if (V == 4) s << "*reinterpret_cast<float4*>(out" << o << " + blockIdx.x * " << C << " + col) = make_float4(cacc" << o << "[4 * q], cacc" << o << "[4 * q + 1], cacc" << o << "[4 * q + 2], cacc" << o << "[4 * q + 3]);\n";
+            else s << "out" << o << "[blockIdx.x * " << C << " + col] = cacc" << o << "[q];\n";
+            s << "        }\n    }\n";
+        }
+    }
+    if (n_glob) {
+        s << "    __shared__ float gsm[" << n_glob << "][" << NT / 32 << "];\n";
+        int gi = 0;
+        for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) {
+            s << "    gacc" << o << " = ormi_warp_sum(gacc" << o << ", 32);\n    if ((threadIdx.x & 31) == 0) gsm[" << gi << "][threadIdx.x >> 5] = gacc" << o << ";\n";
+            ++gi;
+        }
+        s << "    __syncthreads();\n    if (threadIdx.x == 0) {\n";
+        gi = 0;
+        for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) {
+            s << "        { float a = 0.0f; for (int w = 0; w < " << NT / 32 << "; ++w) a = __fadd_rn(a, gsm[" << gi << "][w]); out" << o << "[blockIdx.x] = a; }\n";
+            ++gi;
+        }
+        s << "    }\n";
+    }
+    s << "}\n";
+
+    out.step.name = name;
+    out.step.source = s.str();
+    out.step.grid = grid;
+    out.step.block = NT;
+    out.cols = C;
+    std::ostringstream w;
+    w << "rows[R=" << R << ",C=" << C << ",T=" << T << ",G=" << G << ",VPT=" << VPT << ",V=" << V << ",levels=" << max_level << "] nodes=" << spec.nodes.size()
+      << " loads=" << spec.loads.size() << " outs=";
+    for (auto& o : spec.outputs) w << (o.kind == KOutput::FULL ? "F" : o.kind == KOutput::ROW ? "R" : o.kind == KOutput::COLSUM ? "C" : "G");
+    out.step.what = w.str();
+    for (auto& l : spec.loads) out.step.bytes_read += touched_bytes(l, spec.D);
+    for (auto& o : spec.outputs) {
+        if (o.kind == KOutput::FULL) out.step.bytes_written += R * C * 4;
+        else if (o.kind == KOutput::ROW) out.step.bytes_written += R * 4;
+        else if (o.kind == KOutput::COLSUM) out.step.bytes_written += (int64_t)grid * C * 4;
+        else out.step.bytes_written += (int64_t)grid * 4;
+    }
+    return out;
+}
+
+}  // namespace
+
+GeneratedKernel generate_kernel(const KernelSpec& spec, const std::string& name, const ormi_b200_node*) {
+    bool rows = false;
+    for (auto& kn : spec.nodes) if (kn.row || kn.op == KNode::OP_ROWSUM) rows = true;
+    for (auto& o : spec.outputs) if (o.kind == KOutput::ROW || o.kind == KOutput::COLSUM) rows = true;
+    GeneratedKernel g = rows ? generate_rows(spec, name) : generate_flat(spec, name);
+    if (g.error.empty()) g.step.key = std::to_string(fnv1a(g.step.source));
+    return g;
+}
+
+GeneratedKernel generate_finalize(int parts, int64_t width, const std::string& name) {
+    GeneratedKernel g;
+    std::ostringstream s;
+    s << device_prelude();
+    if (width == 1) {
+        s << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const float* __restrict__ part, float* __restrict__ out) {\n"
+          << "    __shared__ float sm[8];\n    float a = 0.0f;\n"
+          << "    for (int p = threadIdx.x; p < " << parts << "; p += 256) a = __fadd_rn(a, part[p]);\n"
+          << "    a = ormi_warp_sum(a, 32);\n    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = a;\n    __syncthreads();\n"
+          << "    if (threadIdx.x == 0) { float t = 0.0f; for (int w = 0; w < 8; ++w) t = __fadd_rn(t, sm[w]); out[0] = t; }\n}\n";
+        g.step.grid = 1;
+    } else {
+        s << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const float* __restrict__ part, float* __restrict__ out) {\n"
+          << "    const int c = blockIdx.x * 256 + threadIdx.x;\n    if (c >= " << width << ") return;\n"
+          << "    float a = 0.0f;\n    for (int p = 0; p < " << parts << "; ++p) a = __fadd_rn(a, part[p * " << width << " + c]);\n    out[c] = a;\n}\n";
+        g.step.grid = (int)((width + 255) / 256);
+    }
+    g.step.block = 256;
+    g.step.name = name;
+    g.step.source = s.str();
+    g.step.key = std::to_string(fnv1a(g.step.source));
+    g.step.what = "finalize[parts=" + std::to_string(parts) + ",width=" + std::to_string(width) + "]";
+    g.step.bytes_read = (int64_t)parts * width * 4;
+    g.step.bytes_written = width * 4;
+    return g;
+}
+
+GeneratedKernel generate_generic_sum(const std::vector<int>& shape, const std::vector<int>& strides,
+                                     const std::vector<bool>& reduced, const std::string& name) {
+    GeneratedKernel g;
+    int64_t n_out = 1, n_red = 1;
+    for (size_t d = 0; d < shape.size(); ++d) (reduced[d] ? n_red : n_out) *= shape[d];
+    std::ostringstream s;
+    s << device_prelude();
+    s << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const float* __restrict__ in, float* __restrict__ out) {\n"
+      << "    const int o = blockIdx.x * 256 + threadIdx.x;\n    if (o >= " << n_out << ") return;\n    int base = 0;\n    {\n        int rem = o;\n";
+    for (size_t d = shape.size(); d-- > 0;) if (!reduced[d]) s << "        base += (rem % " << shape[d] << ") * " << strides[d] << "; rem /= " << shape[d] << ";\n";
+    s << "    }\n    float a = 0.0f;\n    for (int e = 0; e < " << n_red << "; ++e) {\n        int rem = e, off = base;\n";
+    for (size_t d = shape.size(); d-- > 0;) if (reduced[d]) s << "        off += (rem % " << shape[d] << ") * " << strides[d] << "; rem /= " << shape[d] << ";\n";
+    s << "        a = __fadd_rn(a, in[off]);\n    }\n    out[o] = a;\n}\n";
+    g.step.grid = (int)((n_out + 255) / 256);
+    g.step.block = 256;
+    g.step.name = name;
+    g.step.source = s.str();
+    g.step.key = std::to_string(fnv1a(g.step.source));
+    g.step.what = "generic_sum[out=" + std::to_string(n_out) + ",red=" + std::to_string(n_red) + "]";
+    g.step.bytes_read = n_out * n_red * 4;
+    g.step.bytes_written = n_out * 4;
+    return g;
+}
+
+// ---------------------------------------------------------------------------------------- reference-shaped compile()
+SimpleKernel compile_simple(const ormi_b200_node* nodes, int n_nodes, int root) {
+    SimpleKernel k;
+    if (root < 0 || root >= n_nodes) { k.error = "root out of range"; return k; }
+    std::map<int, std::string> visited;
+    struct Stmt { std::string var; int op; std::vector<std::string> operands; };
+    std::vector<Stmt> tape;
+    int var_counter = 0;
+    std::string err;
+    std::function<std::string(int)> build = [&](int i) -> std::string {
+        auto it = visited.find(i);
+        if (it != visited.end()) return it->second;
+        const auto& nd = nodes[i];
+        if (nd.data) {
+            std::string v = "val_LEAF_" + std::to_string(k.leaves.size());
+            k.leaves.push_back(i);
+            visited[i] = v;
+            return v;
+        }
+        std::vector<std::string> ops;
+        for (int p = 0; p < nd.n_parents; ++p) ops.push_back(build(nd.parents[p]));
+        if (nd.op == ORMI_OP_MATMUL) { err = "FATAL: MATMUL cannot be fused into a 1D element-wise kernel."; return "0"; }
+        if (!(nd.op >= ORMI_OP_NEG && nd.op <= ORMI_OP_POW)) { err = "CUDA JIT Compiler Error: No lowering rule registered for this operation."; return "0"; }
+        std::string v = "v" + std::to_string(var_counter++);
+        tape.push_back(Stmt{v, nd.op, ops});
+        visited[i] = v;
+        return v;
+    };
+    std::string root_var = build(root);
+    if (!err.empty()) { k.error = err; return k; }
+    const auto& rn = nodes[root];
+    k.tensor_size = 1;
+    for (int d = 0; d < rn.ndim; ++d) k.tensor_size *= rn.shape[d];
+    std::ostringstream s;
+    s << device_prelude();
+    s << "extern \"C\" __global__\nvoid fused_kernel(float* OUT_Z";
+    for (size_t l = 0; l < k.leaves.size(); ++l) s << ", const float* LEAF_" << l;
+    s << ") {\n    int idx = blockIdx.x * blockDim.x + threadIdx.x;\n    if (idx >= " << k.tensor_size << ") return;\n\n";
+    std::vector<int> ostr(rn.ndim, 1);
+    for (int d = rn.ndim - 2; d >= 0; --d) ostr[d] = ostr[d + 1] * rn.shape[d + 1];
+    for (size_t l = 0; l < k.leaves.size(); ++l) {
+        const auto& lf = nodes[k.leaves[l]];
+        bool scalar = lf.ndim == 0 || lf.data_bytes == 4;
+        if (scalar) { s << "    float val_LEAF_" << l << " = LEAF_" << l << "[0];\n"; continue; }
+        int off = rn.ndim - lf.ndim;
+        s << "    int leaf_idx_" << l << " = 0;\n    {\n        int rem = idx;\n";
+        for (int d = 0; d < rn.ndim; ++d) {
+            int od = d - off;
+            int st = (od >= 0 && lf.shape[od] != 1) ? lf.strides[od] : 0;
+            if (st != 0) s << "        leaf_idx_" << l << " += (rem / " << ostr[d] << ") * " << st << ";\n";
+            s << "        rem %= " << ostr[d] << ";\n";
+        }
+        s << "    }\n    float val_LEAF_" << l << " = LEAF_" << l << "[leaf_idx_" << l << "];\n";
+    }
+    s << "\n";
+    for (auto& st : tape) {
+        std::string e;
+        const std::string& a = st.operands[0];
+        const std::string b = st.operands.size() > 1 ? st.operands[1] : "";
+        switch (st.op) {   // plain C operators, as in ormi-core/csrc/backend/cuda/lowerings/pointwise.cpp:4-13; -fmad=false keeps them un-fused
+            case ORMI_OP_ADD: e = a + " + " + b; break;
+            case ORMI_OP_SUB: e = a + " - " + b; break;
+            case ORMI_OP_MUL: e = a + " * " + b; break;
+            case ORMI_OP_DIV: e = a + " / " + b; break;
+            case ORMI_OP_POW: e = "ormi_pow(" + a + ", " + b + ")"; break;
+            case ORMI_OP_NEG: e = "-" + a; break;
+            case ORMI_OP_EXP: e = "expf(" + a + ")"; break;
+            case ORMI_OP_LOG: e = "logf(" + a + ")"; break;
+            case ORMI_OP_SIN: e = "sinf(" + a + ")"; break;
+            case ORMI_OP_COS: e = "cosf(" + a + ")"; break;
+        }
+        s << "    float " << st.var << " = " << e << ";\n";
+    }
+    s << "\n    OUT_Z[idx] = " << root_var << ";\n}\n";
+    k.source = s.str();
+    return k;
+}
+
+}  // namespace ormi_b200

@@ -1,0 +1,108 @@
+// Per-device state of the backend: stream, buffer pool, kernel cache, plan cache, counters.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "plan.h"
+
+namespace ormi_b200 {
+
+struct Error : std::runtime_error { using std::runtime_error::runtime_error; };
+
+#define ORMI_CUDA(call)                                                                            \
+    do {                                                                                           \
+        cudaError_t e_ = (call);                                                                   \
+        if (e_ != cudaSuccess) throw ::ormi_b200::Error(std::string("CUDA Error: ") + cudaGetErrorString(e_) + " (" #call ")"); \
+    } while (0)
+
+// Driver entry points, fetched through the runtime so the library itself has no link-time dependency on
+// libcuda (it must load, and its symbols be listed, on a machine without a GPU driver).
+struct DriverApi {
+    CUresult (*ModuleLoadData)(CUmodule*, const void*) = nullptr;
+    CUresult (*ModuleUnload)(CUmodule) = nullptr;
+    CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+    CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**) = nullptr;
+    CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
+    CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
+    CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
+    void load();
+    void check(CUresult r, const char* what) const;
+};
+
+struct CompiledKernel {
+    CUmodule module = nullptr;
+    CUfunction func = nullptr;
+};
+
+struct CachedPlan {
+    Plan plan;
+    std::vector<CompiledKernel*> kernels;   // per step (nullptr for GEMM steps)
+};
+
+enum class MatmulMode { FP32, BF16, TF32, TF32X3 };
+
+}  // namespace ormi_b200
+
+struct ormi_b200_ctx {
+    int device = 0;
+    int num_sms = 148;
+    cudaStream_t stream = nullptr;
+    ormi_b200::DriverApi drv;
+
+    std::mutex pool_mutex;
+    std::unordered_map<size_t, std::vector<void*>> free_blocks;
+
+    std::unordered_map<std::string, ormi_b200::CompiledKernel> kernel_cache;   // source hash -> module
+    std::unordered_map<uint64_t, std::unique_ptr<ormi_b200::CachedPlan>> plan_cache;
+
+    ormi_b200::MatmulMode matmul_mode = ormi_b200::MatmulMode::FP32;
+    bool fusion = true;
+
+    // bf16 staging for the tensor-core GEMM path (grown on demand, reused across calls)
+    void* stage[2] = {nullptr, nullptr};
+    size_t stage_bytes[2] = {0, 0};
+
+    std::map<std::string, int64_t> counters;
+    void* nccl = nullptr;   // opaque: collective state (nccl.cpp)
+};
+
+namespace ormi_b200 {
+
+void* pool_alloc(ormi_b200_ctx* ctx, size_t bytes);
+void pool_free(ormi_b200_ctx* ctx, void* ptr, size_t bytes);
+
+// NVRTC: CUDA C -> sm_100a cubin.  Throws Error with the compiler log on failure.  Needs no device.
+std::vector<char> compile_cubin(const std::string& source, std::string* log = nullptr);
+
+CompiledKernel* get_kernel(ormi_b200_ctx* ctx, const KernelStep& k);
+void launch_kernel(ormi_b200_ctx* ctx, CompiledKernel* k, int grid, int block, std::vector<void*>& pointer_args);
+
+// GEMM launchers (gemm_ffma.cu, gemm_tcgen05.cu)
+struct GemmArgs {
+    const float* A; const float* B; float* C;
+    int M, N, K;
+    int trans_a, trans_b, lda, ldb;
+    int batch, nbatch;
+    int32_t bshape[ORMI_B200_MAX_DIMS];
+    int64_t astride[ORMI_B200_MAX_DIMS], bstride[ORMI_B200_MAX_DIMS];
+};
+void gemm_ffma(ormi_b200_ctx* ctx, const GemmArgs& g);
+void gemm_dispatch(ormi_b200_ctx* ctx, const GemmArgs& g);
+
+// `preassigned`: optional (node, pointer) pairs — write that node's value into a caller-owned buffer
+// instead of a fresh pool block (used by the raw-buffer sum / matmul entry points).
+void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots,
+             const std::vector<std::pair<int, void*>>* preassigned = nullptr);
+
+}  // namespace ormi_b200

@@ -1,0 +1,727 @@
+// Fusion scheduler of the realize path.
+//
+// Replaces the CUDA branch of ormi::execute_graph (ormi-core/csrc/backend/runtime.cpp:13-39), which
+// realizes every parent first and therefore runs one kernel per node, and the graph walk of
+// ormi::cuda::compile / build_ir (ormi-core/csrc/backend/cuda/compiler.cu:22-51).
+//
+// Input:  the flattened lazy graph (ormi_b200_node[], topologically ordered).
+// Output: a Plan — a handful of generated kernels, GEMM steps and the buffers that connect them.
+//
+// Method
+//   1. classify every node: realized input, view, pointwise, SUM (row / column / global / generic), MATMUL;
+//   2. give every un-realized compute node a *domain* (a squeezed shape D and a split k: rows = D[:k],
+//      columns = D[k:]) — a row SUM lives in the domain of its operand, and pointwise work on row sums
+//      stays in that domain too (that is what makes softmax / layernorm one kernel);
+//   3. decide which nodes must be written to memory (roots, externally held nodes, MATMUL operands and
+//      results, column/global sums, anything reached through a view that is not a plain
+//      broadcast/permutation-free mapping).  Everything else is recomputed inside the kernel that needs it;
+//   4. merge materialized nodes of one domain into multi-output kernels when that creates no cycle;
+//   5. emit each kernel (codegen.cpp) and order the steps topologically.
+#include <algorithm>
+#include <cstring>
+#include <functional>
+#include <map>
+#include <set>
+#include <sstream>
+
+#include "kernel_ir.h"
+#include "plan.h"
+
+namespace ormi_b200 {
+
+namespace {
+
+bool is_view_op(int op) { return op == ORMI_OP_TRANSPOSE || op == ORMI_OP_RESHAPE || op == ORMI_OP_EXPAND; }
+bool is_pw_op(int op) { return op >= ORMI_OP_NEG && op <= ORMI_OP_POW; }
+
+enum Kind { K_NONE, K_INPUT, K_VIEW, K_PW, K_IDSUM, K_ROWSUM, K_COLSUM, K_GLOBALSUM, K_GENSUM, K_MATMUL };
+
+struct Info {
+    Kind kind = K_NONE;
+    bool needed = false;
+    std::vector<int> shape, strides, sq;
+    int64_t numel = 1;
+    int base = -1;                 // K_VIEW: first non-view ancestor
+    std::vector<int> vmap;         // K_VIEW over an un-realized base: view dim -> base dim, or -1
+    bool vmap_ok = false;
+    std::vector<int> D;            // domain of an un-realized compute node
+    int k = -1;                    // split; -1: any
+    bool row_cls = false;          // value per row (row sum, or pointwise work on row sums)
+    bool in_M = false;             // materialized
+    int step = -1;                 // step that produces it
+};
+
+std::vector<int> squeeze(const std::vector<int>& s) {
+    std::vector<int> r;
+    for (int v : s) if (v != 1) r.push_back(v);
+    return r;
+}
+
+std::vector<int> contiguous(const std::vector<int>& shape) {
+    std::vector<int> st(shape.size(), 1);
+    for (int i = (int)shape.size() - 2; i >= 0; --i) st[i] = st[i + 1] * shape[i + 1];
+    return st;
+}
+
+// canonical dim map of a value with `shape` inside a domain: the non-1 dims, in order, are driven by
+// domain dims 0,1,2,...
+std::vector<int> canonical_dm(const std::vector<int>& shape) {
+    std::vector<int> dm(shape.size(), -1);
+    int next = 0;
+    for (size_t j = 0; j < shape.size(); ++j) if (shape[j] != 1) dm[j] = next++;
+    return dm;
+}
+
+struct Scheduler {
+    const ormi_b200_node* nodes;
+    int n;
+    SchedOptions opt;
+    std::vector<Info> info;
+    std::set<int> force_generic;   // SUM nodes the fused templates could not take
+    std::string error;
+
+    struct Dep { int node; bool mergeable; };
+
+    Scheduler(const ormi_b200_node* nd, int count, const SchedOptions& o) : nodes(nd), n(count), opt(o) {}
+
+    bool fail(const std::string& msg) { if (error.empty()) error = msg; return false; }
+
+    // ------------------------------------------------------------------ classification
+    bool classify(const int* roots, int n_roots) {
+        info.assign(n, Info());
+        for (int i = 0; i < n; ++i) {
+            const auto& nd = nodes[i];
+            if (nd.ndim < 0 || nd.ndim > ORMI_B200_MAX_DIMS) return fail("node with a bad rank");
+            Info& I = info[i];
+            I.shape.assign(nd.shape, nd.shape + nd.ndim);
+            I.strides.assign(nd.strides, nd.strides + nd.ndim);
+            I.sq = squeeze(I.shape);
+            for (int s : I.shape) { if (s <= 0) return fail("empty or negative dimension"); I.numel *= s; }
+            if (I.numel >= (int64_t(1) << 31)) return fail("tensor with 2^31 or more elements");
+            for (int p = 0; p < nd.n_parents; ++p)
+                if (nd.parents[p] < 0 || nd.parents[p] >= i) return fail("graph is not in topological order");
+        }
+        // needed set
+        std::vector<int> stack(roots, roots + n_roots);
+        while (!stack.empty()) {
+            int i = stack.back(); stack.pop_back();
+            if (i < 0 || i >= n) return fail("root index out of range");
+            if (info[i].needed) continue;
+            info[i].needed = true;
+            if (nodes[i].data) continue;
+            for (int p = 0; p < nodes[i].n_parents; ++p) stack.push_back(nodes[i].parents[p]);
+        }
+        for (int i = 0; i < n; ++i) {
+            Info& I = info[i];
+            if (!I.needed) continue;
+            const auto& nd = nodes[i];
+            if (nd.data) { I.kind = K_INPUT; continue; }
+            if (nd.op == ORMI_OP_LEAF || nd.op == ORMI_OP_CONST) return fail("leaf without data");
+            if (is_view_op(nd.op)) {
+                if (nd.n_parents != 1) return fail("view op needs one parent");
+                I.kind = K_VIEW;
+                int p = nd.parents[0];
+                I.base = info[p].kind == K_VIEW ? info[p].base : p;
+                if (info[I.base].kind != K_INPUT) compute_vmap(i);
+                continue;
+            }
+            if (nd.op == ORMI_OP_MATMUL) { if (nd.n_parents != 2) return fail("MATMUL needs two parents"); I.kind = K_MATMUL; continue; }
+            if (nd.op == ORMI_OP_SUM) { if (nd.n_parents != 1) return fail("SUM needs one parent"); if (!classify_sum(i)) return false; continue; }
+            if (is_pw_op(nd.op)) {
+                int want = (nd.op <= ORMI_OP_COS) ? 1 : 2;
+                if (nd.n_parents != want) return fail("pointwise op with a wrong operand count");
+                I.kind = K_PW;
+                classify_pw(i);
+                continue;
+            }
+            return fail("op " + std::to_string(nd.op) + " has no CUDA lowering");
+        }
+        return true;
+    }
+
+    // view dims -> dims of the (contiguous, once materialized) base
+    void compute_vmap(int v) {
+        Info& V = info[v];
+        const Info& B = info[V.base];
+        std::vector<int> cs = contiguous(B.shape);
+        V.vmap.assign(V.shape.size(), -1);
+        std::vector<bool> used(B.shape.size(), false);
+        bool ok = true;
+        for (size_t j = 0; j < V.shape.size() && ok; ++j) {
+            if (V.shape[j] == 1 || V.strides[j] == 0) continue;
+            bool found = false;
+            for (size_t d = 0; d < B.shape.size(); ++d) {
+                if (!used[d] && B.shape[d] != 1 && cs[d] == V.strides[j] && B.shape[d] == V.shape[j]) {
+                    used[d] = true; V.vmap[j] = (int)d; found = true; break;
+                }
+            }
+            if (!found) ok = false;
+        }
+        for (size_t d = 0; d < B.shape.size() && ok; ++d) if (B.shape[d] != 1 && !used[d]) ok = false;
+        V.vmap_ok = ok;
+    }
+
+    bool classify_sum(int i) {
+        Info& I = info[i];
+        const auto& nd = nodes[i];
+        int p = nd.parents[0];
+        const Info& P = info[p];
+        std::vector<bool> red(P.shape.size(), nd.n_axes == 0);
+        for (int a = 0; a < nd.n_axes; ++a) {
+            if (nd.axes[a] < 0 || nd.axes[a] >= (int)P.shape.size()) return fail("SUM axis out of range");
+            red[nd.axes[a]] = true;
+        }
+        int64_t kept = 1;
+        for (size_t d = 0; d < P.shape.size(); ++d) if (!red[d]) kept *= P.shape[d];
+        if (kept != I.numel) return fail("SUM output shape does not match its axes");
+        std::vector<bool> sred;
+        for (size_t d = 0; d < P.shape.size(); ++d) if (P.shape[d] != 1) sred.push_back(red[d]);
+        int nd_sq = (int)sred.size(), nred = 0;
+        for (bool b : sred) nred += b;
+        I.D = P.sq;
+        bool parent_plain = (P.kind != K_VIEW) && !force_generic.count(i) && opt.fusion;
+        if (nred == 0) { I.kind = K_IDSUM; I.k = -1; if (P.kind == K_VIEW || !opt.fusion) { I.kind = K_GENSUM; } return inherit_idsum(i); }
+        if (!parent_plain) { I.kind = K_GENSUM; return true; }
+        if (nred == nd_sq) { I.kind = K_GLOBALSUM; I.k = -1; return true; }
+        bool trailing = true, leading = true;
+        for (int d = 0; d < nd_sq; ++d) {
+            if (sred[d] != (d >= nd_sq - nred)) trailing = false;
+            if (sred[d] != (d < nred)) leading = false;
+        }
+        if (trailing) { I.kind = K_ROWSUM; I.k = nd_sq - nred; I.row_cls = true; return true; }
+        if (leading) { I.kind = K_COLSUM; I.k = nred; return true; }
+        I.kind = K_GENSUM;
+        return true;
+    }
+
+    // a SUM over size-1 axes copies its operand: it behaves like a unary pointwise op
+    bool inherit_idsum(int i) {
+        Info& I = info[i];
+        if (I.kind != K_IDSUM) return true;
+        const Info& P = info[nodes[i].parents[0]];
+        I.D = I.sq;
+        if ((P.kind == K_PW || P.kind == K_IDSUM || P.kind == K_ROWSUM) && !P.D.empty()) {
+            if (P.row_cls && std::vector<int>(P.D.begin(), P.D.begin() + P.k) == I.sq && P.D != I.sq) { I.D = P.D; I.k = P.k; I.row_cls = true; }
+            else if (P.D == I.sq) I.k = P.k;
+        }
+        return true;
+    }
+
+    // un-realized compute operand behind an operand index (through plain views), or -1
+    int compute_base(int o) const {
+        const Info& O = info[o];
+        if (O.kind == K_VIEW) {
+            if (info[O.base].kind == K_INPUT || !O.vmap_ok) return -1;
+            return O.base;
+        }
+        if (O.kind == K_INPUT) return -1;
+        return o;
+    }
+
+    void classify_pw(int i) {
+        Info& I = info[i];
+        I.D = I.sq;
+        I.k = -1;
+        I.row_cls = false;
+        if (!opt.fusion) return;
+        const auto& nd = nodes[i];
+        bool full_match = false;
+        int row_src = -1;
+        for (int p = 0; p < nd.n_parents; ++p) {
+            int q = compute_base(nd.parents[p]);
+            if (q < 0) continue;
+            const Info& Q = info[q];
+            if (Q.kind != K_PW && Q.kind != K_ROWSUM && Q.kind != K_IDSUM) continue;
+            if (Q.D == I.sq) { full_match = true; if (I.k < 0 && Q.k >= 0) I.k = Q.k; }
+            else if (Q.row_cls && Q.k >= 0 && std::vector<int>(Q.D.begin(), Q.D.begin() + Q.k) == I.sq && row_src < 0) row_src = q;
+        }
+        if (!full_match && row_src >= 0) { I.D = info[row_src].D; I.k = info[row_src].k; I.row_cls = true; }
+    }
+
+    // ------------------------------------------------------------------ walking one kernel
+    struct Walk {
+        std::vector<int> D; int k;
+        std::set<int> outputs;                 // M nodes computed by this kernel
+        std::vector<int> members;              // in-kernel nodes (sorted later)
+        std::set<int> member_set;
+        std::vector<KLoad> loads;
+        std::map<int, std::vector<KRef>> operands;   // node -> operand refs
+        std::vector<Dep> deps;                 // un-realized boundary nodes
+        bool k_conflict = false;
+    };
+
+    static std::vector<int64_t> strides_over_domain(const std::vector<int>& dm, const std::vector<int>& st, size_t nd) {
+        std::vector<int64_t> r(nd, 0);
+        for (size_t j = 0; j < dm.size(); ++j) if (dm[j] >= 0) r[dm[j]] += st[j];
+        return r;
+    }
+
+    int add_load(Walk& w, int src, const std::vector<int64_t>& st) {
+        for (size_t i = 0; i < w.loads.size(); ++i) if (w.loads[i].src_node == src && w.loads[i].st == st) return (int)i;
+        w.loads.push_back(KLoad{src, st});
+        return (int)w.loads.size() - 1;
+    }
+
+    bool k_compatible(int a, int b) const { return a < 0 || b < 0 || a == b; }
+
+    // Is compute node q, reached with dim map dm, a value this kernel can hold in registers?
+    bool eligible(const Walk& w, int q, const std::vector<int>& dm) const {
+        const Info& Q = info[q];
+        if (!opt.fusion) return false;
+        if (Q.kind != K_PW && Q.kind != K_ROWSUM && Q.kind != K_IDSUM) return false;
+        if ((Q.kind == K_PW || Q.kind == K_IDSUM) && Q.numel == 1) return true;   // scalar arithmetic rides along in any kernel
+        if (Q.D != w.D || !k_compatible(Q.k, w.k)) return false;
+        if (dm != canonical_dm(Q.shape)) return false;
+        if (Q.row_cls) {
+            if (Q.k < 0 || (int)Q.sq.size() != Q.k) return false;
+        } else if (Q.sq != w.D) return false;
+        return true;
+    }
+
+    // Resolves operand `o` (seen with dim map dm over o's own dims) into a register value or a load.
+    KRef resolve(Walk& w, int o, const std::vector<int>& dm, bool discover) {
+        const Info& O = info[o];
+        size_t nd = w.D.size();
+        if (O.kind == K_INPUT) {
+            std::vector<int64_t> st(nd, 0);
+            if (!(O.shape.empty() || nodes[o].data_bytes == 4)) st = strides_over_domain(dm, O.strides, nd);
+            return KRef{KRef::LOAD, add_load(w, o, st)};
+        }
+        if (O.kind == K_VIEW) {
+            int b = O.base;
+            const Info& B = info[b];
+            if (B.kind == K_INPUT) {
+                std::vector<int64_t> st(nd, 0);
+                if (nodes[b].data_bytes != 4) st = strides_over_domain(dm, O.strides, nd);
+                return KRef{KRef::LOAD, add_load(w, b, st)};
+            }
+            if (O.vmap_ok) {
+                std::vector<int> dmb(B.shape.size(), -1);
+                for (size_t j = 0; j < O.vmap.size(); ++j) if (O.vmap[j] >= 0) dmb[O.vmap[j]] = dm[j];
+                if (eligible(w, b, dmb) && (!info[b].in_M || w.outputs.count(b))) return enter(w, b, discover);
+                bool mergeable = eligible(w, b, dmb);
+                return boundary(w, b, strides_over_domain(dm, O.strides, nd), mergeable, discover);
+            }
+            return boundary(w, b, strides_over_domain(dm, O.strides, nd), false, discover);
+        }
+        // un-realized compute node
+        if (eligible(w, o, dm) && (!O.in_M || w.outputs.count(o))) return enter(w, o, discover);
+        return boundary(w, o, strides_over_domain(dm, contiguous(O.shape), nd), eligible(w, o, dm), discover);
+    }
+
+    KRef boundary(Walk& w, int q, const std::vector<int64_t>& st, bool mergeable, bool discover) {
+        if (discover) info[q].in_M = true;
+        bool seen = false;
+        for (auto& d : w.deps) if (d.node == q) { seen = true; d.mergeable = d.mergeable && mergeable; }
+        if (!seen) w.deps.push_back(Dep{q, mergeable});
+        return KRef{KRef::LOAD, add_load(w, q, st)};
+    }
+
+    KRef enter(Walk& w, int q, bool discover) {
+        if (!w.member_set.count(q)) {
+            w.member_set.insert(q);
+            const Info& Q = info[q];
+            if (Q.k >= 0) { if (w.k < 0) w.k = Q.k; else if (w.k != Q.k) w.k_conflict = true; }
+            std::vector<KRef> ops;
+            const auto& nd = nodes[q];
+            if (Q.kind == K_PW) {
+                std::vector<int> dmq = canonical_dm(Q.shape);
+                for (int p = 0; p < nd.n_parents; ++p) {
+                    const Info& P = info[nd.parents[p]];
+                    int off = (int)Q.shape.size() - (int)P.shape.size();
+                    std::vector<int> dmo(P.shape.size(), -1);
+                    for (size_t j = 0; j < P.shape.size(); ++j) dmo[j] = (P.shape[j] == 1) ? -1 : dmq[j + off];
+                    ops.push_back(resolve(w, nd.parents[p], dmo, discover));
+                }
+            } else {  // K_ROWSUM / K_IDSUM: the operand is seen in its own canonical layout
+                const Info& P = info[nd.parents[0]];
+                ops.push_back(resolve(w, nd.parents[0], canonical_dm(P.shape), discover));
+            }
+            w.operands[q] = ops;
+            w.members.push_back(q);
+        }
+        return KRef{KRef::NODE, q};
+    }
+
+    // domain of the kernel that computes materialized node m
+    void kernel_domain(int m, std::vector<int>& D, int& k) const {
+        const Info& I = info[m];
+        D = I.D; k = I.k;
+    }
+
+    // value of a terminal sum's operand (register value or load)
+    KRef sum_operand(Walk& w, int m, bool discover) {
+        int p = nodes[m].parents[0];
+        return resolve(w, p, canonical_dm(info[p].shape), discover);
+    }
+
+    void walk_output(Walk& w, int m, bool discover, std::vector<KOutput>* outs) {
+        const Info& I = info[m];
+        KOutput o;
+        o.node = m;
+        if (I.kind == K_PW || I.kind == K_IDSUM || I.kind == K_ROWSUM) {
+            o.kind = I.row_cls ? KOutput::ROW : KOutput::FULL;
+            o.value = enter(w, m, discover);
+        } else if (I.kind == K_COLSUM) {
+            o.kind = KOutput::COLSUM;
+            if (w.k < 0) w.k = I.k; else if (w.k != I.k) w.k_conflict = true;
+            o.value = sum_operand(w, m, discover);
+        } else {  // K_GLOBALSUM
+            o.kind = KOutput::GLOBALSUM;
+            o.value = sum_operand(w, m, discover);
+        }
+        if (outs) outs->push_back(o);
+    }
+
+    bool fusable_output(int m) const {
+        Kind kd = info[m].kind;
+        return kd == K_PW || kd == K_IDSUM || kd == K_ROWSUM || kd == K_COLSUM || kd == K_GLOBALSUM;
+    }
+
+    // source buffer + logical view of a MATMUL / generic-SUM operand; marks bases for materialization
+    void operand_view(int o, int& src, std::vector<int>& shape, std::vector<int>& strides, bool discover) {
+        const Info& O = info[o];
+        shape = O.shape;
+        if (O.kind == K_INPUT) { src = o; strides = O.strides; return; }
+        if (O.kind == K_VIEW) { src = O.base; strides = O.strides; if (info[src].kind != K_INPUT && discover) info[src].in_M = true; return; }
+        src = o; strides = contiguous(O.shape);
+        if (discover) info[o].in_M = true;
+    }
+
+    // ------------------------------------------------------------------ the plan
+    Plan run(const int* roots, int n_roots);
+};
+
+struct StepNode {
+    enum T { FUSED, GEMM, GENSUM } type;
+    std::vector<int> outputs;     // M nodes
+    std::vector<int> D; int k = -1;
+    std::set<int> succ;
+};
+
+Plan Scheduler::run(const int* roots, int n_roots) {
+    Plan plan;
+    if (!classify(roots, n_roots)) { plan.error = error; return plan; }
+
+    // ---- 3. materialization set
+    std::vector<int> root_bases;
+    for (int r = 0; r < n_roots; ++r) {
+        int i = roots[r];
+        if (info[i].kind == K_INPUT) continue;
+        int b = info[i].kind == K_VIEW ? info[i].base : i;
+        if (info[b].kind != K_INPUT) info[b].in_M = true;
+    }
+    for (int i = 0; i < n; ++i) {
+        if (!info[i].needed || info[i].kind == K_INPUT) continue;
+        if (nodes[i].flags & ORMI_NODE_KEEP) {
+            int b = info[i].kind == K_VIEW ? info[i].base : i;
+            if (info[b].kind != K_INPUT) info[b].in_M = true;
+        }
+        if (info[i].kind == K_MATMUL || info[i].kind == K_GENSUM || info[i].kind == K_COLSUM || info[i].kind == K_GLOBALSUM) info[i].in_M = true;
+        if (!opt.fusion && info[i].kind != K_VIEW) info[i].in_M = true;
+    }
+    // Discovery runs from the last node to the first: a walk only ever marks nodes with a lower index, so
+    // every materialized node is visited after it was marked.  The dependency lists are taken in a second
+    // sweep, once the set is final (a node walked through here may have been materialized later on).
+    std::vector<std::vector<Dep>> deps(n);
+    for (int pass = 0; pass < 2; ++pass)
+    for (int m = n - 1; m >= 0; --m) {
+        if (!info[m].in_M) continue;
+        if (fusable_output(m)) {
+            Walk w; kernel_domain(m, w.D, w.k);
+            w.outputs.insert(m);
+            walk_output(w, m, pass == 0, nullptr);
+            deps[m] = w.deps;
+        } else if (pass == 0) {
+            const auto& nd = nodes[m];
+            for (int p = 0; p < nd.n_parents; ++p) {
+                int src; std::vector<int> sh, st;
+                operand_view(nd.parents[p], src, sh, st, true);
+                if (info[src].kind != K_INPUT) deps[m].push_back(Dep{src, false});
+            }
+        }
+    }
+
+    // ---- 4. steps: merge materialized nodes of one domain into multi-output kernels
+    std::vector<StepNode> steps;
+    auto reaches = [&](int from, int to) {
+        std::vector<int> st{from}; std::set<int> seen;
+        while (!st.empty()) { int s = st.back(); st.pop_back(); if (s == to) return true; if (!seen.insert(s).second) continue; for (int t : steps[s].succ) st.push_back(t); }
+        return false;
+    };
+    for (int m = 0; m < n; ++m) {
+        if (!info[m].in_M) continue;
+        int chosen = -1;
+        if (fusable_output(m)) {
+            std::vector<int> D; int k; kernel_domain(m, D, k);
+            for (int s = (int)steps.size() - 1; s >= 0 && chosen < 0; --s) {
+                StepNode& S = steps[s];
+                if (S.type != StepNode::FUSED || S.D != D || !k_compatible(S.k, k)) continue;
+                bool ok = true;
+                for (const Dep& d : deps[m]) {
+                    int ds = info[d.node].step;
+                    if (ds == s) { if (!d.mergeable) { ok = false; break; } }
+                    else if (reaches(s, ds)) { ok = false; break; }
+                }
+                if (ok) chosen = s;
+            }
+            if (chosen < 0) {
+                StepNode S; S.type = StepNode::FUSED; S.D = D; S.k = k;
+                steps.push_back(S); chosen = (int)steps.size() - 1;
+            }
+            if (steps[chosen].k < 0) steps[chosen].k = k;
+        } else {
+            StepNode S; S.type = info[m].kind == K_MATMUL ? StepNode::GEMM : StepNode::GENSUM;
+            steps.push_back(S); chosen = (int)steps.size() - 1;
+        }
+        steps[chosen].outputs.push_back(m);
+        info[m].step = chosen;
+        for (const Dep& d : deps[m]) { int ds = info[d.node].step; if (ds != chosen) steps[ds].succ.insert(chosen); }
+    }
+
+    // ---- 5. buffers
+    std::map<int, int> buf_of_node;   // node -> plan buffer
+    auto buffer_for = [&](int node) {
+        auto it = buf_of_node.find(node);
+        if (it != buf_of_node.end()) return it->second;
+        PlanBuffer b;
+        b.kind = info[node].kind == K_INPUT ? BufKind::External : BufKind::NodeOut;
+        b.node = node;
+        b.bytes = info[node].kind == K_INPUT ? nodes[node].data_bytes : std::max<int64_t>(4, info[node].numel * 4);
+        plan.buffers.push_back(b);
+        buf_of_node[node] = (int)plan.buffers.size() - 1;
+        return (int)plan.buffers.size() - 1;
+    };
+    auto temp_buffer = [&](int64_t bytes) {
+        plan.buffers.push_back(PlanBuffer{BufKind::Temp, -1, std::max<int64_t>(4, bytes)});
+        return (int)plan.buffers.size() - 1;
+    };
+
+    // topological order of the steps (Kahn, lowest first output first)
+    std::vector<int> indeg(steps.size(), 0), order;
+    for (auto& S : steps) for (int t : S.succ) indeg[t]++;
+    std::set<std::pair<int, int>> ready;
+    for (size_t s = 0; s < steps.size(); ++s) if (!indeg[s]) ready.insert({steps[s].outputs[0], (int)s});
+    while (!ready.empty()) {
+        int s = ready.begin()->second; ready.erase(ready.begin());
+        order.push_back(s);
+        for (int t : steps[s].succ) if (--indeg[t] == 0) ready.insert({steps[t].outputs[0], t});
+    }
+    if (order.size() != steps.size()) { plan.error = "internal: cyclic kernel graph"; return plan; }
+
+    int kernel_serial = 0;
+    for (int s : order) {
+        StepNode& S = steps[s];
+        if (S.type == StepNode::GEMM) {
+            int m = S.outputs[0];
+            const auto& nd = nodes[m];
+            int srcs[2]; std::vector<int> sh[2], st[2];
+            for (int p = 0; p < 2; ++p) operand_view(nd.parents[p], srcs[p], sh[p], st[p], false);
+            for (int p = 0; p < 2; ++p) if (sh[p].size() < 2) { plan.error = "MATMUL requires operands to have at least 2 dimensions."; return plan; }
+            GemmStep g;
+            g.node = m;
+            int na = (int)sh[0].size(), nb = (int)sh[1].size();
+            g.M = sh[0][na - 2]; g.K = sh[0][na - 1]; g.N = sh[1][nb - 1];
+            if (sh[1][nb - 2] != g.K) { plan.error = "MATMUL inner dimensions must match (K_a != K_b)."; return plan; }
+            int bufs[2];
+            for (int p = 0; p < 2; ++p) {
+                int nd_p = (int)sh[p].size();
+                int rows = sh[p][nd_p - 2], cols = sh[p][nd_p - 1];
+                int s_row = st[p][nd_p - 2], s_col = st[p][nd_p - 1];
+                bool ok_n = (s_col == 1 || cols == 1) && (rows == 1 || s_row >= cols);
+                bool ok_t = (s_row == 1 || rows == 1) && (cols == 1 || s_col >= rows);
+                bufs[p] = buffer_for(srcs[p]);
+                if (!ok_n && !ok_t) {
+                    // neither row- nor column-contiguous: gather into a contiguous temporary first
+                    KernelSpec ks;
+                    ks.D = squeeze(sh[p]);
+                    ks.k = -1;
+                    ks.num_sms = opt.num_sms;
+                    std::vector<int> dm = canonical_dm(sh[p]);
+                    KLoad ld{srcs[p], strides_over_domain(dm, st[p], ks.D.size())};
+                    ks.loads.push_back(ld);
+                    KOutput o; o.node = -1; o.kind = KOutput::FULL; o.value = KRef{KRef::LOAD, 0};
+                    ks.outputs.push_back(o);
+                    int64_t elems = 1; for (int v : sh[p]) elems *= v;
+                    int tmp = temp_buffer(elems * 4);
+                    GeneratedKernel gk = generate_kernel(ks, "ormi_gather_" + std::to_string(kernel_serial++), nodes);
+                    if (!gk.error.empty()) { plan.error = gk.error; return plan; }
+                    Step stp; stp.type = Step::Kernel; stp.k = gk.step;
+                    stp.k.args = {bufs[p], tmp};
+                    plan.steps.push_back(stp);
+                    bufs[p] = tmp;
+                    st[p] = contiguous(sh[p]);
+                    s_row = st[p][nd_p - 2]; s_col = st[p][nd_p - 1];
+                    ok_n = true;
+                }
+                bool trans = !ok_n;
+                int ld = trans ? s_col : s_row;
+                if (trans && cols == 1) ld = std::max(ld, rows);
+                if (!trans && rows == 1) ld = std::max(ld, cols);
+                if (p == 0) { g.trans_a = trans; g.lda = ld; } else { g.trans_b = trans; g.ldb = ld; }
+            }
+            g.a = bufs[0]; g.b = bufs[1]; g.c = buffer_for(m);
+            const Info& Mo = info[m];
+            g.nbatch = (int)Mo.shape.size() - 2;
+            g.batch = 1;
+            for (int d = 0; d < g.nbatch; ++d) {
+                g.bshape[d] = Mo.shape[d]; g.batch *= Mo.shape[d];
+                for (int p = 0; p < 2; ++p) {
+                    int td = d - (g.nbatch - ((int)sh[p].size() - 2));
+                    int64_t v = (td >= 0 && sh[p][td] > 1) ? st[p][td] : 0;
+                    (p == 0 ? g.astride : g.bstride)[d] = v;
+                }
+            }
+            Step stp; stp.type = Step::Gemm; stp.g = g;
+            plan.steps.push_back(stp);
+            continue;
+        }
+        if (S.type == StepNode::GENSUM) {
+            int m = S.outputs[0];
+            int src; std::vector<int> sh, st;
+            operand_view(nodes[m].parents[0], src, sh, st, false);
+            std::vector<bool> red(sh.size(), nodes[m].n_axes == 0);
+            for (int a = 0; a < nodes[m].n_axes; ++a) red[nodes[m].axes[a]] = true;
+            if (info[src].kind == K_INPUT && nodes[src].data_bytes == 4) std::fill(st.begin(), st.end(), 0);
+            GeneratedKernel gk = generate_generic_sum(sh, st, red, "ormi_sum_" + std::to_string(kernel_serial++));
+            Step stp; stp.type = Step::Kernel; stp.k = gk.step;
+            stp.k.args = {buffer_for(src), buffer_for(m)};
+            plan.steps.push_back(stp);
+            continue;
+        }
+        // fused kernel: final walk over all outputs
+        Walk w; w.D = S.D; w.k = S.k;
+        for (int m : S.outputs) w.outputs.insert(m);
+        KernelSpec ks;
+        for (int m : S.outputs) walk_output(w, m, false, &ks.outputs);
+        if (w.k_conflict) { plan.error = "internal: kernel with two different row/column splits"; return plan; }
+        std::sort(w.members.begin(), w.members.end());
+        ks.D = w.D; ks.k = w.k; ks.num_sms = opt.num_sms;
+        ks.loads = w.loads;
+        for (int q : w.members) {
+            KNode kn;
+            kn.node = q;
+            kn.op = info[q].kind == K_PW ? nodes[q].op : (info[q].kind == K_ROWSUM ? KNode::OP_ROWSUM : KNode::OP_ID);
+            kn.row = info[q].row_cls;
+            kn.scalar = (info[q].kind == K_PW || info[q].kind == K_IDSUM) && info[q].numel == 1 && !w.D.empty();
+            kn.operands = w.operands[q];
+            ks.nodes.push_back(kn);
+        }
+        GeneratedKernel gk = generate_kernel(ks, "ormi_fused_" + std::to_string(kernel_serial++), nodes);
+        if (!gk.error.empty()) {
+            if (gk.unsupported_sums) {   // the row/column template cannot take this shape: retry with generic sums
+                bool added = false;
+                for (int q : w.members) if (info[q].kind == K_ROWSUM) added |= force_generic.insert(q).second;
+                for (int m : S.outputs) if (info[m].kind == K_ROWSUM || info[m].kind == K_COLSUM) added |= force_generic.insert(m).second;
+                if (added) return run(roots, n_roots);
+            }
+            plan.error = gk.error; return plan;
+        }
+        Step stp; stp.type = Step::Kernel; stp.k = gk.step;
+        for (const KLoad& l : ks.loads) stp.k.args.push_back(buffer_for(l.src_node));
+        std::vector<std::pair<int, int>> finals;   // (scratch buffer, output index)
+        for (size_t oi = 0; oi < ks.outputs.size(); ++oi) {
+            const KOutput& o = ks.outputs[oi];
+            if (o.kind == KOutput::FULL || o.kind == KOutput::ROW) stp.k.args.push_back(buffer_for(o.node));
+            else {
+                int64_t per = o.kind == KOutput::COLSUM ? gk.cols : 1;
+                int tmp = temp_buffer(per * 4 * gk.step.grid);
+                stp.k.args.push_back(tmp);
+                finals.push_back({tmp, (int)oi});
+            }
+        }
+        plan.steps.push_back(stp);
+        for (auto& f : finals) {
+            const KOutput& o = ks.outputs[f.second];
+            int64_t per = o.kind == KOutput::COLSUM ? gk.cols : 1;
+            GeneratedKernel fk = generate_finalize(gk.step.grid, per, "ormi_finalize_" + std::to_string(kernel_serial++));
+            Step fs; fs.type = Step::Kernel; fs.k = fk.step;
+            fs.k.args = {f.first, buffer_for(o.node)};
+            plan.steps.push_back(fs);
+        }
+    }
+
+    // ---- results: every materialized node, plus roots / KEEP nodes that are views (aliases)
+    for (int i = 0; i < n; ++i) {
+        if (!info[i].needed || info[i].kind == K_INPUT) continue;
+        if (info[i].in_M) plan.results.push_back(NodeResult{i, buffer_for(i), false});
+    }
+    auto alias_result = [&](int i) {
+        if (info[i].kind != K_VIEW) return;
+        for (auto& r : plan.results) if (r.node == i) return;
+        plan.results.push_back(NodeResult{i, buffer_for(info[i].base), true});
+    };
+    for (int r = 0; r < n_roots; ++r) alias_result(roots[r]);
+    for (int i = 0; i < n; ++i) if (info[i].needed && (nodes[i].flags & ORMI_NODE_KEEP)) alias_result(i);
+    return plan;
+}
+
+std::string json_escape(const std::string& s) {
+    std::string o;
+    for (char c : s) {
+        switch (c) {
+            case '"': o += "\\\""; break;
+            case '\\': o += "\\\\"; break;
+            case '\n': o += "\\n"; break;
+            case '\t': o += "\\t"; break;
+            case '\r': break;
+            default: o += c;
+        }
+    }
+    return o;
+}
+
+}  // namespace
+
+Plan build_plan(const ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots, const SchedOptions& opt) {
+    Scheduler s(nodes, n_nodes, opt);
+    return s.run(roots, n_roots);
+}
+
+std::string plan_to_json(const Plan& plan) {
+    std::ostringstream o;
+    o << "{\"error\": \"" << json_escape(plan.error) << "\", \"buffers\": [";
+    for (size_t i = 0; i < plan.buffers.size(); ++i) {
+        const auto& b = plan.buffers[i];
+        o << (i ? ", " : "") << "{\"kind\": \"" << (b.kind == BufKind::External ? "external" : b.kind == BufKind::NodeOut ? "node" : "temp")
+          << "\", \"node\": " << b.node << ", \"bytes\": " << b.bytes << "}";
+    }
+    o << "], \"steps\": [";
+    for (size_t i = 0; i < plan.steps.size(); ++i) {
+        const auto& s = plan.steps[i];
+        o << (i ? ", " : "");
+        if (s.type == Step::Kernel) {
+            o << "{\"type\": \"kernel\", \"name\": \"" << s.k.name << "\", \"grid\": " << s.k.grid << ", \"block\": " << s.k.block
+              << ", \"what\": \"" << json_escape(s.k.what) << "\", \"bytes_read\": " << s.k.bytes_read << ", \"bytes_written\": " << s.k.bytes_written
+              << ", \"args\": [";
+            for (size_t a = 0; a < s.k.args.size(); ++a) o << (a ? ", " : "") << s.k.args[a];
+            o << "], \"source\": \"" << json_escape(s.k.source) << "\"}";
+        } else {
+            const auto& g = s.g;
+            o << "{\"type\": \"gemm\", \"node\": " << g.node << ", \"a\": " << g.a << ", \"b\": " << g.b << ", \"c\": " << g.c
+              << ", \"M\": " << g.M << ", \"N\": " << g.N << ", \"K\": " << g.K << ", \"trans_a\": " << g.trans_a << ", \"trans_b\": " << g.trans_b
+              << ", \"lda\": " << g.lda << ", \"ldb\": " << g.ldb << ", \"batch\": " << g.batch << ", \"bshape\": [";
+            for (int d = 0; d < g.nbatch; ++d) o << (d ? ", " : "") << g.bshape[d];
+            o << "], \"astride\": [";
+            for (int d = 0; d < g.nbatch; ++d) o << (d ? ", " : "") << g.astride[d];
+            o << "], \"bstride\": [";
+            for (int d = 0; d < g.nbatch; ++d) o << (d ? ", " : "") << g.bstride[d];
+            o << "]}";
+        }
+    }
+    o << "], \"results\": [";
+    for (size_t i = 0; i < plan.results.size(); ++i) {
+        const auto& r = plan.results[i];
+        o << (i ? ", " : "") << "{\"node\": " << r.node << ", \"buffer\": " << r.buffer << ", \"alias\": " << (r.alias ? "true" : "false") << "}";
+    }
+    o << "]}";
+    return o.str();
+}
+
+uint64_t fnv1a(const std::string& s) {
+    uint64_t h = 1469598103934665603ull;
+    for (unsigned char c : s) { h ^= c; h *= 1099511628211ull; }
+    return h;
+}
+
+}  // namespace ormi_b200

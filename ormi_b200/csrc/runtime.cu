@@ -1,0 +1,212 @@
+// Context, buffer pool, kernel cache and plan executor of the B200 backend.
+//
+// Replaces, from the reference CUDA backend:
+//   CUDAAllocator            ormi-core/csrc/backend/cuda/allocator.cu:11-105   (pool, copies, fills)
+//   compile_ptx              ormi-core/csrc/backend/cuda/utils.cu:6-27         (NVRTC; here straight to an sm_100a cubin)
+//   execute_jit              ormi-core/csrc/backend/cuda/jit.cu:13-44          (module load + launch; here cached and on a stream)
+// Differences by design: the device is bound once, every launch and copy goes to one non-blocking stream
+// (the reference uses the legacy default stream and re-initialises the driver on every call), compiled
+// kernels are cached by source hash and whole schedules by graph structure, so a training loop that
+// rebuilds the same graph every step pays for scheduling, code generation and NVRTC once.
+#include <nvrtc.h>
+
+#include <cstring>
+
+#include "context.h"
+
+namespace ormi_b200 {
+
+// ------------------------------------------------------------------------------------------------ driver
+void DriverApi::load() {
+    auto get = [](const char* name, void** fn) {
+        cudaDriverEntryPointQueryResult st;
+        cudaError_t e = cudaGetDriverEntryPoint(name, fn, cudaEnableDefault, &st);
+        if (e != cudaSuccess || st != cudaDriverEntryPointSuccess || !*fn)
+            throw Error(std::string("CUDA Error: driver entry point not found: ") + name);
+    };
+    get("cuModuleLoadData", (void**)&ModuleLoadData);
+    get("cuModuleUnload", (void**)&ModuleUnload);
+    get("cuModuleGetFunction", (void**)&ModuleGetFunction);
+    get("cuLaunchKernel", (void**)&LaunchKernel);
+    get("cuGetErrorString", (void**)&GetErrorString);
+    get("cuFuncSetAttribute", (void**)&FuncSetAttribute);
+    get("cuTensorMapEncodeTiled", (void**)&TensorMapEncodeTiled);
+}
+
+void DriverApi::check(CUresult r, const char* what) const {
+    if (r == CUDA_SUCCESS) return;
+    const char* msg = nullptr;
+    if (GetErrorString) GetErrorString(r, &msg);
+    throw Error(std::string("CUDA Error: ") + (msg ? msg : "unknown") + " (" + what + ")");
+}
+
+// ------------------------------------------------------------------------------------------------ pool
+void* pool_alloc(ormi_b200_ctx* ctx, size_t bytes) {
+    if (bytes == 0) bytes = 4;
+    {
+        std::lock_guard<std::mutex> lock(ctx->pool_mutex);
+        auto it = ctx->free_blocks.find(bytes);
+        if (it != ctx->free_blocks.end() && !it->second.empty()) {
+            void* p = it->second.back();
+            it->second.pop_back();
+            ctx->counters["pool_hits"]++;
+            return p;
+        }
+    }
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaErrorMemoryAllocation) {   // give cached blocks back and try once more
+        cudaGetLastError();
+        {
+            std::lock_guard<std::mutex> lock(ctx->pool_mutex);
+            cudaStreamSynchronize(ctx->stream);
+            for (auto& kv : ctx->free_blocks) for (void* q : kv.second) cudaFree(q);
+            ctx->free_blocks.clear();
+        }
+        e = cudaMalloc(&p, bytes);
+    }
+    if (e != cudaSuccess) throw Error(std::string("CUDA Error: ") + cudaGetErrorString(e) + " (allocating " + std::to_string(bytes) + " bytes)");
+    ctx->counters["bytes_allocated"] += (int64_t)bytes;
+    return p;
+}
+
+void pool_free(ormi_b200_ctx* ctx, void* ptr, size_t bytes) {
+    if (!ptr) return;
+    if (bytes == 0) bytes = 4;
+    std::lock_guard<std::mutex> lock(ctx->pool_mutex);
+    ctx->free_blocks[bytes].push_back(ptr);
+}
+
+// ------------------------------------------------------------------------------------------------ NVRTC
+std::vector<char> compile_cubin(const std::string& source, std::string* log_out) {
+    nvrtcProgram prog;
+    if (nvrtcCreateProgram(&prog, source.c_str(), "ormi_fused.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS)
+        throw Error("NVRTC Error: cannot create program");
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17", "-default-device"};
+    nvrtcResult r = nvrtcCompileProgram(prog, 4, opts);
+    size_t log_size = 0;
+    nvrtcGetProgramLogSize(prog, &log_size);
+    std::string log(log_size, '\0');
+    if (log_size > 1) nvrtcGetProgramLog(prog, &log[0]);
+    if (log_out) *log_out = log;
+    if (r != NVRTC_SUCCESS) {
+        nvrtcDestroyProgram(&prog);
+        throw Error("NVRTC Compilation failed: \n" + log);
+    }
+    size_t size = 0;
+    if (nvrtcGetCUBINSize(prog, &size) != NVRTC_SUCCESS || size == 0) { nvrtcDestroyProgram(&prog); throw Error("NVRTC Error: no cubin produced"); }
+    std::vector<char> cubin(size);
+    nvrtcGetCUBIN(prog, cubin.data());
+    nvrtcDestroyProgram(&prog);
+    return cubin;
+}
+
+CompiledKernel* get_kernel(ormi_b200_ctx* ctx, const KernelStep& k) {
+    auto it = ctx->kernel_cache.find(k.key + ":" + k.name);
+    if (it != ctx->kernel_cache.end()) { ctx->counters["kernel_cache_hits"]++; return &it->second; }
+    std::vector<char> cubin = compile_cubin(k.source);
+    CompiledKernel ck;
+    ctx->drv.check(ctx->drv.ModuleLoadData(&ck.module, cubin.data()), "cuModuleLoadData");
+    ctx->drv.check(ctx->drv.ModuleGetFunction(&ck.func, ck.module, k.name.c_str()), "cuModuleGetFunction");
+    ctx->counters["kernels_compiled"]++;
+    auto res = ctx->kernel_cache.emplace(k.key + ":" + k.name, ck);
+    return &res.first->second;
+}
+
+void launch_kernel(ormi_b200_ctx* ctx, CompiledKernel* k, int grid, int block, std::vector<void*>& pointer_args) {
+    std::vector<void*> argv(pointer_args.size());
+    for (size_t i = 0; i < pointer_args.size(); ++i) argv[i] = &pointer_args[i];
+    ctx->drv.check(ctx->drv.LaunchKernel(k->func, (unsigned)grid, 1, 1, (unsigned)block, 1, 1, 0, (CUstream)ctx->stream, argv.data(), nullptr),
+                   "cuLaunchKernel");
+    ctx->counters["launches"]++;
+}
+
+// ------------------------------------------------------------------------------------------------ realize
+static uint64_t graph_hash(const ormi_b200_ctx* ctx, const ormi_b200_node* nodes, int n, const int* roots, int n_roots) {
+    uint64_t h = 1469598103934665603ull;
+    auto mix = [&](uint64_t v) { h ^= v; h *= 1099511628211ull; };
+    mix((uint64_t)n); mix(ctx->fusion ? 1 : 0);
+    for (int i = 0; i < n; ++i) {
+        const auto& nd = nodes[i];
+        mix((uint64_t)nd.op); mix((uint64_t)nd.n_parents);
+        for (int p = 0; p < nd.n_parents; ++p) mix((uint64_t)nd.parents[p]);
+        mix((uint64_t)nd.ndim);
+        for (int d = 0; d < nd.ndim; ++d) { mix((uint64_t)(uint32_t)nd.shape[d]); mix((uint64_t)(uint32_t)nd.strides[d]); }
+        mix((uint64_t)nd.n_axes);
+        for (int a = 0; a < nd.n_axes; ++a) mix((uint64_t)nd.axes[a]);
+        mix((uint64_t)nd.keepdims); mix((uint64_t)(nd.flags & ORMI_NODE_KEEP));
+        mix(nd.data ? (nd.data_bytes == 4 ? 2 : 1) : 0);
+    }
+    for (int r = 0; r < n_roots; ++r) mix((uint64_t)roots[r]);
+    return h;
+}
+
+void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots,
+             const std::vector<std::pair<int, void*>>* preassigned) {
+    ORMI_CUDA(cudaSetDevice(ctx->device));
+    uint64_t key = graph_hash(ctx, nodes, n_nodes, roots, n_roots);
+    CachedPlan* cp = nullptr;
+    auto it = ctx->plan_cache.find(key);
+    if (it != ctx->plan_cache.end()) { cp = it->second.get(); ctx->counters["plan_cache_hits"]++; }
+    else {
+        SchedOptions opt;
+        opt.num_sms = ctx->num_sms;
+        opt.fusion = ctx->fusion;
+        auto fresh = std::make_unique<CachedPlan>();
+        fresh->plan = build_plan(nodes, n_nodes, roots, n_roots, opt);
+        if (!fresh->plan.error.empty()) throw Error(fresh->plan.error);
+        for (const Step& s : fresh->plan.steps) fresh->kernels.push_back(s.type == Step::Kernel ? get_kernel(ctx, s.k) : nullptr);
+        cp = fresh.get();
+        ctx->plan_cache[key] = std::move(fresh);
+    }
+    const Plan& plan = cp->plan;
+    std::vector<void*> bufs(plan.buffers.size(), nullptr);
+    std::vector<bool> handed(plan.buffers.size(), false);
+    try {
+        for (size_t b = 0; b < plan.buffers.size(); ++b) {
+            const PlanBuffer& pb = plan.buffers[b];
+            if (pb.kind == BufKind::External) {
+                bufs[b] = nodes[pb.node].data;
+                if (!bufs[b]) throw Error("internal: realized input without a buffer");
+            } else {
+                if (preassigned && pb.kind == BufKind::NodeOut)
+                    for (auto& pr : *preassigned) if (pr.first == pb.node) { bufs[b] = pr.second; handed[b] = true; }
+                if (!bufs[b]) bufs[b] = pool_alloc(ctx, (size_t)pb.bytes);
+            }
+        }
+        for (size_t s = 0; s < plan.steps.size(); ++s) {
+            const Step& st = plan.steps[s];
+            if (st.type == Step::Kernel) {
+                std::vector<void*> args;
+                for (int a : st.k.args) args.push_back(bufs[a]);
+                launch_kernel(ctx, cp->kernels[s], st.k.grid, st.k.block, args);
+            } else {
+                GemmArgs g;
+                g.A = (const float*)bufs[st.g.a]; g.B = (const float*)bufs[st.g.b]; g.C = (float*)bufs[st.g.c];
+                g.M = st.g.M; g.N = st.g.N; g.K = st.g.K;
+                g.trans_a = st.g.trans_a; g.trans_b = st.g.trans_b; g.lda = st.g.lda; g.ldb = st.g.ldb;
+                g.batch = st.g.batch; g.nbatch = st.g.nbatch;
+                std::memcpy(g.bshape, st.g.bshape, sizeof g.bshape);
+                std::memcpy(g.astride, st.g.astride, sizeof g.astride);
+                std::memcpy(g.bstride, st.g.bstride, sizeof g.bstride);
+                gemm_dispatch(ctx, g);
+            }
+        }
+    } catch (...) {
+        for (size_t b = 0; b < plan.buffers.size(); ++b)
+            if (plan.buffers[b].kind != BufKind::External && bufs[b] && !handed[b]) pool_free(ctx, bufs[b], (size_t)plan.buffers[b].bytes);
+        throw;
+    }
+    for (const NodeResult& r : plan.results) {
+        ormi_b200_node& nd = nodes[r.node];
+        nd.data = bufs[r.buffer];
+        nd.data_bytes = plan.buffers[r.buffer].bytes;
+        if (r.alias) nd.flags |= ORMI_NODE_ALIAS;
+        else if (handed[r.buffer]) nd.flags |= ORMI_NODE_ALIAS;   // caller-owned target
+        else { nd.flags |= ORMI_NODE_OWNED; handed[r.buffer] = true; }
+    }
+    for (size_t b = 0; b < plan.buffers.size(); ++b)
+        if (plan.buffers[b].kind != BufKind::External && !handed[b]) pool_free(ctx, bufs[b], (size_t)plan.buffers[b].bytes);
+}
+
+}  // namespace ormi_b200

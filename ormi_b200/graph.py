@@ -287,7 +287,8 @@ def _reshape_strides(old_shape, old_strides, out_shape) -> list[int]:
 
 def leaf(array, requires_grad=False) -> Node:
     """A leaf over host data (uploaded by the runtime on first use)."""
-    arr = np.ascontiguousarray(np.asarray(array, dtype=np.float32))
+    arr = np.asarray(array, dtype=np.float32)
+    arr = np.ascontiguousarray(arr).reshape(arr.shape)   # ascontiguousarray would turn rank 0 into rank 1
     return Node(OpEnum.LEAF, data=Buffer(arr.shape, host=arr), requires_grad=requires_grad)
 
 

@@ -1,0 +1,96 @@
+"""TEST INFRASTRUCTURE: executes a schedule (ormi_b200.runtime.plan) on the CPU.
+
+Every generated kernel is compiled unchanged with g++ against tests/cuda_emul.h and launched with its
+real grid/block geometry; GEMM steps are computed with numpy.  This checks the scheduler and the code
+generator against the oracle without a GPU.  It is not a fallback: nothing in the package imports it.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import subprocess
+import tempfile
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_CACHE = os.path.join(tempfile.gettempdir(), "ormi_b200_emul")
+
+
+def _compile(sources: list[tuple[str, str]]):
+    os.makedirs(_CACHE, exist_ok=True)
+    text = '#include "cuda_emul.h"\n' + "\n".join(src for _, src in sources)
+    tag = hashlib.sha1(text.encode()).hexdigest()[:16]
+    so = os.path.join(_CACHE, f"k_{tag}.so")
+    if not os.path.exists(so):
+        cpp = os.path.join(_CACHE, f"k_{tag}.cpp")
+        with open(cpp, "w") as f:
+            f.write(text)
+        cmd = ["g++", "-O1", "-std=c++17", "-fPIC", "-shared", "-ffp-contract=off", "-pthread", "-I", _HERE, cpp, "-o", so]
+        out = subprocess.run(cmd, capture_output=True, text=True)
+        if out.returncode != 0:
+            raise RuntimeError("emulator compile failed:\n" + out.stderr[:4000])
+    return ctypes.CDLL(so)
+
+
+def run_plan(plan: dict) -> dict:
+    """Runs the plan; returns {node index: np.ndarray (raw contiguous buffer)} for plan["results"]."""
+    if plan["error"]:
+        raise RuntimeError(plan["error"])
+    order = plan["order"]
+    bufs = []
+    for b in plan["buffers"]:
+        if b["kind"] == "external":
+            host = order[b["node"]].data.host
+            bufs.append(np.ascontiguousarray(host, dtype=np.float32).reshape(-1))
+        else:
+            bufs.append(np.full(max(1, b["bytes"] // 4), np.nan, dtype=np.float32))
+    kernels = [(s["name"], s["source"]) for s in plan["steps"] if s["type"] == "kernel"]
+    lib = _compile(kernels) if kernels else None
+    for s in plan["steps"]:
+        if s["type"] == "kernel":
+            fn = ctypes.cast(getattr(lib, s["name"]), ctypes.c_void_p)
+            args = (ctypes.c_void_p * len(s["args"]))(*[bufs[a].ctypes.data for a in s["args"]])
+            rc = lib.emul_launch(fn, s["grid"], s["block"], args, len(s["args"]))
+            assert rc == 0
+        else:
+            _gemm(s, bufs)
+    return {r["node"]: bufs[r["buffer"]] for r in plan["results"]}
+
+
+def _gemm(s, bufs):
+    M, N, K = s["M"], s["N"], s["K"]
+    a, b, c = bufs[s["a"]], bufs[s["b"]], bufs[s["c"]]
+    bshape = s["bshape"]
+    for bi in range(s["batch"]):
+        rem, oa, ob = bi, 0, 0
+        for d in range(len(bshape) - 1, -1, -1):
+            coord = rem % bshape[d]
+            rem //= bshape[d]
+            oa += coord * s["astride"][d]
+            ob += coord * s["bstride"][d]
+        sa = (1, s["lda"]) if s["trans_a"] else (s["lda"], 1)
+        sb = (1, s["ldb"]) if s["trans_b"] else (s["ldb"], 1)
+        A = np.lib.stride_tricks.as_strided(a[oa:], shape=(M, K), strides=(4 * sa[0], 4 * sa[1]))
+        B = np.lib.stride_tricks.as_strided(b[ob:], shape=(K, N), strides=(4 * sb[0], 4 * sb[1]))
+        c[bi * M * N:(bi + 1) * M * N] = (A.astype(np.float32) @ B.astype(np.float32)).reshape(-1)
+
+
+def realize(roots):
+    """Plan + run; returns the logical value (view strides applied) of each root."""
+    from ormi_b200 import runtime as RT
+    plan = RT.plan(list(roots), host_pointers=True)
+    res = run_plan(plan)
+    order = plan["order"]
+    outs = []
+    for r, root in zip(plan["roots"], roots):
+        if root.is_realized:
+            raw = np.ascontiguousarray(root.data.host).reshape(-1)
+        else:
+            raw = res[r]
+        if not root.shape:
+            outs.append(raw[:1].reshape(()).copy())
+        else:
+            outs.append(np.lib.stride_tricks.as_strided(raw, shape=root.shape, strides=[4 * st for st in root.strides]).copy())
+    return outs, plan
