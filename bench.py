@@ -1,0 +1,338 @@
+#!/usr/bin/env python
+"""Benchmark of the realize path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (configs[1] of the baseline description): row softmax and layernorm, forward plus the
+autograd-generated backward, on x[16384, 4096] fp32 per GPU.  One step realizes both graphs once.
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank owns its own 16384-row
+shard (weak scaling); the only exchange is the all-reduce of the two [4096] parameter gradients.
+
+Prints ONE JSON line (rank 0): the metric is algorithmic HBM traffic per second.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+R, C = 16384, 4096
+METRIC, UNIT = "fused_graph_hbm_gbps", "GB/s"
+WORKLOAD = "configs[1]: row softmax + layernorm, forward + autograd backward, x[16384,4096] fp32 per GPU"
+# algorithmic bytes of one step (per GPU): softmax reads x, gy and writes y, dx; layernorm reads x, gy, g, b and
+# writes y, dx, dg, db.  Nothing is saved between forward and backward: both run in one kernel per graph.
+BYTES_SOFTMAX = 4 * R * C * 4
+BYTES_LAYERNORM = 4 * R * C * 4 + 4 * C * 4
+BYTES_STEP = BYTES_SOFTMAX + BYTES_LAYERNORM
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def build_graphs(G, W, leaf, rows=R, shard=0):
+    """The two graphs of a step over `rows` rows; returns (roots, inputs) with inputs = dict of leaf nodes.
+    x ~ N(0, 2) (variance 2), gy ~ N(0, 1), g ~ U(0.5, 1.5), b ~ N(0, 0.1); shard s draws x, gy from seeds 100 s + {0, 1}."""
+    x = leaf(W.normal(100 * shard, (rows, C), math.sqrt(2.0)), True)
+    gy = leaf(W.normal(100 * shard + 1, (rows, C)))
+    g = leaf(W.uniform(2, (C,), 0.5, 1.5), True)
+    b = leaf(W.normal(3, (C,), 0.1), True)
+    y = W.softmax(x)
+    y.grad = gy
+    G.compute_gradients(y)
+    sm_roots = [y, x.grad]
+    x.grad = None
+    y2 = W.layernorm(x, g, b)
+    y2.grad = gy
+    G.compute_gradients(y2)
+    ln_roots = [y2, x.grad, g.grad, b.grad]
+    return sm_roots, ln_roots, dict(x=x, gy=gy, g=g, b=b)
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx = float(parts[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+class StepRunner:
+    """Realizes the two cached graphs through the C ABI, the way a host loop over the graph API does: the flattened
+    graph is handed to ormi_b200_realize every step, results are dropped (returned to the pool) afterwards."""
+
+    def __init__(self, dev, G, roots_list):
+        from ormi_b200._lib import lib, check
+        self.dev, self.lib, self.check, self.G = dev, lib, check, G
+        self.graphs = []
+        for roots in roots_list:
+            order = G.topo_order(roots, stop_at_realized=True)
+            dev.ensure_on_device(order)
+            arr, order, ridx = G.flatten(roots, host_pointers=False, stop_at_realized=True)
+            template = bytes(arr)
+            self.graphs.append((arr, template, len(order), (ctypes.c_int * len(ridx))(*ridx), ridx, order))
+
+    def run(self, which=None, keep=False):
+        outs = []
+        for gi, (arr, template, n, ridx, ridx_list, order) in enumerate(self.graphs):
+            if which is not None and gi != which:
+                continue
+            ctypes.memmove(arr, template, len(template))
+            self.check(self.lib.ormi_b200_realize(self.dev.handle, arr, n, ridx, len(ridx_list)))
+            kept = {}
+            for i in range(n):
+                c = arr[i]
+                if c.flags & self.G.NODE_OWNED:
+                    if keep and i in ridx_list:
+                        kept[i] = (c.data, c.data_bytes)
+                    else:
+                        self.dev.free(c.data, c.data_bytes)
+            outs.extend(kept[i] for i in ridx_list if i in kept)      # in the order of the roots
+        return outs
+
+
+def timed(dev, torch, fn, steps, dist=None):
+    stream = torch.cuda.ExternalStream(dev.stream)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    e1.synchronize()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def cpu_reference(rows, repeats=1):
+    """The reference CPU backend (unmodified, oracle/_ref) — or its C restatement when that library is absent — on
+    `rows` rows of the same workload.  Returns (GB/s of algorithmic bytes, seconds per run, kind, cores)."""
+    from ormi_b200 import graph as G, workloads as W
+    from oracle import oracle as O
+    x = G.leaf(W.normal(0, (rows, C), math.sqrt(2.0)), True)
+    gy = G.leaf(W.normal(1, (rows, C)))
+    g = G.leaf(W.uniform(2, (C,), 0.5, 1.5), True)
+    b = G.leaf(W.normal(3, (C,), 0.1), True)
+    best = None
+    kind = "reference" if O.ref_available() else "port"
+    for _ in range(repeats):
+        if kind == "reference":
+            y = W.softmax(x)
+            _, s1 = O.ref_run([(y, "value"), (x, "grad")], seeds=[(y, gy)], backward_root=y, caps=[rows * C] * 2)
+            y2 = W.layernorm(x, g, b)
+            _, s2 = O.ref_run([(y2, "value"), (x, "grad"), (g, "grad"), (b, "grad")], seeds=[(y2, gy)], backward_root=y2,
+                              caps=[rows * C] * 4)
+        else:
+            sm, ln, _ = build_graphs(G, W, G.leaf, rows)
+            _, s1 = O.port_run(sm)
+            _, s2 = O.port_run(ln)
+        secs = s1 + s2
+        best = secs if best is None else min(best, secs)
+    nbytes = BYTES_STEP * rows / R
+    return nbytes / best / 1e9, best, kind, 1
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    rows = 256
+    for _ in range(args.warmup):
+        cpu_reference(rows)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        gbps, secs, kind, cores = cpu_reference(rows)
+    ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    value = (BYTES_STEP * rows / R) / (ms * 1e-3) / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "rows_per_gpu": R, "cols": C},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": f"{rows} of {R} rows per step (same graphs, same seeds), autograd + realize on the reference CPU backend"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    warmup = max(3, args.warmup)
+
+    import torch
+    from ormi_b200 import graph as G, workloads as W
+    from ormi_b200.runtime import Device
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+    dev = Device(local_rank)
+
+    # inputs resident in HBM; each rank draws its own shard (seed offset by rank)
+    sm_roots, ln_roots, inputs = build_graphs(G, W, lambda a, rg=False: dev.leaf(a, rg), shard=rank)
+    runner = StepRunner(dev, G, [sm_roots, ln_roots])
+
+    grads = None
+    if dist is not None:
+        grads = torch.zeros(2 * C, device="cuda")
+
+    def step():
+        outs = runner.run(keep=dist is not None)
+        if dist is not None:
+            # cross-shard combine: dg, db (the last two roots of the layernorm graph) are summed over ranks
+            dg, db = outs[-2], outs[-1]
+            from ormi_b200._lib import lib, check
+            check(lib.ormi_b200_memcpy_d2d(dev.handle, ctypes.c_void_p(grads.data_ptr()), ctypes.c_void_p(dg[0]), C * 4))
+            check(lib.ormi_b200_memcpy_d2d(dev.handle, ctypes.c_void_p(grads.data_ptr() + C * 4), ctypes.c_void_p(db[0]), C * 4))
+            dev.sync()
+            dist.all_reduce(grads)
+            for ptr, nbytes in outs:
+                dev.free(ptr, nbytes)
+
+    for _ in range(warmup):
+        step()
+    dev.sync()
+    launches0 = dev.counter("launches")
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_total = timed(dev, torch, step, args.steps, dist)
+    launches = dev.counter("launches") - launches0
+    # dominant kernel alone (the fused layernorm forward+backward kernel and its two finalize launches)
+    ms_ln = timed(dev, torch, lambda: runner.run(which=1), args.steps, dist)
+    ms_sm = timed(dev, torch, lambda: runner.run(which=0), args.steps, dist)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # end to end: host buffers in, host buffers out, through the public Device API
+    pinned = {k: torch.from_numpy(np.ascontiguousarray(v.data.host if v.data.host is not None else dev.download(v.data))).pin_memory()
+              for k, v in inputs.items()}
+    out_host = [torch.empty(R * C, dtype=torch.float32).pin_memory() for _ in range(4)] + [torch.empty(C, dtype=torch.float32).pin_memory() for _ in range(2)]
+    h2d = sum(t.numel() * 4 for t in pinned.values())
+    d2h = sum(t.numel() * 4 for t in out_host)
+
+    def e2e_step():
+        for k, node in inputs.items():
+            dev.h2d(node.data.dev_ptr, pinned[k].numpy())
+        outs = runner.run(keep=True)
+        for (ptr, nbytes), host in zip(outs, out_host):
+            dev.d2h(host.numpy(), ptr)
+            dev.free(ptr, nbytes)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    dev.sync()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+
+    if rank == 0:
+        peak, peak_src = peaks()
+        ms_step = ms_total / args.steps
+        value = world * BYTES_STEP / (ms_step * 1e-3) / 1e9
+        ln_gbps = BYTES_LAYERNORM / (ms_ln / args.steps * 1e-3) / 1e9
+        sm_gbps = BYTES_SOFTMAX / (ms_sm / args.steps * 1e-3) / 1e9
+        cpu_gbps, cpu_secs, kind, cores = cpu_reference(2048)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "rows_per_gpu": R, "cols": C,
+                       "l2": "inputs larger than L2: every kernel reads 537 MB and writes 537 MB",
+                       "exchange": "all-reduce of dg, db (2 x 4096 fp32) per step" if world > 1 else "none"},
+            "clocks": clocks,
+            "e2e": {"value": world * BYTES_STEP / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "kernel": "fused layernorm forward+backward (rows template) + 2 finalize launches",
+                         "achieved": ln_gbps, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": ln_gbps / peak,
+                         "traffic": None, "softmax_kernel_gbps": sm_gbps},
+            "cpu_baseline": {"value": cpu_gbps, "unit": UNIT, "cores": cores, "kind": kind,
+                             "sample": f"2048 of {R} rows, one run ({cpu_secs:.1f} s), autograd + realize on the reference CPU backend"},
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+    dev.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,219 @@
+"""Scheduler + code generator, checked on the CPU: every generated CUDA C kernel is compiled unchanged
+against tests/cuda_emul.h, launched with its real geometry by tests/emulator.py, and compared with the
+oracle.  No GPU needed; the same cases run on the B200 in tests/test_gpu_parity.py."""
+import math
+
+import numpy as np
+import pytest
+
+import emulator as E
+import make_golden
+from ormi_b200 import graph as G
+from ormi_b200 import runtime as RT
+from ormi_b200 import workloads as W
+from oracle import oracle as O
+
+POINTWISE_TOL = 1e-6     # |gpu - cpu| <= tol * max|cpu|  (fp32 pointwise)
+REDUCE_TOL = 1e-5        # fp32 reductions and FFMA matmul
+
+
+def compare(roots, tol):
+    outs, plan = E.realize(roots)
+    ref, _ = O.port_run(roots)
+    for a, b in zip(outs, ref):
+        assert a.shape == b.shape
+        assert np.abs(a - b).max() <= tol * max(1e-30, np.abs(b).max()), np.abs(a - b).max() / np.abs(b).max()
+    return plan
+
+
+def kinds(plan):
+    return [s["what"].split("[")[0] if s["type"] == "kernel" else "gemm" for s in plan["steps"]]
+
+
+@pytest.mark.parametrize("name", list(make_golden.CASES))
+def test_golden_cases_through_generated_kernels(name):
+    roots, _ = make_golden.CASES[name]()
+    compare(roots, REDUCE_TOL)
+
+
+def test_fused_rowsum_is_one_kernel():
+    a, b, c = (G.leaf(W.normal(i, (8, 4096))) for i in range(3))
+    plan = compare([W.fused_rowsum(a, b, c)], REDUCE_TOL)
+    assert kinds(plan) == ["rows"]
+    step = plan["steps"][0]
+    assert step["bytes_read"] == 3 * 8 * 4096 * 4 + 3 * 4      # a, b, c once each, plus the three rank-0 constants
+    assert "T=256" in step["what"] and "V=4" in step["what"]
+
+
+def test_softmax_forward_backward_is_one_kernel():
+    x = G.leaf(W.normal(0, (24, 96), math.sqrt(2.0)), True)
+    gy = G.leaf(W.normal(1, (24, 96)))
+    y = W.softmax(x)
+    y.grad = gy
+    G.compute_gradients(y)
+    plan = compare([y, x.grad], REDUCE_TOL)
+    assert kinds(plan) == ["rows"]
+
+
+@pytest.mark.parametrize("shape", [(12, 256), (7, 100), (5, 37), (3, 1024), (2, 4096)])
+def test_layernorm_forward_backward(shape):
+    R, C = shape
+    x = G.leaf(W.normal(0, (R, C), math.sqrt(2.0)), True)
+    g, b = G.leaf(W.uniform(2, (C,), 0.5, 1.5), True), G.leaf(W.normal(3, (C,), 0.1), True)
+    gy = G.leaf(W.normal(1, (R, C)))
+    y = W.layernorm(x, g, b)
+    y.grad = gy
+    G.compute_gradients(y)
+    plan = compare([y, x.grad, g.grad, b.grad], 2 * REDUCE_TOL)
+    assert kinds(plan) == ["rows", "finalize", "finalize"]       # y, dx, dg, db from one pass over x and gy
+
+
+def test_mlp_step_schedule():
+    B, D, H = 32, 16, 64
+    x, t = G.leaf(W.normal(0, (B, D))), G.leaf(W.normal(1, (B, D)))
+    w1, b1 = G.leaf(W.kaiming_uniform(2, D, (D, H)), True), G.leaf(np.zeros(H, np.float32), True)
+    w2, b2 = G.leaf(W.kaiming_uniform(3, H, (H, D)), True), G.leaf(np.zeros(D, np.float32), True)
+    loss = W.mlp_loss(x, w1, b1, w2, b2, t)
+    G.compute_gradients(loss)
+    ups = [W.sgd_update(p, 0.1) for p in (w1, b1, w2, b2)]
+    plan = compare([loss] + ups, 2 * REDUCE_TOL)
+    k = kinds(plan)
+    assert k.count("gemm") == 5
+    assert len(k) <= 17, k    # 5 GEMMs + gelu, loss/grad/bias-grad, hidden grad, loss scale, 4 updates, 3 finalizes
+
+
+def test_fusion_off_is_one_kernel_per_node():
+    a, b = G.leaf(W.normal(0, (4, 8))), G.leaf(W.normal(1, (4, 8)))
+    root = G.mul(G.add(a, b), G.exp(a))
+    arr, order, roots = G.flatten([root], host_pointers=True)
+    assert len(RT.plan([root])["steps"]) == 1
+
+
+# ---------------------------------------------------------------------------- edge cases
+def test_reference_known_answers_through_generated_kernels():
+    full = lambda s, v: G.leaf(np.full(s, v, dtype=np.float32))
+    cases = [
+        (G.add(full([4], 2.0), full([4], 3.0)), 5.0),
+        (G.mul(G.add(full([2, 2], 2.0), full([2, 2], 3.0)), full([2, 2], 4.0)), 20.0),
+        (G.add(full([2, 3], 2.0), full([3], 5.0)), 7.0),
+        (G.add(full([2, 2], 10.0), full([], 3.0)), 13.0),
+        (G.matmul(full([2, 3], 2.0), full([3, 2], 3.0)), 18.0),
+        (G.matmul(full([2, 1, 2, 3], 1.5), full([1, 2, 3, 2], 2.0)), 9.0),
+        (G.sum_(full([2, 3], 2.0), [], True), 12.0),
+        (G.sum_(full([2, 3, 2], 1.0), [0, 2], False), 4.0),
+    ]
+    outs, _ = E.realize([c for c, _ in cases])
+    for o, (_, want) in zip(outs, cases):
+        assert np.all(o == want)
+
+
+def test_sums_every_kind():
+    a = G.leaf(W.normal(0, (6, 5, 8)))
+    roots = [G.sum_(a, [], False), G.sum_(a, [], True), G.sum_(a, [2], False), G.sum_(a, [1, 2], True),
+             G.sum_(a, [0], False), G.sum_(a, [0, 1], False), G.sum_(a, [1], False), G.sum_(a, [0, 2], True)]
+    compare(roots, REDUCE_TOL)
+    e = G.exp(a)                                # the same, fused behind a producer
+    roots = [G.sum_(e, [], False), G.sum_(e, [2], True), G.sum_(e, [0, 1], False), G.sum_(e, [1], False)]
+    compare(roots, REDUCE_TOL)
+
+
+def test_size_one_axes_and_rank0():
+    a = G.leaf(W.normal(0, (1, 7, 1)))
+    s = G.leaf(np.float32(3.0))
+    roots = [G.sum_(a, [0], False), G.sum_(a, [0, 2], True), G.sum_(a, [1], False), G.mul(G.sum_(a, [], False), s),
+             G.add(s, s), G.exp(G.neg(s))]
+    compare(roots, REDUCE_TOL)
+
+
+def test_views_as_operands():
+    a = G.leaf(W.normal(0, (6, 10)))
+    b = G.leaf(W.normal(1, (10, 6)))
+    at = G.transpose(a, [1, 0])                                   # strided input
+    r1 = G.mul(at, b)
+    r2 = G.add(G.reshape(G.exp(a), [3, 20]), G.leaf(W.normal(2, (20,))))   # reshape of an un-realized node
+    r3 = G.transpose(G.add(a, a), [1, 0])                         # root that is a view of an un-realized node
+    r4 = G.add(G.expand(G.leaf(W.normal(3, (6, 1))), [6, 10]), a)
+    r5 = G.mul(G.transpose(G.exp(a), [1, 0]), b)                  # permuted access to an un-realized node
+    outs, plan = E.realize([r1, r2, r3, r4, r5])
+    ref, _ = O.port_run([r1, r2, r3, r4, r5])
+    for o, r in zip(outs, ref):
+        assert np.abs(o - r).max() <= POINTWISE_TOL * np.abs(r).max()
+
+
+def test_square_row_vector_is_not_mistaken_for_a_row_value():
+    """[R] broadcast against [R, R] runs along columns; a row sum of shape [R] must not be fused as a per-row value."""
+    x = G.leaf(W.normal(0, (8, 8)))
+    s = G.sum_(x, [1], False)            # [8]
+    compare([G.add(x, s)], REDUCE_TOL)   # x[i, j] + s[j]
+
+
+def test_pointwise_tail_sizes():
+    for n in (1, 3, 5, 127, 1000, 1025):
+        a, b = G.leaf(W.normal(0, (n,))), G.leaf(W.normal(1, (n,)))
+        compare([G.div(G.sub(a, b), G.add(G.mul(b, b), G.const(1.0))), G.sum_(G.mul(a, b), [], False)], REDUCE_TOL)
+
+
+def test_wide_rows_fall_back_to_generic_sum():
+    a = G.leaf(W.normal(0, (2, 40000)))
+    plan = compare([G.sum_(G.mul(a, a), [1], False)], REDUCE_TOL)
+    assert "generic_sum" in kinds(plan)
+
+
+def test_matmul_layouts_and_gather():
+    a = G.leaf(W.normal(0, (5, 7)))
+    b = G.leaf(W.normal(1, (7, 3)))
+    c = G.leaf(W.normal(2, (3, 7)))
+    roots = [G.matmul(a, b), G.matmul(a, G.transpose(c, [1, 0])), G.matmul(G.transpose(b, [1, 0]), G.transpose(a, [1, 0])),
+             G.matmul(G.expand(G.leaf(W.normal(3, (1, 7))), [5, 7]), b),                      # stride-0 rows
+             G.matmul(G.expand(G.leaf(W.normal(4, (5, 1))), [5, 7]), b)]                      # stride-0 columns: gathered first
+    compare(roots, REDUCE_TOL)
+
+
+def test_random_graphs_against_oracle():
+    rng = np.random.default_rng(1234)
+    unary = [G.neg, G.exp, G.sin, G.cos]
+    binary = [G.add, G.sub, G.mul]
+    for trial in range(12):
+        R, C = int(rng.integers(1, 9)), int(rng.choice([1, 4, 12, 33, 64]))
+        pool = [G.leaf(rng.uniform(0.5, 1.5, size=s).astype(np.float32)) for s in ((R, C), (R, C), (C,), (R, 1), ())]
+        for _ in range(int(rng.integers(3, 12))):
+            if rng.random() < 0.35:
+                pool.append(unary[int(rng.integers(len(unary)))](pool[int(rng.integers(len(pool)))]))
+            elif rng.random() < 0.75:
+                x, y = pool[int(rng.integers(len(pool)))], pool[int(rng.integers(len(pool)))]
+                try:
+                    pool.append(binary[int(rng.integers(len(binary)))](x, y))
+                except RuntimeError:      # shapes that do not broadcast
+                    pass
+            else:
+                x = pool[int(rng.integers(len(pool)))]
+                if len(x.shape) == 2 and x.op not in G.VIEW_OPS:
+                    axes = [[1], [0], []][int(rng.integers(3))]
+                    pool.append(G.sum_(x, axes, bool(rng.integers(2))))
+        roots = [n for n in pool[-3:] if not n.is_realized]
+        if roots:
+            compare(roots, 5 * REDUCE_TOL)
+
+
+# ---------------------------------------------------------------------------- full-size schedules compile for sm_100a
+def _fake(shape, rg=False):
+    buf = G.Buffer(shape, host=np.zeros(1, np.float32))
+    return G.Node(G.OpEnum.LEAF, data=buf, requires_grad=rg)
+
+
+def test_full_size_schedules_compile_with_nvrtc():
+    """The kernels of the benchmark configurations, generated at full size and compiled for sm_100a (no GPU needed)."""
+    x, gy = _fake((16384, 4096), True), _fake((16384, 4096))
+    y = W.softmax(x); y.grad = gy; G.compute_gradients(y)
+    x2, g, b = _fake((16384, 4096), True), _fake((4096,), True), _fake((4096,), True)
+    y2 = W.layernorm(x2, g, b); y2.grad = gy; G.compute_gradients(y2)
+    a = [_fake((4096, 4096)) for _ in range(3)]
+    plans = [RT.plan([y, x.grad]), RT.plan([y2, x2.grad, g.grad, b.grad]), RT.plan([W.fused_rowsum(*a)])]
+    assert [len(p["steps"]) for p in plans] == [1, 3, 1]
+    for p in plans:
+        assert p["error"] == ""
+        for s in p["steps"]:
+            assert RT.compile_cubin(s["source"]) > 0
+    # algorithmic traffic of the layernorm backward+forward kernel: x, gy in; y, dx out (+ small vectors and partials)
+    big = plans[1]["steps"][0]
+    assert big["bytes_read"] >= 2 * 16384 * 4096 * 4 and big["bytes_written"] >= 2 * 16384 * 4096 * 4
