@@ -19,6 +19,7 @@
 // ormi-core/csrc/backend/cpu/lowerings/pointwise.cpp:5-15), and exp/log/sin/cos are the accurate CUDA
 // functions, never the fast intrinsics.
 #include <algorithm>
+#include <cstdlib>
 #include <functional>
 #include <map>
 #include <sstream>
@@ -245,16 +246,39 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         if (li[l].sc != 1) V = 1;
         for (int d = 0; d < k; ++d) if (spec.loads[l].st[d] % 4 != 0) V = 1;
     }
-    const int target = (V == 4) ? 16 : 8;
+    // Tuning knobs (environment overrides are for experiments only).
+    auto env_int = [](const char* name, int dflt) { const char* v = std::getenv(name); return v ? std::atoi(v) : dflt; };
+    // Depth = number of dependent row-sum levels.  Measured on B200 at [16384, 4096]: a shallow kernel (softmax,
+    // depth 2) is fastest with 16 elements per thread and many resident blocks (5.9 TB/s); a deep one (layernorm
+    // forward+backward, depth 4) needs the register budget capped so that two 512-thread blocks share an SM and
+    // overlap their barrier phases (3.2 TB/s against 2.0 TB/s uncapped).
+    int depth = 0;
+    {
+        std::map<int, int> lvl;
+        for (const KNode& kn : spec.nodes) {
+            int lv = 0;
+            for (auto& r : kn.operands) if (r.t == KRef::NODE) lv = std::max(lv, lvl[r.id]);
+            if (kn.op == KNode::OP_ROWSUM) lv += 1;
+            lvl[kn.node] = lv;
+            depth = std::max(depth, lv);
+        }
+    }
+    const bool deep = depth >= 3;
+    const int target = env_int("ORMI_B200_ROWS_VPT", spec.tune_vpt > 0 ? spec.tune_vpt : ((V == 4) ? (deep ? 8 : 16) : 8));
+    const bool hoist = env_int("ORMI_B200_ROWS_HOIST", spec.tune_hoist) != 0;
+    int minb = env_int("ORMI_B200_ROWS_MINB", spec.tune_minblocks > 0 ? spec.tune_minblocks : (deep ? 2 : 0));
+    const int grid_mult = env_int("ORMI_B200_ROWS_GRID", spec.tune_grid > 0 ? spec.tune_grid : (deep ? 2 : 8));
     int T = std::min(1024, std::max(32, ceil_pow2((C + target - 1) / target)));
     int64_t VPT = (C + T - 1) / T;
     VPT = (VPT + V - 1) / V * V;
     if (VPT > 32) return unsupported("row of " + std::to_string(C) + " elements does not fit in registers");
     const int NT = std::max(T, 256), G = NT / T, NV = (int)VPT / V, NW = T / 32;
+    if (NT * minb > 1024) minb = 0;     // never squeeze a block below 64 registers per thread
     const bool col_pred = (VPT * T != C);
     const bool row_pred = (R % G != 0);
-    int grid = (int)std::min<int64_t>((R + G - 1) / G, (int64_t)spec.num_sms * (NT <= 256 ? 4 : (NT <= 512 ? 2 : 1)));
+    int grid = (int)std::min<int64_t>((R + G - 1) / G, (int64_t)spec.num_sms * (grid_mult > 0 ? grid_mult : (NT <= 256 ? 4 : (NT <= 512 ? 2 : 1))));
     if (grid < 1) grid = 1;
+    if (!hoist) for (auto& I : li) if (I.elem && !I.row_var) I.row_var = true;   // re-read row-invariant vectors every row (L1/L2 hits)
 
     // levels
     std::map<int, int> level;       // node -> level
@@ -281,7 +305,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
 
     std::ostringstream s;
     s << device_prelude();
-    s << "extern \"C\" __global__ void __launch_bounds__(" << NT << ") " << name << "(";
+    s << "extern \"C\" __global__ void __launch_bounds__(" << NT << (minb > 0 ? ", " + std::to_string(minb) : "") << ") " << name << "(";
     for (size_t l = 0; l < spec.loads.size(); ++l) s << (l ? ", " : "") << "const float* __restrict__ in" << l;
     for (size_t o = 0; o < spec.outputs.size(); ++o) s << ((spec.loads.size() + o) ? ", " : "") << "float* __restrict__ out" << o;
     s << ") {\n";
@@ -327,7 +351,10 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     for (size_t l = 0; l < spec.loads.size(); ++l) {
         if (!li[l].row_var) continue;
         std::string ro = "ro" + std::to_string(l);
-        if (li[l].row_collapsed) s << "        const int " << ro << " = r * " << li[l].sr << ";\n";
+        bool invariant = true;
+        for (int d = 0; d < k; ++d) if (spec.loads[l].st[d] != 0) invariant = false;
+        if (invariant) s << "        const int " << ro << " = 0;\n";
+        else if (li[l].row_collapsed) s << "        const int " << ro << " = r * " << li[l].sr << ";\n";
         else {
             s << "        const int " << ro << " = 0";
             for (int d = 0; d < k; ++d) if (spec.loads[l].st[d] != 0) s << " + rc" << d << " * " << spec.loads[l].st[d];

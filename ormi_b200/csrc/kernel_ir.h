@@ -41,6 +41,12 @@ struct KernelSpec {
     std::vector<KNode> nodes;   // in topological (index) order
     std::vector<KOutput> outputs;
     int num_sms = 148;
+    // rows template tuning: elements per thread (0 = default), keep row-invariant vectors in registers,
+    // minimum resident blocks per SM for __launch_bounds__ (0 = none), blocks per SM in the grid (0 = default)
+    int tune_vpt = 0;
+    int tune_hoist = 1;
+    int tune_minblocks = 0;
+    int tune_grid = 0;
 };
 
 struct GeneratedKernel {

@@ -10,6 +10,8 @@
 // rebuilds the same graph every step pays for scheduling, code generation and NVRTC once.
 #include <nvrtc.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "context.h"
@@ -82,13 +84,16 @@ std::vector<char> compile_cubin(const std::string& source, std::string* log_out)
     nvrtcProgram prog;
     if (nvrtcCreateProgram(&prog, source.c_str(), "ormi_fused.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS)
         throw Error("NVRTC Error: cannot create program");
-    const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17", "-default-device"};
-    nvrtcResult r = nvrtcCompileProgram(prog, 4, opts);
+    // ORMI_B200_NVRTC_LOG=1 adds ptxas -v (registers, spills, shared memory) and prints the compiler log
+    const bool verbose = std::getenv("ORMI_B200_NVRTC_LOG") != nullptr;
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17", "-default-device", "--ptxas-options=-v"};
+    nvrtcResult r = nvrtcCompileProgram(prog, verbose ? 5 : 4, opts);
     size_t log_size = 0;
     nvrtcGetProgramLogSize(prog, &log_size);
     std::string log(log_size, '\0');
     if (log_size > 1) nvrtcGetProgramLog(prog, &log[0]);
     if (log_out) *log_out = log;
+    if (verbose && log_size > 1) fprintf(stderr, "%s\n", log.c_str());
     if (r != NVRTC_SUCCESS) {
         nvrtcDestroyProgram(&prog);
         throw Error("NVRTC Compilation failed: \n" + log);

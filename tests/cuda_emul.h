@@ -22,7 +22,7 @@ static float emul_slots[1024];
 #define __global__
 #define __device__
 #define __forceinline__ inline
-#define __launch_bounds__(x)
+#define __launch_bounds__(...)
 #define __shared__ static
 
 static inline float __fadd_rn(float a, float b) { return a + b; }
