@@ -139,6 +139,19 @@ int ormi_b200_matmul(ormi_b200_ctx* ctx,
                      const float* B, int ndim_b, const int32_t* shape_b, const int32_t* strides_b,
                      float* out, int ndim_out, const int32_t* shape_out);
 
+/* Column sums of a contiguous fp32 matrix, out[c] = sum over r of in[r * cols + c], WITHOUT allocating anything.
+ * No counterpart in the reference: it exists for callers that cannot call cudaMalloc when they need the
+ * reduction — their device memory is already owned, whole, by another allocator, or they sit in a steady-state
+ * loop that must not hit an allocation's device-wide synchronisation.  The per-block partials that
+ * ormi_b200_sum takes from the context's pool live here in a fixed 2 MiB array inside the library image (every
+ * GPU that loads the library holds it until exit).  Limits and rules:
+ *   - cols <= 65536, otherwise the call fails with an explanatory error (use ormi_b200_sum instead);
+ *   - runs on the CURRENT device, on `stream` (a cudaStream_t, NULL = default stream); needs no context;
+ *   - all calls share the one scratch array: calls that overlap on the GPU (other streams, other threads) race;
+ *   - the first call on a device also fetches the array's device address; make it before any stream capture.
+ * Results are deterministic; they differ from ormi_b200_sum only by fp32 summation order. */
+int ormi_b200_colsum_static(const float* in, int64_t rows, int64_t cols, float* out, void* stream);
+
 /* ------------------------------------------------------------------ options, counters -- */
 
 /* Matmul arithmetic used by ormi_b200_realize / ormi_b200_matmul (additive knob; the reference has none):

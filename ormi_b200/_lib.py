@@ -40,6 +40,7 @@ _SIGNATURES = {
     "ormi_b200_sum": (c_int, [c_void_p, c_void_p, c_int, P(ctypes.c_int32), P(ctypes.c_int32), P(ctypes.c_int32), c_int, c_void_p]),
     "ormi_b200_matmul": (c_int, [c_void_p, c_void_p, c_int, P(ctypes.c_int32), P(ctypes.c_int32),
                                  c_void_p, c_int, P(ctypes.c_int32), P(ctypes.c_int32), c_void_p, c_int, P(ctypes.c_int32)]),
+    "ormi_b200_colsum_static": (c_int, [c_void_p, ctypes.c_int64, ctypes.c_int64, c_void_p, c_void_p]),
     "ormi_b200_set_option": (c_int, [c_void_p, c_char_p, c_char_p]),
     "ormi_b200_get_counter": (c_int, [c_void_p, c_char_p, P(ctypes.c_int64)]),
 }

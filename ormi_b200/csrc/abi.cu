@@ -18,6 +18,7 @@ static int guarded(F&& f) {
 static void need(bool cond, const char* msg) { if (!cond) throw Error(msg); }
 
 namespace ormi_b200 {
+void set_last_error(const std::string& msg) { g_last_error = msg; }
 void gemm_bf16(ormi_b200_ctx* ctx, const GemmArgs& g);
 void gemm_dispatch(ormi_b200_ctx* ctx, const GemmArgs& g) {
     if (ctx->matmul_mode == MatmulMode::BF16) gemm_bf16(ctx, g);
