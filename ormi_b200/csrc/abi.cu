@@ -19,7 +19,6 @@ static void need(bool cond, const char* msg) { if (!cond) throw Error(msg); }
 
 namespace ormi_b200 {
 void set_last_error(const std::string& msg) { g_last_error = msg; }
-void gemm_bf16(ormi_b200_ctx* ctx, const GemmArgs& g);
 void gemm_dispatch(ormi_b200_ctx* ctx, const GemmArgs& g) {
     if (ctx->matmul_mode == MatmulMode::BF16) gemm_bf16(ctx, g);
     else gemm_ffma(ctx, g);
@@ -59,6 +58,7 @@ int ormi_b200_shutdown(ormi_b200_ctx* ctx) {
         for (auto& kv : ctx->kernel_cache) if (kv.second.module) ctx->drv.ModuleUnload(kv.second.module);
         for (auto& kv : ctx->free_blocks) for (void* p : kv.second) cudaFree(p);
         for (int i = 0; i < 2; ++i) if (ctx->stage[i]) cudaFree(ctx->stage[i]);
+        if (ctx->gemm_err) cudaFree(ctx->gemm_err);
         cudaStreamDestroy(ctx->stream);
         delete ctx;
     });
@@ -104,6 +104,7 @@ int ormi_b200_memcpy_d2h(ormi_b200_ctx* ctx, void* dst, const void* src, size_t 
         need(ctx != nullptr, "ctx is NULL");
         ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
         ORMI_CUDA(cudaStreamSynchronize(ctx->stream));
+        check_gemm_error(ctx);
     });
 }
 
@@ -126,7 +127,7 @@ int ormi_b200_fill_u8(ormi_b200_ctx* ctx, void* dst, uint8_t pattern, size_t cou
 }
 
 int ormi_b200_sync(ormi_b200_ctx* ctx) {
-    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); ORMI_CUDA(cudaStreamSynchronize(ctx->stream)); });
+    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); ORMI_CUDA(cudaStreamSynchronize(ctx->stream)); check_gemm_error(ctx); });
 }
 
 void* ormi_b200_stream(ormi_b200_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }

@@ -72,6 +72,8 @@ struct ormi_b200_ctx {
     // bf16 staging for the tensor-core GEMM path (grown on demand, reused across calls)
     void* stage[2] = {nullptr, nullptr};
     size_t stage_bytes[2] = {0, 0};
+    int* gemm_err = nullptr;          // device word: non-zero when a bounded wait inside the tensor-core GEMM ran out
+    bool gemm_err_pending = false;    // a tensor-core GEMM was launched since the word was last read
 
     std::map<std::string, int64_t> counters;
     void* nccl = nullptr;   // opaque: collective state (nccl.cpp)
@@ -99,6 +101,8 @@ struct GemmArgs {
 };
 void gemm_ffma(ormi_b200_ctx* ctx, const GemmArgs& g);
 void gemm_dispatch(ormi_b200_ctx* ctx, const GemmArgs& g);
+void gemm_bf16(ormi_b200_ctx* ctx, const GemmArgs& g);
+void check_gemm_error(ormi_b200_ctx* ctx);   // throws when the tensor-core kernel reported a wait that ran out
 
 // `preassigned`: optional (node, pointer) pairs — write that node's value into a caller-owned buffer
 // instead of a fresh pool block (used by the raw-buffer sum / matmul entry points).

@@ -1,5 +1,359 @@
-// placeholder until the tensor-core path lands
+// bf16 tensor-core GEMM for sm_100a: tcgen05.mma with TMEM accumulators, operands staged by TMA.
+//
+// Opt-in matmul arithmetic ("matmul" = "bf16") behind ormi::cuda::matmul
+// (ormi-core/csrc/backend/cuda/kernels/blas/matmul.cu:19-112, which calls cublasSgemmBatched): fp32 operands
+// are rounded to bf16 once, products are accumulated in fp32 in tensor memory, C is written in fp32.
+//
+//   C[M,N] = A[M,K] * B[K,N]
+//
+// Layout in HBM.  Both operands are first brought into "K-major" bf16 staging buffers, A as [M][Kp] and B
+// transposed as [N][Kp] (Kp = K rounded up to 64, zero padded), whatever strides / transposition the
+// views had: one conversion pass each (cvt_kmajor), which is also where fp32 -> bf16 happens.
+//
+// Kernel.  Persistent, one 192-thread block per SM, tile 128 x 256 x 64:
+//   warp 0     producer: one lane issues the TMA loads of the A (128x64) and B (256x64) boxes of the next
+//              k-slice into a 4-stage shared-memory ring (128-byte swizzle), completion counted on an mbarrier;
+//   warp 1     allocates 512 TMEM columns (two 128x256 fp32 accumulators); one lane issues 4 tcgen05.mma
+//              (M=128, N=256, K=16) per stage and commits them to the stage's "empty" barrier; after the last
+//              slice of a tile it commits to the accumulator's "full" barrier;
+//   warps 2-5  epilogue: each warp owns 32 TMEM lanes (= 32 rows of the tile), reads the accumulator with
+//              tcgen05.ld 32 columns at a time and stores fp32 rows to C; then releases the accumulator.
+// The two accumulators let the epilogue of tile i overlap the MMAs of tile i+1.  Tiles are walked in groups
+// of 16 row-blocks so that concurrently running blocks share A and B panels in L2.
+//
+// No cluster launch and no multicast anywhere: every block fetches its own boxes.
+//
+// Every wait is bounded (about two seconds on the global timer).  A wait that runs out raises a block-wide
+// abort flag and an error word in global memory; every role then leaves its loop, the block lets copies in
+// flight land, frees its tensor memory and exits; the host turns the error word into a failure.
+#include <cuda_bf16.h>
+
 #include "context.h"
+
 namespace ormi_b200 {
-void gemm_bf16(ormi_b200_ctx*, const GemmArgs&) { throw Error("bf16 tensor-core matmul is not built yet"); }
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2, B_STAGE_BYTES = BN * BK * 2;
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 16;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long global_ns() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the block is aborting (this wait ran out, or another role's did).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i) if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; atomicCAS(err, 0, code); return false; }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) and were written with the
+// 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO), the leading-dimension offset is unused (1),
+// descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, N = 256, M = 128.
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(IDESC), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    #pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mb, int& nb) {
+    const int per_group = GROUP_M * tiles_n;
+    const int g = t / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsz = min(GROUP_M, tiles_m - first_m);
+    const int in_g = t - g * per_group;
+    mb = first_m + in_g % gsz;
+    nb = in_g / gsz;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 float* __restrict__ C, int M, int N, int num_kb, int tiles_m, int tiles_n, int* err) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;       // swizzled tiles need 1024-byte alignment
+    uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + STAGES * STAGE_BYTES;                   // 8-byte mbarriers
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = tiles_m * tiles_n;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            int s = 0; uint32_t phase = 0;
+            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+                int mb, nb; tile_coords(t, tiles_m, tiles_n, mb, nb);
+                bool ok = true;
+                for (int kb = 0; kb < num_kb && ok; ++kb) {
+                    ok = mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, err, 1);
+                    if (!ok) break;
+                    mbar_expect_tx(full_bar(s), STAGE_BYTES);
+                    tma_load_2d(base + s * STAGE_BYTES, &map_a, full_bar(s), kb * BK, mb * BM);
+                    tma_load_2d(base + s * STAGE_BYTES + A_STAGE_BYTES, &map_b, full_bar(s), kb * BK, nb * BN);
+                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int s = 0; uint32_t phase = 0;
+            int it = 0;
+            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+                const int a = it & 1;
+                const uint32_t aphase = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(a), aphase ^ 1u, abort_flag, err, 2)) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(a * BN);
+                bool ok = true;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(full_bar(s), phase, abort_flag, err, 3);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da = umma_desc_sw128(base + s * STAGE_BYTES);
+                    const uint64_t db = umma_desc_sw128(base + s * STAGE_BYTES + A_STAGE_BYTES);
+                    #pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)     // 32 bytes further along K inside the swizzle atom
+                        umma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(empty_bar(s));                // frees the stage once these MMAs have read it
+                    if (++s == STAGES) { s = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                umma_commit(tfull_bar(a));                    // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;                         // TMEM lanes 32*quarter .. 32*quarter+31
+        int it = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+            int mb, nb; tile_coords(t, tiles_m, tiles_n, mb, nb);
+            const int a = it & 1;
+            const uint32_t aphase = (uint32_t)(it >> 1) & 1u;
+            bool ok = mbar_wait(tfull_bar(a), aphase, abort_flag, err, 4);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = mb * BM + quarter * 32 + lane;
+            float* crow = C + (size_t)row * N + (size_t)nb * BN;
+            #pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                float v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * BN + c * 32), v);
+                const int col0 = nb * BN + c * 32;
+                if (row < M) {
+                    if (col0 + 32 <= N && (N & 3) == 0) {
+                        #pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            *reinterpret_cast<float4*>(crow + c * 32 + 4 * i) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    } else {
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) if (col0 + i < N) crow[c * 32 + i] = v[i];
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(a));
+        }
+    }
+
+    // ------------------------------------------------------------------ teardown
+    __syncwarp();
+    if (*abort_flag) {                     // let copies that are still in flight land before the block goes away
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 200000ull) { }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// dst[row * Kp + k] = bf16(src[row * s_row + k * s_k]) for row < rows, k < K; zero for K <= k < Kp.
+// A 32x32 tile goes through shared memory so that both the read (along whichever source axis is contiguous) and the
+// write (along k) are coalesced.
+template <bool SRC_K_CONTIG>
+__global__ void __launch_bounds__(256)
+cvt_kmajor(const float* __restrict__ src, long long s_row, long long s_k, int rows, int K, int Kp, __nv_bfloat16* __restrict__ dst) {
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // 32 x 8
+    const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+    #pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (SRC_K_CONTIG) {
+            const int r = r0 + ty + 8 * j, k = k0 + tx;
+            tile[ty + 8 * j][tx] = (r < rows && k < K) ? src[r * s_row + k * s_k] : 0.0f;
+        } else {
+            const int r = r0 + tx, k = k0 + ty + 8 * j;
+            tile[tx][ty + 8 * j] = (r < rows && k < K) ? src[r * s_row + k * s_k] : 0.0f;
+        }
+    }
+    __syncthreads();
+    #pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int r = r0 + ty + 8 * j, k = k0 + tx;
+        if (r < rows && k < Kp) dst[(size_t)r * Kp + k] = __float2bfloat16_rn(tile[ty + 8 * j][tx]);
+    }
+}
+
+void convert(ormi_b200_ctx* ctx, const float* src, long long s_row, long long s_k, int rows, int K, int Kp, __nv_bfloat16* dst) {
+    dim3 grid((Kp + 31) / 32, (rows + 31) / 32);
+    if (s_k == 1) cvt_kmajor<true><<<grid, 256, 0, ctx->stream>>>(src, s_row, s_k, rows, K, Kp, dst);
+    else cvt_kmajor<false><<<grid, 256, 0, ctx->stream>>>(src, s_row, s_k, rows, K, Kp, dst);
+    ORMI_CUDA(cudaGetLastError());
+    ctx->counters["launches"]++;
+}
+
+void* stage_buffer(ormi_b200_ctx* ctx, int which, size_t bytes) {
+    if (ctx->stage_bytes[which] < bytes) {
+        if (ctx->stage[which]) { ORMI_CUDA(cudaStreamSynchronize(ctx->stream)); ORMI_CUDA(cudaFree(ctx->stage[which])); ctx->stage[which] = nullptr; }
+        ORMI_CUDA(cudaMalloc(&ctx->stage[which], bytes));
+        ctx->stage_bytes[which] = bytes;
+    }
+    return ctx->stage[which];
+}
+
+void make_map(ormi_b200_ctx* ctx, CUtensorMap* map, void* ptr, int rows, int Kp, int box_rows) {
+    cuuint64_t dims[2] = {(cuuint64_t)Kp, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)Kp * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    ctx->drv.check(ctx->drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr,
+                                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+                   "cuTensorMapEncodeTiled");
+}
+
+}  // namespace
+
+void gemm_bf16(ormi_b200_ctx* ctx, const GemmArgs& g) {
+    // Small or batched problems stay on the fp32 path (a batch is a loop of independent GEMMs; the tensor path is
+    // worth its two conversion passes only for large single products).
+    if (g.batch != 1 || (long long)g.M * g.N * g.K < (1ll << 21) || g.K < 64) { gemm_ffma(ctx, g); return; }
+    const int Kp = (g.K + BK - 1) / BK * BK;
+    __nv_bfloat16* a16 = (__nv_bfloat16*)stage_buffer(ctx, 0, (size_t)g.M * Kp * 2);
+    __nv_bfloat16* b16 = (__nv_bfloat16*)stage_buffer(ctx, 1, (size_t)g.N * Kp * 2);
+    // A(m,k) = A[m*lda + k] (or A[k*lda + m] when stored transposed); B(k,n) = B[k*ldb + n] (or B[n*ldb + k])
+    convert(ctx, g.A, g.trans_a ? 1 : g.lda, g.trans_a ? g.lda : 1, g.M, g.K, Kp, a16);
+    convert(ctx, g.B, g.trans_b ? g.ldb : 1, g.trans_b ? 1 : g.ldb, g.N, g.K, Kp, b16);
+
+    CUtensorMap map_a, map_b;
+    make_map(ctx, &map_a, a16, g.M, Kp, BM);
+    make_map(ctx, &map_b, b16, g.N, Kp, BN);
+    if (!ctx->gemm_err) {
+        ORMI_CUDA(cudaMalloc(&ctx->gemm_err, sizeof(int)));
+        ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err, 0, sizeof(int), ctx->stream));
+        ORMI_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    }
+    const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
+    const int grid = std::min(tiles_m * tiles_n, ctx->num_sms);
+    gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(map_a, map_b, g.C, g.M, g.N, Kp / BK, tiles_m, tiles_n, ctx->gemm_err);
+    ORMI_CUDA(cudaGetLastError());
+    ctx->gemm_err_pending = true;
+    ctx->counters["gemm_launches"]++;
+    ctx->counters["launches"]++;
+}
+
+// Called at host-visible boundaries (sync, device -> host copies): a bounded wait that ran out inside the tensor-core
+// kernel left a code in the error word.
+void check_gemm_error(ormi_b200_ctx* ctx) {
+    if (!ctx->gemm_err || !ctx->gemm_err_pending) return;
+    int code = 0;
+    ORMI_CUDA(cudaMemcpyAsync(&code, ctx->gemm_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    ORMI_CUDA(cudaStreamSynchronize(ctx->stream));
+    ctx->gemm_err_pending = false;
+    if (code != 0) {
+        ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err, 0, sizeof(int), ctx->stream));
+        throw Error("tensor-core GEMM: a pipeline wait ran out (code " + std::to_string(code) + ": 1 producer, 2 accumulator, 3 operands, 4 epilogue)");
+    }
+}
+
+}  // namespace ormi_b200

@@ -242,3 +242,49 @@ def test_raw_buffer_sum_and_matmul_entry_points(device):
     ok(lib.ormi_b200_matmul(device.handle, ctypes.c_void_p(da.dev_ptr), 2, sa, sta, ctypes.c_void_p(db.dev_ptr), 2, sb, stb,
                             ctypes.c_void_p(dc.dev_ptr), 2, so))
     assert rel(device.download(dc), A @ B) <= REDUCE_TOL
+
+
+@pytest.mark.parametrize("mnk", [(256, 256, 256), (1024, 1024, 1024), (300, 520, 200), (128, 2048, 4096), (4096, 256, 512)])
+def test_matmul_bf16_tensor_core(mnk):
+    """Opt-in tcgen05 path: bf16 operands, fp32 accumulation in tensor memory; tolerance 2e-2."""
+    from ormi_b200.runtime import Device
+    M, N, K = mnk
+    dev = Device(0)
+    try:
+        dev.set_option("matmul", "bf16")
+        a = W.normal(0, (M, K), 1 / math.sqrt(K))
+        b = W.normal(1, (K, N), 1 / math.sqrt(K))
+        want = a.astype(np.float64) @ b.astype(np.float64)
+        la, lb = G.leaf(a), G.leaf(b)
+        lat, lbt = G.leaf(np.ascontiguousarray(a.T)), G.leaf(np.ascontiguousarray(b.T))
+        for root in (G.matmul(la, lb), G.matmul(G.transpose(lat, [1, 0]), lb), G.matmul(la, G.transpose(lbt, [1, 0])),
+                     G.matmul(G.transpose(lat, [1, 0]), G.transpose(lbt, [1, 0]))):
+            got = dev.numpy(root)
+            assert rel(got, want) <= BF16_TOL, rel(got, want)
+        # exact check: operands that are exactly representable in bf16 give the fp32 result of the same products
+        ai = np.random.default_rng(0).integers(-4, 5, size=(M, K)).astype(np.float32)
+        bi = np.random.default_rng(1).integers(-4, 5, size=(K, N)).astype(np.float32)
+        got = dev.numpy(G.matmul(G.leaf(ai), G.leaf(bi)))
+        assert np.array_equal(got, ai @ bi)
+        assert dev.counter("gemm_launches") >= 5
+    finally:
+        dev.close()
+
+
+def test_mlp_training_step_bf16_matmuls():
+    from ormi_b200.runtime import Device
+    dev = Device(0)
+    try:
+        dev.set_option("matmul", "bf16")
+        B, D, H = 1024, 256, 1024
+        x, t = G.leaf(W.normal(0, (B, D))), G.leaf(W.normal(1, (B, D)))
+        w1, b1 = G.leaf(W.kaiming_uniform(2, D, (D, H)), True), G.leaf(np.zeros(H, np.float32), True)
+        w2, b2 = G.leaf(W.kaiming_uniform(3, H, (H, D)), True), G.leaf(np.zeros(D, np.float32), True)
+        loss = W.mlp_loss(x, w1, b1, w2, b2, t)
+        G.compute_gradients(loss)
+        roots = [loss, w1.grad, b1.grad, w2.grad, b2.grad]
+        ref, _ = O.port_run(roots)
+        for r, w in zip(roots, ref):
+            assert rel(dev.numpy(r), w) <= BF16_TOL
+    finally:
+        dev.close()
