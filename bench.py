@@ -212,6 +212,66 @@ def run_reference_arm(args, rank):
     print(json.dumps(line))
 
 
+def matmul_sweep(dev, torch, G, W, steps=5):
+    """configs[2]: C = A @ B, fp32 (SIMT FFMA path, through the graph) and bf16 (tcgen05 path on operands already
+    converted to bf16 in HBM; the conversion pass is timed on its own)."""
+    from ormi_b200._lib import lib, check
+    out = {}
+    for (M, N, K) in [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (8192, 1024, 8192)]:
+        a = dev.leaf(W.normal(0, (M, K), 1 / math.sqrt(K)))
+        b = dev.leaf(W.normal(1, (K, N), 1 / math.sqrt(K)))
+        flop = 2.0 * M * N * K
+        rec = {}
+        dev.set_option("matmul", "fp32")
+        runner = StepRunner(dev, G, [[G.matmul(a, b)]])
+        n32 = steps if flop < 3e11 else 2
+        for _ in range(2):
+            runner.run()
+        rec["fp32_ffma_tflops"] = flop / (timed(dev, torch, lambda: runner.run(), n32) / n32 * 1e-3) / 1e12
+        Kp = (K + 63) // 64 * 64
+        a16, b16, c = dev.alloc(M * Kp * 2), dev.alloc(N * Kp * 2), dev.alloc(M * N * 4)
+        h = dev.handle
+
+        def cvt():
+            check(lib.ormi_b200_cvt_bf16_kmajor(h, ctypes.c_void_p(a.data.dev_ptr), K, 1, M, K, ctypes.c_void_p(a16)))
+            check(lib.ormi_b200_cvt_bf16_kmajor(h, ctypes.c_void_p(b.data.dev_ptr), 1, N, N, K, ctypes.c_void_p(b16)))
+
+        def gemm():
+            check(lib.ormi_b200_gemm_bf16_kmajor(h, ctypes.c_void_p(a16), ctypes.c_void_p(b16), ctypes.c_void_p(c), M, N, Kp))
+
+        for _ in range(3):
+            cvt(); gemm()
+        rec["bf16_convert_ms"] = timed(dev, torch, cvt, steps) / steps
+        rec["bf16_tcgen05_tflops"] = flop / (timed(dev, torch, gemm, 2 * steps) / (2 * steps) * 1e-3) / 1e12
+        for ptr, nbytes in ((a16, M * Kp * 2), (b16, N * Kp * 2), (c, M * N * 4)):
+            dev.free(ptr, nbytes)
+        out[f"{M}x{N}x{K}"] = rec
+        del runner, a, b
+    dev.set_option("matmul", "fp32")
+    return out
+
+
+def mlp_steps_per_s(dev, torch, W, batch, d_in, hidden, matmul, steps, rank=0, world=1, dist=None, global_batch=None):
+    """configs[3] / configs[4]: full training step (forward, autograd backward, SGD update) of the 2-layer MLP."""
+    from ormi_b200.train_step import MLPTrainer
+    dev.set_option("matmul", matmul)
+    x = W.normal(1000 + rank, (batch, d_in))
+    t = W.normal(2000 + rank, (batch, d_in))
+    w1, w2 = W.kaiming_uniform(2, d_in, (d_in, hidden)), W.kaiming_uniform(3, hidden, (hidden, d_in))
+    b1, b2 = np.zeros(hidden, np.float32), np.zeros(d_in, np.float32)
+    tr = MLPTrainer(dev, x, t, w1, b1, w2, b2, lr=0.05, global_batch=global_batch or batch * world, world=world)
+    for _ in range(3):
+        tr.step()
+    dev.sync()
+    first = tr.loss()
+    ms = timed(dev, torch, tr.step, steps, dist) / steps
+    last = tr.loss()
+    dev.set_option("matmul", "fp32")
+    flop = 5 * 2.0 * batch * world * d_in * hidden
+    return {"steps_per_s": 1e3 / ms, "ms_per_step": ms, "gemm_tflops_per_gpu": flop / world / (ms * 1e-3) / 1e12,
+            "loss_first": first, "loss_last": last}
+
+
 def run_only(args):
     """One graph, a few launches, nothing else: the small case profilers attach to."""
     import torch
@@ -243,6 +303,7 @@ def main():
     ap.add_argument("--only", default=None, choices=["softmax", "layernorm", "rowsum"],
                     help="profiling aid: run just this graph --steps times on --rows rows and exit")
     ap.add_argument("--rows", type=int, default=8192)
+    ap.add_argument("--no-extras", action="store_true", help="skip the matmul sweep and the MLP training steps")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -340,6 +401,36 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
 
+    # the other two legs of the metric: matmul TFLOP/s (configs[2]) and MLP training steps/s (configs[3], configs[4])
+    extras = {}
+    if not args.no_extras:
+        del runner, pinned, out_host
+        for node in inputs.values():
+            node.data = None
+        inputs.clear()
+        sm_roots.clear(); ln_roots.clear()
+        import gc
+        gc.collect()
+        from ormi_b200._lib import lib as _lib, check as _check
+        _check(_lib.ormi_b200_trim(dev.handle))
+        if world == 1:
+            extras["matmul"] = matmul_sweep(dev, torch, G, W)
+            extras["mlp_fp32_config3"] = dict(mlp_steps_per_s(dev, torch, W, 8192, 1024, 4096, "fp32", 5),
+                                              shape="B=8192, 1024->4096->1024, fp32 FFMA matmuls")
+        else:
+            from ormi_b200.train_step import init_comm
+
+            def bcast(payload):
+                obj = [payload]
+                dist.broadcast_object_list(obj, src=0)
+                return obj[0]
+            init_comm(dev, rank, world, bcast)
+        gb = 65536
+        extras["mlp_bf16_config4"] = dict(mlp_steps_per_s(dev, torch, W, gb // world, 2048, 8192, "bf16", 10, rank, world, dist, gb),
+                                          shape=f"global batch {gb} split over {world} GPU(s), 2048->8192->2048, bf16 tcgen05 matmuls, "
+                                                "fp32 master weights, gradient all-reduce overlapped with backward",
+                                          scaling="strong")
+
     if rank == 0:
         peak, peak_src = peaks()
         ms_step = ms_total / args.steps
@@ -364,6 +455,7 @@ def main():
             "cpu_baseline": {"value": cpu_gbps, "unit": UNIT, "cores": cores, "kind": kind,
                              "sample": f"2048 of {R} rows, one run ({cpu_secs:.1f} s), autograd + realize on the reference CPU backend"},
         }
+        line["extra"] = extras
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

@@ -139,6 +139,30 @@ int ormi_b200_matmul(ormi_b200_ctx* ctx,
                      const float* B, int ndim_b, const int32_t* shape_b, const int32_t* strides_b,
                      float* out, int ndim_out, const int32_t* shape_out);
 
+/* The two halves of the bf16 tensor-core matmul, for callers that keep bf16 copies of their operands (weights that
+ * change once per step) instead of converting inside every matmul.  No counterpart in the reference, whose matmul is
+ * one cublasSgemmBatched call (kernels/blas/matmul.cu:98-105).
+ *   cvt:  dst[r][k] = bf16(src[r * row_stride + k * k_stride]) for r < rows, k < K; dst is rows x Kp bf16 with
+ *         Kp = K rounded up to a multiple of 64, the padding zero ("K-major" staging layout).
+ *   gemm: C[M,N] (fp32, contiguous) = A16[M][Kp] * B16[N][Kp]^T, fp32 accumulation (tcgen05.mma, TMEM, TMA). */
+int ormi_b200_cvt_bf16_kmajor(ormi_b200_ctx* ctx, const float* src, int64_t row_stride, int64_t k_stride,
+                              int rows, int K, void* dst);
+int ormi_b200_gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, float* C, int M, int N, int Kp);
+
+/* ------------------------------------------------------------------ multi-GPU combine -- */
+
+/* Batch-sharded runs: one process per GPU, each realizes its own row shard; parameter gradients (and column / global
+ * sums of sharded inputs) are summed over the ranks with NCCL over NVLink.  The reference has no counterpart (single
+ * device).  `id` is NCCL's 128-byte unique id: create it on one rank, hand it to the others by any host channel.
+ * allreduce: in-place fp32 sum of `n` buffers (one NCCL group).  overlap = 0 queues it on the compute stream;
+ * overlap = 1 queues it on a second stream behind everything queued so far, so later kernels run beside it —
+ * ormi_b200_comm_join then makes the compute stream wait for the results. */
+int ormi_b200_comm_unique_id(char id[128]);
+int ormi_b200_comm_init(ormi_b200_ctx* ctx, const char id[128], int rank, int world_size);
+int ormi_b200_allreduce_sum_f32(ormi_b200_ctx* ctx, void* const* buffers, const size_t* counts, int n, int overlap);
+int ormi_b200_comm_join(ormi_b200_ctx* ctx);
+int ormi_b200_comm_destroy(ormi_b200_ctx* ctx);
+
 /* Column sums of a contiguous fp32 matrix, out[c] = sum over r of in[r * cols + c], WITHOUT allocating anything.
  * No counterpart in the reference: it exists for callers that cannot call cudaMalloc when they need the
  * reduction — their device memory is already owned, whole, by another allocator, or they sit in a steady-state

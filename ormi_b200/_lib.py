@@ -41,6 +41,13 @@ _SIGNATURES = {
     "ormi_b200_matmul": (c_int, [c_void_p, c_void_p, c_int, P(ctypes.c_int32), P(ctypes.c_int32),
                                  c_void_p, c_int, P(ctypes.c_int32), P(ctypes.c_int32), c_void_p, c_int, P(ctypes.c_int32)]),
     "ormi_b200_colsum_static": (c_int, [c_void_p, ctypes.c_int64, ctypes.c_int64, c_void_p, c_void_p]),
+    "ormi_b200_cvt_bf16_kmajor": (c_int, [c_void_p, c_void_p, ctypes.c_int64, ctypes.c_int64, c_int, c_int, c_void_p]),
+    "ormi_b200_gemm_bf16_kmajor": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
+    "ormi_b200_comm_unique_id": (c_int, [c_char_p]),
+    "ormi_b200_comm_init": (c_int, [c_void_p, c_char_p, c_int, c_int]),
+    "ormi_b200_allreduce_sum_f32": (c_int, [c_void_p, P(c_void_p), P(c_size_t), c_int, c_int]),
+    "ormi_b200_comm_join": (c_int, [c_void_p]),
+    "ormi_b200_comm_destroy": (c_int, [c_void_p]),
     "ormi_b200_set_option": (c_int, [c_void_p, c_char_p, c_char_p]),
     "ormi_b200_get_counter": (c_int, [c_void_p, c_char_p, P(ctypes.c_int64)]),
 }

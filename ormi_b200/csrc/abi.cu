@@ -54,6 +54,7 @@ int ormi_b200_shutdown(ormi_b200_ctx* ctx) {
     return guarded([&] {
         if (!ctx) return;
         cudaSetDevice(ctx->device);
+        comm_destroy(ctx);
         cudaStreamSynchronize(ctx->stream);
         for (auto& kv : ctx->kernel_cache) if (kv.second.module) ctx->drv.ModuleUnload(kv.second.module);
         for (auto& kv : ctx->free_blocks) for (void* p : kv.second) cudaFree(p);
@@ -226,6 +227,43 @@ int ormi_b200_matmul(ormi_b200_ctx* ctx,
         std::vector<std::pair<int, void*>> pre{{2, (void*)out}};
         realize(ctx, g, 3, &root, 1, &pre);
     });
+}
+
+int ormi_b200_cvt_bf16_kmajor(ormi_b200_ctx* ctx, const float* src, int64_t row_stride, int64_t k_stride, int rows, int K, void* dst) {
+    return guarded([&] {
+        need(ctx && src && dst && rows > 0 && K > 0, "ormi_b200_cvt_bf16_kmajor: bad arguments");
+        cvt_bf16_kmajor(ctx, src, row_stride, k_stride, rows, K, dst);
+    });
+}
+
+int ormi_b200_gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, float* C, int M, int N, int Kp) {
+    return guarded([&] {
+        need(ctx && a16 && b16 && C, "ormi_b200_gemm_bf16_kmajor: NULL argument");
+        gemm_bf16_kmajor(ctx, a16, b16, C, M, N, Kp);
+    });
+}
+
+int ormi_b200_comm_unique_id(char id[128]) {
+    return guarded([&] { need(id != nullptr, "ormi_b200_comm_unique_id: NULL argument"); comm_unique_id(id); });
+}
+
+int ormi_b200_comm_init(ormi_b200_ctx* ctx, const char id[128], int rank, int world_size) {
+    return guarded([&] { need(ctx && id, "ormi_b200_comm_init: NULL argument"); comm_init(ctx, id, rank, world_size); });
+}
+
+int ormi_b200_allreduce_sum_f32(ormi_b200_ctx* ctx, void* const* buffers, const size_t* counts, int n, int overlap) {
+    return guarded([&] {
+        need(ctx && buffers && counts && n > 0, "ormi_b200_allreduce_sum_f32: bad arguments");
+        comm_allreduce(ctx, buffers, counts, n, overlap);
+    });
+}
+
+int ormi_b200_comm_join(ormi_b200_ctx* ctx) {
+    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); comm_join(ctx); });
+}
+
+int ormi_b200_comm_destroy(ormi_b200_ctx* ctx) {
+    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); comm_destroy(ctx); });
 }
 
 int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value) {

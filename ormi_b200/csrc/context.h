@@ -103,6 +103,15 @@ void gemm_ffma(ormi_b200_ctx* ctx, const GemmArgs& g);
 void gemm_dispatch(ormi_b200_ctx* ctx, const GemmArgs& g);
 void gemm_bf16(ormi_b200_ctx* ctx, const GemmArgs& g);
 void check_gemm_error(ormi_b200_ctx* ctx);   // throws when the tensor-core kernel reported a wait that ran out
+void gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, float* C, int M, int N, int Kp);
+void cvt_bf16_kmajor(ormi_b200_ctx* ctx, const float* src, long long s_row, long long s_k, int rows, int K, void* dst);
+
+// collectives (comm.cu)
+void comm_unique_id(char* out128);
+void comm_init(ormi_b200_ctx* ctx, const char* id128, int rank, int world);
+void comm_allreduce(ormi_b200_ctx* ctx, void* const* bufs, const size_t* counts, int n, int overlap);
+void comm_join(ormi_b200_ctx* ctx);
+void comm_destroy(ormi_b200_ctx* ctx);
 
 // `preassigned`: optional (node, pointer) pairs — write that node's value into a caller-owned buffer
 // instead of a fresh pool block (used by the raw-buffer sum / matmul entry points).

@@ -325,21 +325,33 @@ void gemm_bf16(ormi_b200_ctx* ctx, const GemmArgs& g) {
     convert(ctx, g.A, g.trans_a ? 1 : g.lda, g.trans_a ? g.lda : 1, g.M, g.K, Kp, a16);
     convert(ctx, g.B, g.trans_b ? g.ldb : 1, g.trans_b ? 1 : g.ldb, g.N, g.K, Kp, b16);
 
+    gemm_bf16_kmajor(ctx, a16, b16, g.C, g.M, g.N, Kp);
+}
+
+// C[M,N] (fp32) = A16[M][Kp] * B16[N][Kp]^T, both operands bf16, K-major, Kp a multiple of 64 (zero padded).
+void gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, float* C, int M, int N, int Kp) {
+    if (M <= 0 || N <= 0 || Kp <= 0 || Kp % BK != 0) throw Error("gemm_bf16: K of the staged operands must be a positive multiple of 64");
+    if (((uintptr_t)a16 | (uintptr_t)b16 | (uintptr_t)C) & 15) throw Error("gemm_bf16: operands must be 16-byte aligned");
     CUtensorMap map_a, map_b;
-    make_map(ctx, &map_a, a16, g.M, Kp, BM);
-    make_map(ctx, &map_b, b16, g.N, Kp, BN);
+    make_map(ctx, &map_a, const_cast<void*>(a16), M, Kp, BM);
+    make_map(ctx, &map_b, const_cast<void*>(b16), N, Kp, BN);
     if (!ctx->gemm_err) {
         ORMI_CUDA(cudaMalloc(&ctx->gemm_err, sizeof(int)));
         ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err, 0, sizeof(int), ctx->stream));
         ORMI_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     }
-    const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
     const int grid = std::min(tiles_m * tiles_n, ctx->num_sms);
-    gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(map_a, map_b, g.C, g.M, g.N, Kp / BK, tiles_m, tiles_n, ctx->gemm_err);
+    gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(map_a, map_b, C, M, N, Kp / BK, tiles_m, tiles_n, ctx->gemm_err);
     ORMI_CUDA(cudaGetLastError());
     ctx->gemm_err_pending = true;
     ctx->counters["gemm_launches"]++;
     ctx->counters["launches"]++;
+}
+
+// dst[row][k] = bf16(src[row * s_row + k * s_k]), rows x Kp bf16 with Kp = K rounded up to 64 (zero padded).
+void cvt_bf16_kmajor(ormi_b200_ctx* ctx, const float* src, long long s_row, long long s_k, int rows, int K, void* dst) {
+    convert(ctx, src, s_row, s_k, rows, K, (K + BK - 1) / BK * BK, (__nv_bfloat16*)dst);
 }
 
 // Called at host-visible boundaries (sync, device -> host copies): a bounded wait that ran out inside the tensor-core

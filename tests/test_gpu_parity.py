@@ -288,3 +288,24 @@ def test_mlp_training_step_bf16_matmuls():
             assert rel(dev.numpy(r), w) <= BF16_TOL
     finally:
         dev.close()
+
+
+def test_mlp_trainer_matches_oracle_over_steps(device):
+    """The repeated-step host loop (ormi_b200.train_step.MLPTrainer): three SGD steps against the oracle."""
+    from ormi_b200.train_step import MLPTrainer
+    B, D, H, lr = 256, 64, 256, 0.1
+    x, t = W.normal(0, (B, D)), W.normal(1, (B, D))
+    w1, b1 = W.kaiming_uniform(2, D, (D, H)), np.zeros(H, np.float32)
+    w2, b2 = W.kaiming_uniform(3, H, (H, D)), np.zeros(D, np.float32)
+    tr = MLPTrainer(device, x, t, w1, b1, w2, b2, lr=lr)
+    params = [w1, b1, w2, b2]
+    for _ in range(3):
+        tr.step()
+        leaves = [G.leaf(p, True) for p in params]
+        loss = W.mlp_loss(G.leaf(x), leaves[0], leaves[1], leaves[2], leaves[3], G.leaf(t))
+        G.compute_gradients(loss)
+        outs, _ = O.port_run([loss] + [W.sgd_update(l, lr) for l in leaves])
+        assert abs(tr.loss() - float(outs[0])) <= 3 * REDUCE_TOL * abs(float(outs[0]))
+        params = [o for o in outs[1:]]
+    for name, want in zip(tr.names, params):
+        assert rel(tr.parameter(name).reshape(want.shape), want) <= 3 * REDUCE_TOL
