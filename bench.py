@@ -332,20 +332,24 @@ def main():
     sm_roots, ln_roots, inputs = build_graphs(G, W, lambda a, rg=False: dev.leaf(a, rg), shard=rank)
     runner = StepRunner(dev, G, [sm_roots, ln_roots])
 
-    grads = None
     if dist is not None:
-        grads = torch.zeros(2 * C, device="cuda")
+        from ormi_b200._lib import lib, check
+        from ormi_b200.train_step import init_comm
+
+        def bcast(payload):
+            obj = [payload]
+            dist.broadcast_object_list(obj, src=0)
+            return obj[0]
+        init_comm(dev, rank, world, bcast)
 
     def step():
         outs = runner.run(keep=dist is not None)
         if dist is not None:
-            # cross-shard combine: dg, db (the last two roots of the layernorm graph) are summed over ranks
-            dg, db = outs[-2], outs[-1]
-            from ormi_b200._lib import lib, check
-            check(lib.ormi_b200_memcpy_d2d(dev.handle, ctypes.c_void_p(grads.data_ptr()), ctypes.c_void_p(dg[0]), C * 4))
-            check(lib.ormi_b200_memcpy_d2d(dev.handle, ctypes.c_void_p(grads.data_ptr() + C * 4), ctypes.c_void_p(db[0]), C * 4))
-            dev.sync()
-            dist.all_reduce(grads)
+            # cross-shard combine: dg, db (the last two roots of the layernorm graph) are summed over the ranks, in
+            # place, by NCCL on the compute stream (no host synchronisation inside a step)
+            bufs = (ctypes.c_void_p * 2)(outs[-2][0], outs[-1][0])
+            counts = (ctypes.c_size_t * 2)(C, C)
+            check(lib.ormi_b200_allreduce_sum_f32(dev.handle, bufs, counts, 2, 0))
             for ptr, nbytes in outs:
                 dev.free(ptr, nbytes)
 
@@ -417,14 +421,6 @@ def main():
             extras["matmul"] = matmul_sweep(dev, torch, G, W)
             extras["mlp_fp32_config3"] = dict(mlp_steps_per_s(dev, torch, W, 8192, 1024, 4096, "fp32", 5),
                                               shape="B=8192, 1024->4096->1024, fp32 FFMA matmuls")
-        else:
-            from ormi_b200.train_step import init_comm
-
-            def bcast(payload):
-                obj = [payload]
-                dist.broadcast_object_list(obj, src=0)
-                return obj[0]
-            init_comm(dev, rank, world, bcast)
         gb = 65536
         extras["mlp_bf16_config4"] = dict(mlp_steps_per_s(dev, torch, W, gb // world, 2048, 8192, "bf16", 10, rank, world, dist, gb),
                                           shape=f"global batch {gb} split over {world} GPU(s), 2048->8192->2048, bf16 tcgen05 matmuls, "
