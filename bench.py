@@ -278,6 +278,20 @@ def run_only(args):
     from ormi_b200 import graph as G, workloads as W
     from ormi_b200.runtime import Device
     dev = Device(0)
+    if args.only in ("gemm_bf16", "gemm_fp32"):
+        # C = A @ B at M = N = K = --rows (default 8192 is too long under a profiler: use --rows 4096)
+        n = args.rows
+        a = dev.leaf(W.normal(0, (n, n), 1 / math.sqrt(n)))
+        b = dev.leaf(W.normal(1, (n, n), 1 / math.sqrt(n)))
+        dev.set_option("matmul", "bf16" if args.only == "gemm_bf16" else "fp32")
+        runner = StepRunner(dev, G, [[G.matmul(a, b)]])
+        for _ in range(args.warmup):
+            runner.run()
+        ms = timed(dev, torch, lambda: runner.run(), args.steps)
+        print(json.dumps({"only": args.only, "n": n, "ms_per_matmul": ms / args.steps,
+                          "tflops_including_conversion": 2.0 * n ** 3 / (ms / args.steps * 1e-3) / 1e12}))
+        dev.close()
+        return
     if args.only == "rowsum":
         a, b, c = (dev.leaf(W.normal(i, (args.rows, C))) for i in range(3))
         roots, nbytes = [W.fused_rowsum(a, b, c)], 3 * args.rows * C * 4 + args.rows * 4
@@ -300,7 +314,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, choices=["softmax", "layernorm", "rowsum"],
+    ap.add_argument("--only", default=None, choices=["softmax", "layernorm", "rowsum", "gemm_bf16", "gemm_fp32"],
                     help="profiling aid: run just this graph --steps times on --rows rows and exit")
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--no-extras", action="store_true", help="skip the matmul sweep and the MLP training steps")

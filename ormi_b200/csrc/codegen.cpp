@@ -248,10 +248,12 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     }
     // Tuning knobs (environment overrides are for experiments only).
     auto env_int = [](const char* name, int dflt) { const char* v = std::getenv(name); return v ? std::atoi(v) : dflt; };
-    // Depth = number of dependent row-sum levels.  Measured on B200 at [16384, 4096]: a shallow kernel (softmax,
-    // depth 2) is fastest with 16 elements per thread and many resident blocks (5.9 TB/s); a deep one (layernorm
-    // forward+backward, depth 4) needs the register budget capped so that two 512-thread blocks share an SM and
-    // overlap their barrier phases (3.2 TB/s against 2.0 TB/s uncapped).
+    // Depth = number of dependent row-sum levels.  Measured on B200 at [16384, 4096] (GB/s of algorithmic bytes):
+    //   depth 4 (layernorm fwd+bwd): 16 elements/thread, registers capped for 2 blocks/SM, grid 2/SM -> 4470;
+    //            uncapped (154 registers, 1 block/SM) -> 2420.  The kernel is as much instruction-issue bound as
+    //            bandwidth bound, so it needs two resident blocks to overlap their barrier phases.
+    //   depth 2 (softmax fwd+bwd):   16 elements/thread, 3 blocks/SM, grid 3/SM -> 6360 (0.97 of the copy bandwidth).
+    //   depth <= 1 (config 1):       uncapped, grid 8/SM -> 4320 on a 46 us kernel.
     int depth = 0;
     {
         std::map<int, int> lvl;
@@ -263,11 +265,10 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
             depth = std::max(depth, lv);
         }
     }
-    const bool deep = depth >= 3;
-    const int target = env_int("ORMI_B200_ROWS_VPT", spec.tune_vpt > 0 ? spec.tune_vpt : ((V == 4) ? (deep ? 8 : 16) : 8));
+    const int target = env_int("ORMI_B200_ROWS_VPT", spec.tune_vpt > 0 ? spec.tune_vpt : ((V == 4) ? 16 : 8));
     const bool hoist = env_int("ORMI_B200_ROWS_HOIST", spec.tune_hoist) != 0;
-    int minb = env_int("ORMI_B200_ROWS_MINB", spec.tune_minblocks > 0 ? spec.tune_minblocks : (deep ? 2 : 0));
-    const int grid_mult = env_int("ORMI_B200_ROWS_GRID", spec.tune_grid > 0 ? spec.tune_grid : (deep ? 2 : 8));
+    int minb = env_int("ORMI_B200_ROWS_MINB", spec.tune_minblocks > 0 ? spec.tune_minblocks : (depth >= 3 ? 2 : (depth == 2 ? 3 : 0)));
+    const int grid_mult = env_int("ORMI_B200_ROWS_GRID", spec.tune_grid > 0 ? spec.tune_grid : (depth >= 3 ? 2 : (depth == 2 ? 3 : 8)));
     int T = std::min(1024, std::max(32, ceil_pow2((C + target - 1) / target)));
     int64_t VPT = (C + T - 1) / T;
     VPT = (VPT + V - 1) / V * V;
@@ -382,11 +383,22 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         bool any = false;
         for (const KNode& kn : spec.nodes) if (!rowv(&kn) && level[kn.node] == lv) any = true;
         if (any) {
+            // A division of a per-element value by a per-row (or scalar) divisor becomes one correctly rounded
+            // reciprocal per row and a multiplication per element: at most ~2 ulp (2.4e-7) away from the IEEE
+            // quotient, inside the 1e-6 pointwise tolerance, and about ten instructions per element cheaper —
+            // the deep row kernels are instruction-issue bound, not only bandwidth bound.
+            for (const KNode& kn : spec.nodes) {
+                if (rowv(&kn) || level[kn.node] != lv || kn.op != ORMI_OP_DIV || is_elem(kn.operands[1])) continue;
+                s << "        const float rcp" << kn.node << " = __frcp_rn(" << ref(kn.operands[1], "0") << ");\n";
+            }
             s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) {\n";
             for (const KNode& kn : spec.nodes) {
                 if (rowv(&kn) || level[kn.node] != lv) continue;
                 std::string a = ref(kn.operands[0], "j"), b = kn.operands.size() > 1 ? ref(kn.operands[1], "j") : "";
-                s << "            v" << kn.node << "[j] = " << op_expr(kn.op, a, b) << ";\n";
+                if (kn.op == ORMI_OP_DIV && !is_elem(kn.operands[1]))
+                    s << "            v" << kn.node << "[j] = __fmul_rn(" << a << ", rcp" << kn.node << ");\n";
+                else
+                    s << "            v" << kn.node << "[j] = " << op_expr(kn.op, a, b) << ";\n";
             }
             s << "        }\n";
         }

@@ -29,6 +29,7 @@ static inline float __fadd_rn(float a, float b) { return a + b; }
 static inline float __fsub_rn(float a, float b) { return a - b; }
 static inline float __fmul_rn(float a, float b) { return a * b; }
 static inline float __fdiv_rn(float a, float b) { return a / b; }
+static inline float __frcp_rn(float a) { return 1.0f / a; }
 static inline void __syncthreads() { pthread_barrier_wait(&emul_barrier); }
 static inline float __shfl_xor_sync(unsigned, float v, int lane_mask) {
     unsigned t = threadIdx.x;
