@@ -46,6 +46,44 @@ __device__ __forceinline__ float ormi_warp_sum(float v, int width) {
     for (int o = width >> 1; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+#ifndef ORMI_EMULATE
+// Rows staged in shared memory by bulk asynchronous copies (the TMA engine), completion counted on an mbarrier.
+#define ORMI_DYN_SMEM(name) extern __shared__ __align__(1024) unsigned char name[]
+__device__ __forceinline__ unsigned ormi_smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ormi_mbar_init(unsigned long long* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ormi_smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void ormi_mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void ormi_async_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void ormi_mbar_expect(unsigned long long* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(ormi_smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void ormi_bulk_load(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(ormi_smem_addr(dst)), "l"(src), "r"(bytes), "r"(ormi_smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ unsigned long long ormi_global_ns() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+// Bounded wait (about one second): false means the copy never arrived; the caller raises the error word and leaves.
+__device__ __forceinline__ bool ormi_mbar_wait(unsigned long long* bar, unsigned parity) {
+    const unsigned addr = ormi_smem_addr(bar);
+    unsigned long long t0 = 0;
+    for (unsigned spin = 0;; ++spin) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((spin & 255u) == 255u) {
+            const unsigned long long now = ormi_global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 1000000000ull) return false;
+        }
+    }
+}
+__device__ __forceinline__ void ormi_drain() { const unsigned long long t0 = ormi_global_ns(); while (ormi_global_ns() - t0 < 200000ull) { } }
+#endif
 #endif
 )PRE";
 }
@@ -281,6 +319,30 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     if (grid < 1) grid = 1;
     if (!hoist) for (auto& I : li) if (I.elem && !I.row_var) I.row_var = true;   // re-read row-invariant vectors every row (L1/L2 hits)
 
+    // Staging: the row-variant operands of the NEXT rows are fetched into a shared-memory ring by bulk asynchronous
+    // copies while the current row is being reduced, so global-load latency no longer sits between the barrier phases.
+    std::vector<size_t> staged;
+    int stages = 0;
+    {
+        const int want = env_int("ORMI_B200_ROWS_STAGE", spec.tune_stage >= 0 ? spec.tune_stage : (depth >= 3 ? 1 : 0));
+        bool can = want && V == 4 && G == 1 && !col_pred;
+        for (size_t l = 0; can && l < spec.loads.size(); ++l) {
+            bool varies = false;
+            for (int d = 0; d < k; ++d) if (spec.loads[l].st[d] != 0) varies = true;
+            if (!li[l].elem || !varies) continue;
+            if (li[l].sc != 1 || !li[l].row_collapsed || li[l].sr % 4 != 0) can = false;
+            else staged.push_back(l);
+        }
+        if (can && !staged.empty()) {
+            const int64_t per_stage = (int64_t)staged.size() * C * 4;
+            const int64_t budget = (int64_t)(minb >= 3 ? 70 : (minb == 2 ? 100 : 200)) * 1024;
+            stages = (int)std::min<int64_t>(env_int("ORMI_B200_ROWS_NSTAGE", 4), budget / per_stage);
+            if (stages < 2) stages = 0;
+        }
+        if (!stages) staged.clear();
+    }
+    auto staged_slot = [&](size_t l) { for (size_t i = 0; i < staged.size(); ++i) if (staged[i] == l) return (int)i; return -1; };
+
     // levels
     std::map<int, int> level;       // node -> level
     std::map<int, const KNode*> by_id;
@@ -309,6 +371,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     s << "extern \"C\" __global__ void __launch_bounds__(" << NT << (minb > 0 ? ", " + std::to_string(minb) : "") << ") " << name << "(";
     for (size_t l = 0; l < spec.loads.size(); ++l) s << (l ? ", " : "") << "const float* __restrict__ in" << l;
     for (size_t o = 0; o < spec.outputs.size(); ++o) s << ((spec.loads.size() + o) ? ", " : "") << "float* __restrict__ out" << o;
+    if (stages) s << ", int* __restrict__ err";
     s << ") {\n";
     s << "    // rows=" << R << " cols=" << C << " threads/row=" << T << " rows/block=" << G << " elems/thread=" << VPT << " vec=" << V << "\n";
     s << "    const int tid = threadIdx.x % " << T << ";\n    const int grp = threadIdx.x / " << T << ";\n";
@@ -341,8 +404,26 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         if (spec.outputs[o].kind == KOutput::COLSUM) { s << "    float cacc" << o << "[" << VPT << "];\n    #pragma unroll\n    for (int j = 0; j < " << VPT << "; ++j) cacc" << o << "[j] = 0.0f;\n"; }
         if (spec.outputs[o].kind == KOutput::GLOBALSUM) s << "    float gacc" << o << " = 0.0f;\n";
     }
-    s << "    for (int rb = blockIdx.x * " << G << "; rb < " << R << "; rb += gridDim.x * " << G << ") {\n";
-    s << "        const int r = rb + grp;\n";
+    if (stages) {
+        s << "    ORMI_DYN_SMEM(dsm);\n    float* const ring = reinterpret_cast<float*>(dsm);\n";
+        s << "    __shared__ unsigned long long fullbar[" << stages << "];\n";
+        s << "    const int n_mine = (" << R << " - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;\n";
+        s << "    auto issue = [&](int i) {\n        const int rr = blockIdx.x + i * gridDim.x;\n        const int st = i % " << stages << ";\n";
+        s << "        ormi_mbar_expect(&fullbar[st], " << staged.size() * C * 4 << "u);\n";
+        for (size_t i = 0; i < staged.size(); ++i)
+            s << "        ormi_bulk_load(ring + (st * " << staged.size() << " + " << i << ") * " << C << ", in" << staged[i] << " + (long long)rr * " << li[staged[i]].sr
+              << ", " << C * 4 << "u, &fullbar[st]);\n";
+        s << "    };\n";
+        s << "    if (threadIdx.x == 0) {\n        for (int st = 0; st < " << stages << "; ++st) ormi_mbar_init(&fullbar[st], 1);\n        ormi_mbar_fence_init();\n    }\n";
+        s << "    __syncthreads();\n";
+        s << "    if (threadIdx.x == 0) for (int i = 0; i < " << stages - 1 << " && i < n_mine; ++i) issue(i);\n";
+        s << "    for (int it = 0; it < n_mine; ++it) {\n        const int r = blockIdx.x + it * gridDim.x;\n";
+        s << "        const int stg = it % " << stages << ";\n";
+        s << "        const bool arrived = ormi_mbar_wait(&fullbar[stg], (unsigned)(it / " << stages << ") & 1u);\n";
+    } else {
+        s << "    for (int rb = blockIdx.x * " << G << "; rb < " << R << "; rb += gridDim.x * " << G << ") {\n";
+        s << "        const int r = rb + grp;\n";
+    }
     if (row_pred) s << "        const bool rok = r < " << R << ";\n";
     if (need_row_coords) {
         s << "        int rrem = " << (row_pred ? "rok ? r : 0" : "r") << ";\n";
@@ -361,8 +442,18 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
             for (int d = 0; d < k; ++d) if (spec.loads[l].st[d] != 0) s << " + rc" << d << " * " << spec.loads[l].st[d];
             s << ";\n";
         }
-        if (li[l].elem) emit_array_load(l, ro, "        ", row_pred);
+        if (li[l].elem && staged_slot(l) >= 0) {
+            s << "        float L" << l << "[" << VPT << "];\n        #pragma unroll\n        for (int q = 0; q < " << NV << "; ++q) {\n";
+            s << "            const float4 t = *reinterpret_cast<const float4*>(ring + (stg * " << staged.size() << " + " << staged_slot(l) << ") * " << C << " + " << col_of("q", "0") << ");\n";
+            s << "            L" << l << "[4 * q] = t.x; L" << l << "[4 * q + 1] = t.y; L" << l << "[4 * q + 2] = t.z; L" << l << "[4 * q + 3] = t.w;\n        }\n";
+        }
+        else if (li[l].elem) emit_array_load(l, ro, "        ", row_pred);
         else s << "        const float L" << l << " = " << (row_pred ? "rok ? " : "") << "in" << l << "[" << ro << "]" << (row_pred ? " : 0.0f" : "") << ";\n";
+    }
+    if (stages) {
+        // every thread now holds its part of the row: the stage of the previous row can be refilled
+        s << "        if (__syncthreads_or(!arrived)) {\n            if (threadIdx.x == 0) atomicExch(err, 101);\n            ormi_drain();\n            break;\n        }\n";
+        s << "        if (threadIdx.x == 0 && it + " << stages - 1 << " < n_mine) { ormi_async_fence(); issue(it + " << stages - 1 << "); }\n";
     }
     for (const KNode& kn : spec.nodes) if (!rowv(&kn)) s << "        float v" << kn.node << "[" << VPT << "];\n";
 
@@ -489,9 +580,11 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     out.step.source = s.str();
     out.step.grid = grid;
     out.step.block = NT;
+    out.step.dyn_smem = stages ? (int)(stages * (int64_t)staged.size() * C * 4) : 0;
+    out.step.err_arg = stages > 0;
     out.cols = C;
     std::ostringstream w;
-    w << "rows[R=" << R << ",C=" << C << ",T=" << T << ",G=" << G << ",VPT=" << VPT << ",V=" << V << ",levels=" << max_level << "] nodes=" << spec.nodes.size()
+    w << "rows[R=" << R << ",C=" << C << ",T=" << T << ",G=" << G << ",VPT=" << VPT << ",V=" << V << ",levels=" << max_level << ",stages=" << stages << "] nodes=" << spec.nodes.size()
       << " loads=" << spec.loads.size() << " outs=";
     for (auto& o : spec.outputs) w << (o.kind == KOutput::FULL ? "F" : o.kind == KOutput::ROW ? "R" : o.kind == KOutput::COLSUM ? "C" : "G");
     out.step.what = w.str();

@@ -73,7 +73,8 @@ struct ormi_b200_ctx {
     void* stage[2] = {nullptr, nullptr};
     size_t stage_bytes[2] = {0, 0};
     int* gemm_err = nullptr;          // device word: non-zero when a bounded wait inside the tensor-core GEMM ran out
-    bool gemm_err_pending = false;    // a tensor-core GEMM was launched since the word was last read
+    bool gemm_err_pending = false;    // a kernel with bounded waits was launched since the word was last read
+    bool gemm_attr_set = false;
 
     std::map<std::string, int64_t> counters;
     void* nccl = nullptr;   // opaque: collective state (nccl.cpp)
@@ -88,7 +89,8 @@ void pool_free(ormi_b200_ctx* ctx, void* ptr, size_t bytes);
 std::vector<char> compile_cubin(const std::string& source, std::string* log = nullptr);
 
 CompiledKernel* get_kernel(ormi_b200_ctx* ctx, const KernelStep& k);
-void launch_kernel(ormi_b200_ctx* ctx, CompiledKernel* k, int grid, int block, std::vector<void*>& pointer_args);
+void launch_kernel(ormi_b200_ctx* ctx, CompiledKernel* k, int grid, int block, std::vector<void*>& pointer_args, int dyn_smem = 0);
+int* device_error_word(ormi_b200_ctx* ctx);
 
 // GEMM launchers (gemm_ffma.cu, gemm_tcgen05.cu)
 struct GemmArgs {

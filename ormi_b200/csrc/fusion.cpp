@@ -630,6 +630,12 @@ Plan Scheduler::run(const int* roots, int n_roots) {
                 finals.push_back({tmp, (int)oi});
             }
         }
+        if (gk.step.err_arg) {
+            int eb = -1;
+            for (size_t b = 0; b < plan.buffers.size(); ++b) if (plan.buffers[b].kind == BufKind::ErrorWord) eb = (int)b;
+            if (eb < 0) { plan.buffers.push_back(PlanBuffer{BufKind::ErrorWord, -1, 4}); eb = (int)plan.buffers.size() - 1; }
+            stp.k.args.push_back(eb);
+        }
         plan.steps.push_back(stp);
         for (auto& f : finals) {
             const KOutput& o = ks.outputs[f.second];
@@ -683,7 +689,7 @@ std::string plan_to_json(const Plan& plan) {
     o << "{\"error\": \"" << json_escape(plan.error) << "\", \"buffers\": [";
     for (size_t i = 0; i < plan.buffers.size(); ++i) {
         const auto& b = plan.buffers[i];
-        o << (i ? ", " : "") << "{\"kind\": \"" << (b.kind == BufKind::External ? "external" : b.kind == BufKind::NodeOut ? "node" : "temp")
+        o << (i ? ", " : "") << "{\"kind\": \"" << (b.kind == BufKind::External ? "external" : b.kind == BufKind::NodeOut ? "node" : b.kind == BufKind::ErrorWord ? "error" : "temp")
           << "\", \"node\": " << b.node << ", \"bytes\": " << b.bytes << "}";
     }
     o << "], \"steps\": [";
@@ -691,7 +697,7 @@ std::string plan_to_json(const Plan& plan) {
         const auto& s = plan.steps[i];
         o << (i ? ", " : "");
         if (s.type == Step::Kernel) {
-            o << "{\"type\": \"kernel\", \"name\": \"" << s.k.name << "\", \"grid\": " << s.k.grid << ", \"block\": " << s.k.block
+            o << "{\"type\": \"kernel\", \"name\": \"" << s.k.name << "\", \"grid\": " << s.k.grid << ", \"block\": " << s.k.block << ", \"dyn_smem\": " << s.k.dyn_smem
               << ", \"what\": \"" << json_escape(s.k.what) << "\", \"bytes_read\": " << s.k.bytes_read << ", \"bytes_written\": " << s.k.bytes_written
               << ", \"args\": [";
             for (size_t a = 0; a < s.k.args.size(); ++a) o << (a ? ", " : "") << s.k.args[a];

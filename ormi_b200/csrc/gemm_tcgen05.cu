@@ -335,10 +335,10 @@ void gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, floa
     CUtensorMap map_a, map_b;
     make_map(ctx, &map_a, const_cast<void*>(a16), M, Kp, BM);
     make_map(ctx, &map_b, const_cast<void*>(b16), N, Kp, BN);
-    if (!ctx->gemm_err) {
-        ORMI_CUDA(cudaMalloc(&ctx->gemm_err, sizeof(int)));
-        ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err, 0, sizeof(int), ctx->stream));
+    device_error_word(ctx);
+    if (!ctx->gemm_attr_set) {
         ORMI_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        ctx->gemm_attr_set = true;
     }
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
     const int grid = std::min(tiles_m * tiles_n, ctx->num_sms);
@@ -364,7 +364,8 @@ void check_gemm_error(ormi_b200_ctx* ctx) {
     ctx->gemm_err_pending = false;
     if (code != 0) {
         ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err, 0, sizeof(int), ctx->stream));
-        throw Error("tensor-core GEMM: a pipeline wait ran out (code " + std::to_string(code) + ": 1 producer, 2 accumulator, 3 operands, 4 epilogue)");
+        throw Error("a bounded device-side wait ran out (code " + std::to_string(code) +
+                    ": tensor-core GEMM 1 producer, 2 accumulator, 3 operands, 4 epilogue; 101 staged row kernel)");
     }
 }
 

@@ -47,6 +47,7 @@ struct KernelSpec {
     int tune_hoist = 1;
     int tune_minblocks = 0;
     int tune_grid = 0;
+    int tune_stage = -1;        // stage row operands through shared memory with bulk async copies (-1 = automatic)
 };
 
 struct GeneratedKernel {

@@ -11,7 +11,7 @@
 
 namespace ormi_b200 {
 
-enum class BufKind { External, NodeOut, Temp };
+enum class BufKind { External, NodeOut, Temp, ErrorWord /* the context's device error word */ };
 
 struct PlanBuffer {
     BufKind kind;
@@ -24,6 +24,8 @@ struct KernelStep {
     std::string source;      // CUDA C (NVRTC)
     std::string key;         // cache key (hash of the source)
     int grid = 1, block = 1;
+    int dyn_smem = 0;        // dynamic shared memory per block (bytes)
+    bool err_arg = false;    // the kernel takes the device error word as its last argument
     std::vector<int> args;   // plan buffer ids, in kernel-argument order (every argument is a pointer)
     std::string what;        // human-readable summary (template, domain, outputs)
     int64_t bytes_read = 0, bytes_written = 0;   // algorithmic traffic of the launch

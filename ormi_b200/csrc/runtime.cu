@@ -113,17 +113,29 @@ CompiledKernel* get_kernel(ormi_b200_ctx* ctx, const KernelStep& k) {
     CompiledKernel ck;
     ctx->drv.check(ctx->drv.ModuleLoadData(&ck.module, cubin.data()), "cuModuleLoadData");
     ctx->drv.check(ctx->drv.ModuleGetFunction(&ck.func, ck.module, k.name.c_str()), "cuModuleGetFunction");
+    if (k.dyn_smem > 48 * 1024)
+        ctx->drv.check(ctx->drv.FuncSetAttribute(ck.func, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, k.dyn_smem), "cuFuncSetAttribute");
     ctx->counters["kernels_compiled"]++;
     auto res = ctx->kernel_cache.emplace(k.key + ":" + k.name, ck);
     return &res.first->second;
 }
 
-void launch_kernel(ormi_b200_ctx* ctx, CompiledKernel* k, int grid, int block, std::vector<void*>& pointer_args) {
+void launch_kernel(ormi_b200_ctx* ctx, CompiledKernel* k, int grid, int block, std::vector<void*>& pointer_args, int dyn_smem) {
     std::vector<void*> argv(pointer_args.size());
     for (size_t i = 0; i < pointer_args.size(); ++i) argv[i] = &pointer_args[i];
-    ctx->drv.check(ctx->drv.LaunchKernel(k->func, (unsigned)grid, 1, 1, (unsigned)block, 1, 1, 0, (CUstream)ctx->stream, argv.data(), nullptr),
+    ctx->drv.check(ctx->drv.LaunchKernel(k->func, (unsigned)grid, 1, 1, (unsigned)block, 1, 1, (unsigned)dyn_smem, (CUstream)ctx->stream, argv.data(), nullptr),
                    "cuLaunchKernel");
     ctx->counters["launches"]++;
+}
+
+// The device word into which kernels with bounded waits (staged row kernels, the tensor-core GEMM) report a wait
+// that ran out.  Read back at host-visible boundaries by check_gemm_error.
+int* device_error_word(ormi_b200_ctx* ctx) {
+    if (!ctx->gemm_err) {
+        ORMI_CUDA(cudaMalloc(&ctx->gemm_err, sizeof(int)));
+        ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err, 0, sizeof(int), ctx->stream));
+    }
+    return ctx->gemm_err;
 }
 
 // ------------------------------------------------------------------------------------------------ realize
@@ -173,6 +185,9 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
             if (pb.kind == BufKind::External) {
                 bufs[b] = nodes[pb.node].data;
                 if (!bufs[b]) throw Error("internal: realized input without a buffer");
+            } else if (pb.kind == BufKind::ErrorWord) {
+                bufs[b] = device_error_word(ctx);
+                handed[b] = true;      // not a pool block
             } else {
                 if (preassigned && pb.kind == BufKind::NodeOut)
                     for (auto& pr : *preassigned) if (pr.first == pb.node) { bufs[b] = pr.second; handed[b] = true; }
@@ -184,7 +199,8 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
             if (st.type == Step::Kernel) {
                 std::vector<void*> args;
                 for (int a : st.k.args) args.push_back(bufs[a]);
-                launch_kernel(ctx, cp->kernels[s], st.k.grid, st.k.block, args);
+                launch_kernel(ctx, cp->kernels[s], st.k.grid, st.k.block, args, st.k.dyn_smem);
+                if (st.k.err_arg) ctx->gemm_err_pending = true;
             } else {
                 GemmArgs g;
                 g.A = (const float*)bufs[st.g.a]; g.B = (const float*)bufs[st.g.b]; g.C = (float*)bufs[st.g.c];

@@ -40,6 +40,28 @@ static inline float __shfl_xor_sync(unsigned, float v, int lane_mask) {
     return r;
 }
 
+// ---- the staged (bulk asynchronous copy) row kernels: the copy happens at once, the barrier wait is a block barrier
+#include <cstring>
+#define ORMI_DYN_SMEM(name) static unsigned char name[512 * 1024]
+static int emul_or_flag;
+static inline int __syncthreads_or(int pred) {
+    if (pred) __atomic_store_n(&emul_or_flag, 1, __ATOMIC_SEQ_CST);
+    pthread_barrier_wait(&emul_barrier);
+    int r = __atomic_load_n(&emul_or_flag, __ATOMIC_SEQ_CST);
+    pthread_barrier_wait(&emul_barrier);
+    if (threadIdx.x == 0) __atomic_store_n(&emul_or_flag, 0, __ATOMIC_SEQ_CST);
+    pthread_barrier_wait(&emul_barrier);
+    return r;
+}
+static inline int atomicExch(int* p, int v) { return __atomic_exchange_n(p, v, __ATOMIC_SEQ_CST); }
+static inline void ormi_mbar_init(unsigned long long*, unsigned) {}
+static inline void ormi_mbar_fence_init() {}
+static inline void ormi_async_fence() {}
+static inline void ormi_mbar_expect(unsigned long long*, unsigned) {}
+static inline void ormi_bulk_load(void* dst, const void* src, unsigned bytes, unsigned long long*) { std::memcpy(dst, src, bytes); }
+static inline bool ormi_mbar_wait(unsigned long long*, unsigned) { pthread_barrier_wait(&emul_barrier); return true; }
+static inline void ormi_drain() {}
+
 typedef void (*emul_kernel_t)(void*, void*, void*, void*, void*, void*, void*, void*, void*, void*, void*, void*,
                               void*, void*, void*, void*, void*, void*, void*, void*, void*, void*, void*, void*);
 

@@ -20,7 +20,7 @@ _CACHE = os.path.join(tempfile.gettempdir(), "ormi_b200_emul")
 
 def _compile(sources: list[tuple[str, str]]):
     os.makedirs(_CACHE, exist_ok=True)
-    text = '#include "cuda_emul.h"\n' + "\n".join(src for _, src in sources)
+    text = '#define ORMI_EMULATE 1\n#include "cuda_emul.h"\n' + "\n".join(src for _, src in sources)
     tag = hashlib.sha1(text.encode()).hexdigest()[:16]
     so = os.path.join(_CACHE, f"k_{tag}.so")
     if not os.path.exists(so):
@@ -41,7 +41,9 @@ def run_plan(plan: dict) -> dict:
     order = plan["order"]
     bufs = []
     for b in plan["buffers"]:
-        if b["kind"] == "external":
+        if b["kind"] == "error":
+            bufs.append(np.zeros(1, dtype=np.float32))     # the device error word (an int, never set here)
+        elif b["kind"] == "external":
             host = order[b["node"]].data.host
             bufs.append(np.ascontiguousarray(host, dtype=np.float32).reshape(-1))
         else:
