@@ -286,12 +286,12 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     }
     // Tuning knobs (environment overrides are for experiments only).
     auto env_int = [](const char* name, int dflt) { const char* v = std::getenv(name); return v ? std::atoi(v) : dflt; };
-    // Depth = number of dependent row-sum levels.  Measured on B200 at [16384, 4096] (GB/s of algorithmic bytes):
-    //   depth 4 (layernorm fwd+bwd): 16 elements/thread, registers capped for 2 blocks/SM, grid 2/SM -> 4470;
-    //            uncapped (154 registers, 1 block/SM) -> 2420.  The kernel is as much instruction-issue bound as
-    //            bandwidth bound, so it needs two resident blocks to overlap their barrier phases.
-    //   depth 2 (softmax fwd+bwd):   16 elements/thread, 3 blocks/SM, grid 3/SM -> 6360 (0.97 of the copy bandwidth).
-    //   depth <= 1 (config 1):       uncapped, grid 8/SM -> 4320 on a 46 us kernel.
+    // Depth = number of dependent row-sum levels.  Defaults measured on B200 at [16384, 4096] (GB/s of algorithmic
+    // bytes, measured copy bandwidth 6537):
+    //   depth 4 (layernorm fwd+bwd): 16 elements/thread, registers capped for 2 blocks/SM, grid 2/SM, next rows
+    //            staged in shared memory (2 stages) -> 5190; same without staging -> 4470; uncapped registers -> 2420.
+    //   depth 2 (softmax fwd+bwd):   16 elements/thread, 3 blocks/SM, grid 3/SM, direct loads -> 6370; staged -> 5800.
+    //   depth <= 1 (config 1, a 46 us kernel): 8 elements/thread, 2 blocks/SM, staged -> 4570; direct -> 4320.
     int depth = 0;
     {
         std::map<int, int> lvl;
@@ -303,10 +303,10 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
             depth = std::max(depth, lv);
         }
     }
-    const int target = env_int("ORMI_B200_ROWS_VPT", spec.tune_vpt > 0 ? spec.tune_vpt : ((V == 4) ? 16 : 8));
+    const int target = env_int("ORMI_B200_ROWS_VPT", spec.tune_vpt > 0 ? spec.tune_vpt : ((V == 4 && depth >= 2) ? 16 : 8));
     const bool hoist = env_int("ORMI_B200_ROWS_HOIST", spec.tune_hoist) != 0;
-    int minb = env_int("ORMI_B200_ROWS_MINB", spec.tune_minblocks > 0 ? spec.tune_minblocks : (depth >= 3 ? 2 : (depth == 2 ? 3 : 0)));
-    const int grid_mult = env_int("ORMI_B200_ROWS_GRID", spec.tune_grid > 0 ? spec.tune_grid : (depth >= 3 ? 2 : (depth == 2 ? 3 : 8)));
+    int minb = env_int("ORMI_B200_ROWS_MINB", spec.tune_minblocks > 0 ? spec.tune_minblocks : (depth == 2 ? 3 : 2));
+    const int grid_mult = env_int("ORMI_B200_ROWS_GRID", spec.tune_grid > 0 ? spec.tune_grid : (depth == 2 ? 3 : 2));
     int T = std::min(1024, std::max(32, ceil_pow2((C + target - 1) / target)));
     int64_t VPT = (C + T - 1) / T;
     VPT = (VPT + V - 1) / V * V;
@@ -324,7 +324,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     std::vector<size_t> staged;
     int stages = 0;
     {
-        const int want = env_int("ORMI_B200_ROWS_STAGE", spec.tune_stage >= 0 ? spec.tune_stage : (depth >= 3 ? 1 : 0));
+        const int want = env_int("ORMI_B200_ROWS_STAGE", spec.tune_stage >= 0 ? spec.tune_stage : (depth == 2 ? 0 : 1));
         bool can = want && V == 4 && G == 1 && !col_pred;
         for (size_t l = 0; can && l < spec.loads.size(); ++l) {
             bool varies = false;
@@ -336,7 +336,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         if (can && !staged.empty()) {
             const int64_t per_stage = (int64_t)staged.size() * C * 4;
             const int64_t budget = (int64_t)(minb >= 3 ? 70 : (minb == 2 ? 100 : 200)) * 1024;
-            stages = (int)std::min<int64_t>(env_int("ORMI_B200_ROWS_NSTAGE", 4), budget / per_stage);
+            stages = (int)std::min<int64_t>(env_int("ORMI_B200_ROWS_NSTAGE", 2), budget / per_stage);
             if (stages < 2) stages = 0;
         }
         if (!stages) staged.clear();

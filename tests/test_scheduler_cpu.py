@@ -42,7 +42,7 @@ def test_fused_rowsum_is_one_kernel():
     assert kinds(plan) == ["rows"]
     step = plan["steps"][0]
     assert step["bytes_read"] == 3 * 8 * 4096 * 4 + 3 * 4      # a, b, c once each, plus the three rank-0 constants
-    assert "T=256" in step["what"] and "V=4" in step["what"]
+    assert "V=4" in step["what"] and "stages=2" in step["what"]      # 128-bit accesses, next rows staged in shared memory
 
 
 def test_softmax_forward_backward_is_one_kernel():
