@@ -21,6 +21,8 @@ namespace ormi_b200 {
 void set_last_error(const std::string& msg) { g_last_error = msg; }
 void gemm_dispatch(ormi_b200_ctx* ctx, const GemmArgs& g) {
     if (ctx->matmul_mode == MatmulMode::BF16) gemm_bf16(ctx, g);
+    else if (ctx->matmul_mode == MatmulMode::TF32) gemm_tf32(ctx, g, 1);
+    else if (ctx->matmul_mode == MatmulMode::TF32X3) gemm_tf32(ctx, g, 3);
     else gemm_ffma(ctx, g);
 }
 }  // namespace ormi_b200
@@ -273,6 +275,8 @@ int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value)
         if (k == "matmul") {
             if (v == "fp32") ctx->matmul_mode = MatmulMode::FP32;
             else if (v == "bf16") ctx->matmul_mode = MatmulMode::BF16;
+            else if (v == "tf32") ctx->matmul_mode = MatmulMode::TF32;
+            else if (v == "3xtf32") ctx->matmul_mode = MatmulMode::TF32X3;
             else throw Error("unknown matmul mode: " + v);
         } else if (k == "fusion") {
             if (v == "on") ctx->fusion = true; else if (v == "off") ctx->fusion = false; else throw Error("fusion must be on or off");

@@ -1,4 +1,4 @@
-// bf16 tensor-core GEMM for sm_100a: tcgen05.mma with TMEM accumulators, operands staged by TMA.
+// Tensor-core GEMM for sm_100a (bf16, tf32 and 3xTF32 operands): tcgen05.mma with TMEM accumulators, operands staged by TMA.
 //
 // Opt-in matmul arithmetic ("matmul" = "bf16") behind ormi::cuda::matmul
 // (ormi-core/csrc/backend/cuda/kernels/blas/matmul.cu:19-112, which calls cublasSgemmBatched): fp32 operands
@@ -89,13 +89,21 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     return d;
 }
 
-// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, N = 256, M = 128.
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// Instruction descriptor: D fp32 (bits 4-5 = 1), A and B format (bits 7-9, 10-12: 1 = bf16, 2 = tf32), both K-major,
+// N = 256 (bits 17-22 = N/8), M = 128 (bits 24-28 = M/16).
+__host__ __device__ constexpr uint32_t idesc(uint32_t fmt) { return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24); }
 
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(IDESC), "r"(accumulate) : "memory");
+// One MMA covers 32 bytes of K per operand row: 16 bf16 (kind::f16) or 8 tf32 (kind::tf32).
+template <bool TF32>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+    if (TF32)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc(2)), "r"(accumulate) : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc(1)), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -128,8 +136,11 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     nb = in_g / gsz;
 }
 
+// TF32 = false: operands are bf16, a stage row holds 64 elements.  TF32 = true: operands are fp32 words already rounded
+// to tf32, a stage row holds 32 elements.  Both are 128 bytes per row, so ring, swizzle and descriptors are the same.
+template <bool TF32>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  float* __restrict__ C, int M, int N, int num_kb, int tiles_m, int tiles_n, int* err) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;       // swizzled tiles need 1024-byte alignment
@@ -172,8 +183,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     ok = mbar_wait(empty_bar(s), phase ^ 1u, abort_flag, err, 1);
                     if (!ok) break;
                     mbar_expect_tx(full_bar(s), STAGE_BYTES);
-                    tma_load_2d(base + s * STAGE_BYTES, &map_a, full_bar(s), kb * BK, mb * BM);
-                    tma_load_2d(base + s * STAGE_BYTES + A_STAGE_BYTES, &map_b, full_bar(s), kb * BK, nb * BN);
+                    tma_load_2d(base + s * STAGE_BYTES, &map_a, full_bar(s), kb * (TF32 ? BK / 2 : BK), mb * BM);
+                    tma_load_2d(base + s * STAGE_BYTES + A_STAGE_BYTES, &map_b, full_bar(s), kb * (TF32 ? BK / 2 : BK), nb * BN);
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
@@ -199,7 +210,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const uint64_t db = umma_desc_sw128(base + s * STAGE_BYTES + A_STAGE_BYTES);
                     #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)     // 32 bytes further along K inside the swizzle atom
-                        umma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), (kb > 0 || k > 0) ? 1u : 0u);
+                        umma<TF32>(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), (kb > 0 || k > 0) ? 1u : 0u);
                     umma_commit(empty_bar(s));                // frees the stage once these MMAs have read it
                     if (++s == STAGES) { s = 0; phase ^= 1u; }
                 }
@@ -284,6 +295,54 @@ cvt_kmajor(const float* __restrict__ src, long long s_row, long long s_k, int ro
     }
 }
 
+// tf32 staging: dst is rows x ld fp32 words.  PARTS = 1: dst[r][k] = tf32(x).  PARTS = 3 (the "3xTF32" split):
+// hi = tf32(x), lo = tf32(x - hi); an A operand stores (hi, hi, lo) and a B operand (hi, lo, hi) at k, Kp + k, 2 Kp + k, so
+// that one GEMM over 3 Kp columns adds up  A_hi B_hi + A_hi B_lo + A_lo B_hi  — fp32 products to about 2^-22.
+__device__ __forceinline__ float to_tf32(float x) { uint32_t r; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x)); return __uint_as_float(r); }
+
+template <bool SRC_K_CONTIG>
+__global__ void __launch_bounds__(256)
+cvt_kmajor_tf32(const float* __restrict__ src, long long s_row, long long s_k, int rows, int K, int Kp, float* __restrict__ dst,
+                int parts, int is_b) {
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
+    #pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (SRC_K_CONTIG) {
+            const int r = r0 + ty + 8 * j, k = k0 + tx;
+            tile[ty + 8 * j][tx] = (r < rows && k < K) ? src[r * s_row + k * s_k] : 0.0f;
+        } else {
+            const int r = r0 + tx, k = k0 + ty + 8 * j;
+            tile[tx][ty + 8 * j] = (r < rows && k < K) ? src[r * s_row + k * s_k] : 0.0f;
+        }
+    }
+    __syncthreads();
+    const size_t ld = (size_t)Kp * parts;
+    #pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int r = r0 + ty + 8 * j, k = k0 + tx;
+        if (r >= rows || k >= Kp) continue;
+        const float x = tile[ty + 8 * j][tx];
+        const float hi = to_tf32(x);
+        float* row = dst + (size_t)r * ld;
+        row[k] = hi;
+        if (parts == 3) {
+            const float lo = to_tf32(x - hi);
+            row[Kp + k] = is_b ? lo : hi;
+            row[2 * Kp + k] = is_b ? hi : lo;
+        }
+    }
+}
+
+void convert_tf32(ormi_b200_ctx* ctx, const float* src, long long s_row, long long s_k, int rows, int K, int Kp, float* dst, int parts, int is_b) {
+    dim3 grid((Kp + 31) / 32, (rows + 31) / 32);
+    if (s_k == 1) cvt_kmajor_tf32<true><<<grid, 256, 0, ctx->stream>>>(src, s_row, s_k, rows, K, Kp, dst, parts, is_b);
+    else cvt_kmajor_tf32<false><<<grid, 256, 0, ctx->stream>>>(src, s_row, s_k, rows, K, Kp, dst, parts, is_b);
+    ORMI_CUDA(cudaGetLastError());
+    ctx->counters["launches"]++;
+}
+
 void convert(ormi_b200_ctx* ctx, const float* src, long long s_row, long long s_k, int rows, int K, int Kp, __nv_bfloat16* dst) {
     dim3 grid((Kp + 31) / 32, (rows + 31) / 32);
     if (s_k == 1) cvt_kmajor<true><<<grid, 256, 0, ctx->stream>>>(src, s_row, s_k, rows, K, Kp, dst);
@@ -301,12 +360,12 @@ void* stage_buffer(ormi_b200_ctx* ctx, int which, size_t bytes) {
     return ctx->stage[which];
 }
 
-void make_map(ormi_b200_ctx* ctx, CUtensorMap* map, void* ptr, int rows, int Kp, int box_rows) {
+void make_map(ormi_b200_ctx* ctx, CUtensorMap* map, void* ptr, int rows, int Kp, int box_rows, bool fp32 = false) {
     cuuint64_t dims[2] = {(cuuint64_t)Kp, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)Kp * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)Kp * (fp32 ? 4 : 2)};
+    cuuint32_t box[2] = {(cuuint32_t)(fp32 ? BK / 2 : BK), (cuuint32_t)box_rows};     // 128 bytes of K either way
     cuuint32_t estr[2] = {1, 1};
-    ctx->drv.check(ctx->drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr,
+    ctx->drv.check(ctx->drv.TensorMapEncodeTiled(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr,
                                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
                    "cuTensorMapEncodeTiled");
@@ -337,12 +396,42 @@ void gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, floa
     make_map(ctx, &map_b, const_cast<void*>(b16), N, Kp, BN);
     device_error_word(ctx);
     if (!ctx->gemm_attr_set) {
-        ORMI_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        ORMI_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        ORMI_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         ctx->gemm_attr_set = true;
     }
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
     const int grid = std::min(tiles_m * tiles_n, ctx->num_sms);
-    gemm_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(map_a, map_b, C, M, N, Kp / BK, tiles_m, tiles_n, ctx->gemm_err);
+    gemm_tc_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(map_a, map_b, C, M, N, Kp / BK, tiles_m, tiles_n, ctx->gemm_err);
+    ORMI_CUDA(cudaGetLastError());
+    ctx->gemm_err_pending = true;
+    ctx->counters["gemm_launches"]++;
+    ctx->counters["launches"]++;
+}
+
+// fp32 matmul on the tensor cores: operands rounded to tf32 (parts = 1, about 1e-3 relative) or split in two tf32 terms
+// each (parts = 3, "3xTF32": three products per k, fp32-grade results at a third of the tf32 rate).
+void gemm_tf32(ormi_b200_ctx* ctx, const GemmArgs& g, int parts) {
+    if (g.batch != 1 || (long long)g.M * g.N * g.K < (1ll << 21) || g.K < 32) { gemm_ffma(ctx, g); return; }
+    const int KB = BK / 2;                                   // 32 fp32 words per stage row
+    const int Kp = (g.K + KB - 1) / KB * KB;
+    const size_t ld = (size_t)Kp * parts;
+    float* a32 = (float*)stage_buffer(ctx, 0, (size_t)g.M * ld * 4);
+    float* b32 = (float*)stage_buffer(ctx, 1, (size_t)g.N * ld * 4);
+    convert_tf32(ctx, g.A, g.trans_a ? 1 : g.lda, g.trans_a ? g.lda : 1, g.M, g.K, Kp, a32, parts, 0);
+    convert_tf32(ctx, g.B, g.trans_b ? g.ldb : 1, g.trans_b ? 1 : g.ldb, g.N, g.K, Kp, b32, parts, 1);
+    CUtensorMap map_a, map_b;
+    make_map(ctx, &map_a, a32, g.M, (int)ld, BM, true);
+    make_map(ctx, &map_b, b32, g.N, (int)ld, BN, true);
+    device_error_word(ctx);
+    if (!ctx->gemm_attr_set) {
+        ORMI_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        ORMI_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        ctx->gemm_attr_set = true;
+    }
+    const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
+    const int grid = std::min(tiles_m * tiles_n, ctx->num_sms);
+    gemm_tc_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(map_a, map_b, g.C, g.M, g.N, (int)(ld / KB), tiles_m, tiles_n, ctx->gemm_err);
     ORMI_CUDA(cudaGetLastError());
     ctx->gemm_err_pending = true;
     ctx->counters["gemm_launches"]++;

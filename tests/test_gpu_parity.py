@@ -309,3 +309,23 @@ def test_mlp_trainer_matches_oracle_over_steps(device):
         params = [o for o in outs[1:]]
     for name, want in zip(tr.names, params):
         assert rel(tr.parameter(name).reshape(want.shape), want) <= 3 * REDUCE_TOL
+
+
+@pytest.mark.parametrize("mode,tol", [("tf32", 2e-3), ("3xtf32", REDUCE_TOL)])
+@pytest.mark.parametrize("mnk", [(512, 512, 512), (300, 520, 200), (1024, 256, 4096)])
+def test_matmul_tf32_modes(mode, tol, mnk):
+    """Opt-in fp32 matmul on the tensor cores: tf32 operands (about 1e-3), or the three-product 3xTF32 split, which
+    must stay inside the fp32 matmul tolerance of 1e-5."""
+    from ormi_b200.runtime import Device
+    M, N, K = mnk
+    dev = Device(0)
+    try:
+        dev.set_option("matmul", mode)
+        a = W.normal(0, (M, K), 1 / math.sqrt(K))
+        b = W.normal(1, (K, N), 1 / math.sqrt(K))
+        want = a.astype(np.float64) @ b.astype(np.float64)
+        la, lbt = G.leaf(a), G.leaf(np.ascontiguousarray(b.T))
+        for root in (G.matmul(la, G.leaf(b)), G.matmul(la, G.transpose(lbt, [1, 0]))):
+            assert rel(dev.numpy(root), want) <= tol, rel(dev.numpy(root), want)
+    finally:
+        dev.close()
