@@ -278,6 +278,14 @@ def run_only(args):
     from ormi_b200 import graph as G, workloads as W
     from ormi_b200.runtime import Device
     dev = Device(0)
+    if args.only in ("mlp_bf16", "mlp_fp32"):
+        # one rank's share of the MLP training step: --rows rows of the batch (8192 = one of 8 ranks of configs[4])
+        wide = args.only == "mlp_bf16"
+        res = mlp_steps_per_s(dev, torch, W, args.rows, 2048 if wide else 1024, 8192 if wide else 4096,
+                              "bf16" if wide else "fp32", args.steps)
+        print(json.dumps(dict(res, only=args.only, rows=args.rows)))
+        dev.close()
+        return
     if args.only in ("gemm_bf16", "gemm_fp32"):
         # C = A @ B at M = N = K = --rows (default 8192 is too long under a profiler: use --rows 4096)
         n = args.rows
@@ -314,7 +322,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, choices=["softmax", "layernorm", "rowsum", "gemm_bf16", "gemm_fp32"],
+    ap.add_argument("--only", default=None, choices=["softmax", "layernorm", "rowsum", "gemm_bf16", "gemm_fp32", "mlp_bf16", "mlp_fp32"],
                     help="profiling aid: run just this graph --steps times on --rows rows and exit")
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--no-extras", action="store_true", help="skip the matmul sweep and the MLP training steps")
