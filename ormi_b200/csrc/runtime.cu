@@ -113,7 +113,7 @@ CompiledKernel* get_kernel(ormi_b200_ctx* ctx, const KernelStep& k) {
     CompiledKernel ck;
     ctx->drv.check(ctx->drv.ModuleLoadData(&ck.module, cubin.data()), "cuModuleLoadData");
     ctx->drv.check(ctx->drv.ModuleGetFunction(&ck.func, ck.module, k.name.c_str()), "cuModuleGetFunction");
-    if (k.dyn_smem > 48 * 1024)
+    if (k.dyn_smem > 0)     // static shared memory counts against the 48 KB default too: always raise the limit
         ctx->drv.check(ctx->drv.FuncSetAttribute(ck.func, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, k.dyn_smem), "cuFuncSetAttribute");
     ctx->counters["kernels_compiled"]++;
     auto res = ctx->kernel_cache.emplace(k.key + ":" + k.name, ck);
