@@ -37,6 +37,16 @@ BYTES_LAYERNORM = 4 * R * C * 4 + 4 * C * 4
 BYTES_STEP = BYTES_SOFTMAX + BYTES_LAYERNORM
 
 
+_REAL_STDOUT = None
+
+
+def emit(obj):
+    """The one JSON line of the run, on the process's original stdout."""
+    text = (json.dumps(obj) + "\n").encode()
+    sys.stdout.flush()
+    os.write(_REAL_STDOUT if _REAL_STDOUT is not None else 1, text)
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -209,7 +219,7 @@ def run_reference_arm(args, rank):
                          "sample": f"{rows} of {R} rows per step (same graphs, same seeds), autograd + realize on the reference CPU backend"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 def matmul_sweep(dev, torch, G, W, steps=5):
@@ -283,7 +293,7 @@ def run_only(args):
         wide = args.only == "mlp_bf16"
         res = mlp_steps_per_s(dev, torch, W, args.rows, 2048 if wide else 1024, 8192 if wide else 4096,
                               "bf16" if wide else "fp32", args.steps)
-        print(json.dumps(dict(res, only=args.only, rows=args.rows)))
+        emit((dict(res, only=args.only, rows=args.rows)))
         dev.close()
         return
     if args.only in ("gemm_bf16", "gemm_fp32"):
@@ -296,7 +306,7 @@ def run_only(args):
         for _ in range(args.warmup):
             runner.run()
         ms = timed(dev, torch, lambda: runner.run(), args.steps)
-        print(json.dumps({"only": args.only, "n": n, "ms_per_matmul": ms / args.steps,
+        emit(({"only": args.only, "n": n, "ms_per_matmul": ms / args.steps,
                           "tflops_including_conversion": 2.0 * n ** 3 / (ms / args.steps * 1e-3) / 1e12}))
         dev.close()
         return
@@ -311,7 +321,7 @@ def run_only(args):
     for _ in range(args.warmup):
         runner.run()
     ms = timed(dev, torch, lambda: runner.run(), args.steps)
-    print(json.dumps({"only": args.only, "rows": args.rows, "cols": C, "ms_per_launch": ms / args.steps,
+    emit(({"only": args.only, "rows": args.rows, "cols": C, "ms_per_launch": ms / args.steps,
                       "algorithmic_bytes": nbytes, "gbps": nbytes / (ms / args.steps * 1e-3) / 1e9}))
     dev.close()
 
@@ -327,6 +337,12 @@ def main():
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--no-extras", action="store_true", help="skip the matmul sweep and the MLP training steps")
     args = ap.parse_args()
+    # Libraries (NCCL's version banner, for one) print to stdout; the contract is ONE JSON line there.  Everything but
+    # that line goes to stderr.
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.dup(1)
+    os.dup2(2, 1)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -474,7 +490,7 @@ def main():
                              "sample": f"2048 of {R} rows, one run ({cpu_secs:.1f} s), autograd + realize on the reference CPU backend"},
         }
         line["extra"] = extras
-        print(json.dumps(line))
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
     dev.close()
