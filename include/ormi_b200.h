@@ -156,11 +156,16 @@ int ormi_b200_gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* 
  * device).  `id` is NCCL's 128-byte unique id: create it on one rank, hand it to the others by any host channel.
  * allreduce: in-place fp32 sum of `n` buffers (one NCCL group).  overlap = 0 queues it on the compute stream;
  * overlap = 1 queues it on a second stream behind everything queued so far, so later kernels run beside it —
- * ormi_b200_comm_join then makes the compute stream wait for the results. */
+ * ormi_b200_comm_join then makes the compute stream wait for the results.  For a wait that comes later than the
+ * point where the bucket was queued (another bucket, or the next step's first kernels, in between):
+ * ormi_b200_comm_mark(slot) remembers the second stream's current tail in one of 8 slots and
+ * ormi_b200_comm_wait(slot) makes the compute stream wait for exactly that point. */
 int ormi_b200_comm_unique_id(char id[128]);
 int ormi_b200_comm_init(ormi_b200_ctx* ctx, const char id[128], int rank, int world_size);
 int ormi_b200_allreduce_sum_f32(ormi_b200_ctx* ctx, void* const* buffers, const size_t* counts, int n, int overlap);
 int ormi_b200_comm_join(ormi_b200_ctx* ctx);
+int ormi_b200_comm_mark(ormi_b200_ctx* ctx, int slot);
+int ormi_b200_comm_wait(ormi_b200_ctx* ctx, int slot);
 int ormi_b200_comm_destroy(ormi_b200_ctx* ctx);
 
 /* Column sums of a contiguous fp32 matrix, out[c] = sum over r of in[r * cols + c], WITHOUT allocating anything.

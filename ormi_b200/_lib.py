@@ -47,6 +47,8 @@ _SIGNATURES = {
     "ormi_b200_comm_init": (c_int, [c_void_p, c_char_p, c_int, c_int]),
     "ormi_b200_allreduce_sum_f32": (c_int, [c_void_p, P(c_void_p), P(c_size_t), c_int, c_int]),
     "ormi_b200_comm_join": (c_int, [c_void_p]),
+    "ormi_b200_comm_mark": (c_int, [c_void_p, c_int]),
+    "ormi_b200_comm_wait": (c_int, [c_void_p, c_int]),
     "ormi_b200_comm_destroy": (c_int, [c_void_p]),
     "ormi_b200_set_option": (c_int, [c_void_p, c_char_p, c_char_p]),
     "ormi_b200_get_counter": (c_int, [c_void_p, c_char_p, P(ctypes.c_int64)]),

@@ -264,6 +264,14 @@ int ormi_b200_comm_join(ormi_b200_ctx* ctx) {
     return guarded([&] { need(ctx != nullptr, "ctx is NULL"); comm_join(ctx); });
 }
 
+int ormi_b200_comm_mark(ormi_b200_ctx* ctx, int slot) {
+    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); comm_mark(ctx, slot); });
+}
+
+int ormi_b200_comm_wait(ormi_b200_ctx* ctx, int slot) {
+    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); comm_wait(ctx, slot); });
+}
+
 int ormi_b200_comm_destroy(ormi_b200_ctx* ctx) {
     return guarded([&] { need(ctx != nullptr, "ctx is NULL"); comm_destroy(ctx); });
 }

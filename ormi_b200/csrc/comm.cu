@@ -56,11 +56,14 @@ void nccl_check(ncclResult_t r, const char* what) {
     if (r != ncclSuccess) throw Error(std::string("NCCL Error: ") + api().GetErrorString(r) + " (" + what + ")");
 }
 
+constexpr int kCommMarks = 8;
+
 struct CommState {
     ncclComm_t comm = nullptr;
     int rank = 0, world = 1;
     cudaStream_t stream = nullptr;     // second stream for overlapped buckets
     cudaEvent_t ready = nullptr, done = nullptr;
+    cudaEvent_t marks[kCommMarks] = {};   // ormi_b200_comm_mark / ormi_b200_comm_wait
 };
 
 CommState* state(ormi_b200_ctx* ctx) {
@@ -89,6 +92,7 @@ void comm_init(ormi_b200_ctx* ctx, const char* id128, int rank, int world) {
     ORMI_CUDA(cudaStreamCreateWithFlags(&st->stream, cudaStreamNonBlocking));
     ORMI_CUDA(cudaEventCreateWithFlags(&st->ready, cudaEventDisableTiming));
     ORMI_CUDA(cudaEventCreateWithFlags(&st->done, cudaEventDisableTiming));
+    for (auto& e : st->marks) ORMI_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     ctx->nccl = st.release();
 }
 
@@ -114,6 +118,18 @@ void comm_join(ormi_b200_ctx* ctx) {
     ORMI_CUDA(cudaStreamWaitEvent(ctx->stream, st->done, 0));
 }
 
+void comm_mark(ormi_b200_ctx* ctx, int slot) {
+    CommState* st = state(ctx);
+    if (slot < 0 || slot >= kCommMarks) throw Error("NCCL Error: mark slot out of range");
+    ORMI_CUDA(cudaEventRecord(st->marks[slot], st->stream));
+}
+
+void comm_wait(ormi_b200_ctx* ctx, int slot) {
+    CommState* st = state(ctx);
+    if (slot < 0 || slot >= kCommMarks) throw Error("NCCL Error: mark slot out of range");
+    ORMI_CUDA(cudaStreamWaitEvent(ctx->stream, st->marks[slot], 0));   // a slot never marked is already complete
+}
+
 void comm_destroy(ormi_b200_ctx* ctx) {
     if (!ctx->nccl) return;
     CommState* st = static_cast<CommState*>(ctx->nccl);
@@ -122,6 +138,7 @@ void comm_destroy(ormi_b200_ctx* ctx) {
     if (st->comm) api().CommDestroy(st->comm);
     cudaEventDestroy(st->ready);
     cudaEventDestroy(st->done);
+    for (auto& e : st->marks) cudaEventDestroy(e);
     cudaStreamDestroy(st->stream);
     delete st;
     ctx->nccl = nullptr;

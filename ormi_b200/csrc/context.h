@@ -54,6 +54,8 @@ enum class MatmulMode { FP32, BF16, TF32, TF32X3 };
 
 }  // namespace ormi_b200
 
+namespace ormi_b200 { constexpr int kErrorWords = 64, kTileCounterWord = 32; }
+
 struct ormi_b200_ctx {
     int device = 0;
     int num_sms = 148;
@@ -72,6 +74,7 @@ struct ormi_b200_ctx {
     // bf16 staging for the tensor-core GEMM path (grown on demand, reused across calls)
     void* stage[2] = {nullptr, nullptr};
     size_t stage_bytes[2] = {0, 0};
+    // kErrorWords ints: word 0 is the error word, word kTileCounterWord (its own 128-byte line) the GEMM's tile counter
     int* gemm_err = nullptr;          // device word: non-zero when a bounded wait inside the tensor-core GEMM ran out
     bool gemm_err_pending = false;    // a kernel with bounded waits was launched since the word was last read
     bool gemm_attr_set = false;
@@ -114,6 +117,8 @@ void comm_unique_id(char* out128);
 void comm_init(ormi_b200_ctx* ctx, const char* id128, int rank, int world);
 void comm_allreduce(ormi_b200_ctx* ctx, void* const* bufs, const size_t* counts, int n, int overlap);
 void comm_join(ormi_b200_ctx* ctx);
+void comm_mark(ormi_b200_ctx* ctx, int slot);
+void comm_wait(ormi_b200_ctx* ctx, int slot);
 void comm_destroy(ormi_b200_ctx* ctx);
 
 // `preassigned`: optional (node, pointer) pairs — write that node's value into a caller-owned buffer

@@ -21,6 +21,11 @@
 // The two accumulators let the epilogue of tile i overlap the MMAs of tile i+1.  Tiles are walked in groups
 // of 16 row-blocks so that concurrently running blocks share A and B panels in L2.
 //
+// Tiles are handed out dynamically: the producer lane takes the next tile index from a counter in global memory
+// (zeroed before every launch) and passes it to the other roles through a 4-slot ring in shared memory.  A block
+// that becomes resident late — another stream's kernel, a collective for one, holds some SMs — then finds
+// only what is left instead of a fixed share the others would have to wait for.
+//
 // No cluster launch and no multicast anywhere: every block fetches its own boxes.
 //
 // Every wait is bounded (about two seconds on the global timer).  A wait that runs out raises a block-wide
@@ -34,7 +39,7 @@ namespace ormi_b200 {
 
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16, SCHED = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2, B_STAGE_BYTES = BN * BK * 2;
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
@@ -141,7 +146,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 template <bool TF32>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 float* __restrict__ C, int M, int N, int num_kb, int tiles_m, int tiles_n, int* err) {
+                 float* __restrict__ C, int M, int N, int num_kb, int tiles_m, int tiles_n, int* err, int* tile_counter) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;       // swizzled tiles need 1024-byte alignment
     uint8_t* smem = smem_raw + (base - smem_u32(smem_raw));
@@ -150,8 +155,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
     auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+    auto sfull_bar = [&](int q) { return bars + 8u * (2 * STAGES + 4 + q); };
+    auto sempty_bar = [&](int q) { return bars + 8u * (2 * STAGES + 4 + SCHED + q); };
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4 + 2 * SCHED));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* sched_tile = reinterpret_cast<volatile int*>(tmem_slot + 2);      // SCHED slots; -1 = no tiles left
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_tiles = tiles_m * tiles_n;
@@ -160,6 +168,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         *abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        for (int q = 0; q < SCHED; ++q) { mbar_init(sfull_bar(q), 1); mbar_init(sempty_bar(q), 5); }   // readers: MMA lane + 4 epilogue warps
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -176,7 +185,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
             int s = 0; uint32_t phase = 0;
-            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            int q = 0; uint32_t qphase = 0;
+            for (;;) {
+                if (!mbar_wait(sempty_bar(q), qphase ^ 1u, abort_flag, err, 5)) break;
+                int t = atomicAdd(tile_counter, 1);
+                if (t >= num_tiles) t = -1;
+                sched_tile[q] = t;
+                mbar_arrive(sfull_bar(q));                    // release: the slot is visible to whoever sees this phase
+                if (++q == SCHED) { q = 0; qphase ^= 1u; }
+                if (t < 0) break;
                 int mb, nb; tile_coords(t, tiles_m, tiles_n, mb, nb);
                 bool ok = true;
                 for (int kb = 0; kb < num_kb && ok; ++kb) {
@@ -194,8 +211,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             int s = 0; uint32_t phase = 0;
-            int it = 0;
-            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+            int q = 0; uint32_t qphase = 0;
+            for (int it = 0;; ++it) {
+                if (!mbar_wait(sfull_bar(q), qphase, abort_flag, err, 6)) break;
+                const int t = sched_tile[q];
+                mbar_arrive(sempty_bar(q));
+                if (++q == SCHED) { q = 0; qphase ^= 1u; }
+                if (t < 0) break;
                 const int a = it & 1;
                 const uint32_t aphase = (uint32_t)(it >> 1) & 1u;
                 if (!mbar_wait(tempty_bar(a), aphase ^ 1u, abort_flag, err, 2)) break;
@@ -221,8 +243,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         // ------------------------------------------------------------------ epilogue (warps 2..5)
         const int quarter = warp & 3;                         // TMEM lanes 32*quarter .. 32*quarter+31
-        int it = 0;
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+        int q = 0; uint32_t qphase = 0;
+        for (int it = 0;; ++it) {
+            bool got = mbar_wait(sfull_bar(q), qphase, abort_flag, err, 7);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) break;
+            const int t = sched_tile[q];
+            __syncwarp();                                     // every lane has read the slot
+            if (lane == 0) mbar_arrive(sempty_bar(q));
+            if (++q == SCHED) { q = 0; qphase ^= 1u; }
+            if (t < 0) break;
             int mb, nb; tile_coords(t, tiles_m, tiles_n, mb, nb);
             const int a = it & 1;
             const uint32_t aphase = (uint32_t)(it >> 1) & 1u;
@@ -402,7 +432,9 @@ void gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, floa
     }
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
     const int grid = std::min(tiles_m * tiles_n, ctx->num_sms);
-    gemm_tc_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(map_a, map_b, C, M, N, Kp / BK, tiles_m, tiles_n, ctx->gemm_err);
+    ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err + kTileCounterWord, 0, sizeof(int), ctx->stream));
+    gemm_tc_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(map_a, map_b, C, M, N, Kp / BK, tiles_m, tiles_n, ctx->gemm_err,
+                                                                           ctx->gemm_err + kTileCounterWord);
     ORMI_CUDA(cudaGetLastError());
     ctx->gemm_err_pending = true;
     ctx->counters["gemm_launches"]++;
@@ -431,7 +463,9 @@ void gemm_tf32(ormi_b200_ctx* ctx, const GemmArgs& g, int parts) {
     }
     const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
     const int grid = std::min(tiles_m * tiles_n, ctx->num_sms);
-    gemm_tc_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(map_a, map_b, g.C, g.M, g.N, (int)(ld / KB), tiles_m, tiles_n, ctx->gemm_err);
+    ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err + kTileCounterWord, 0, sizeof(int), ctx->stream));
+    gemm_tc_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(map_a, map_b, g.C, g.M, g.N, (int)(ld / KB), tiles_m, tiles_n, ctx->gemm_err,
+                                                                          ctx->gemm_err + kTileCounterWord);
     ORMI_CUDA(cudaGetLastError());
     ctx->gemm_err_pending = true;
     ctx->counters["gemm_launches"]++;
@@ -454,7 +488,7 @@ void check_gemm_error(ormi_b200_ctx* ctx) {
     if (code != 0) {
         ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err, 0, sizeof(int), ctx->stream));
         throw Error("a bounded device-side wait ran out (code " + std::to_string(code) +
-                    ": tensor-core GEMM 1 producer, 2 accumulator, 3 operands, 4 epilogue; 101 staged row kernel)");
+                    ": tensor-core GEMM 1 producer, 2 accumulator, 3 operands, 4 epilogue, 5-7 tile ring; 101 staged row kernel)");
     }
 }
 

@@ -132,8 +132,8 @@ void launch_kernel(ormi_b200_ctx* ctx, CompiledKernel* k, int grid, int block, s
 // that ran out.  Read back at host-visible boundaries by check_gemm_error.
 int* device_error_word(ormi_b200_ctx* ctx) {
     if (!ctx->gemm_err) {
-        ORMI_CUDA(cudaMalloc(&ctx->gemm_err, sizeof(int)));
-        ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err, 0, sizeof(int), ctx->stream));
+        ORMI_CUDA(cudaMalloc(&ctx->gemm_err, kErrorWords * sizeof(int)));
+        ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err, 0, kErrorWords * sizeof(int), ctx->stream));
     }
     return ctx->gemm_err;
 }

@@ -4,8 +4,8 @@ The step is ordinary Ormi graph code (ormi_b200.workloads.mlp_loss, compute_grad
 module adds is the host loop a data-parallel job needs around ``ormi_b200_realize``:
 
 * the step is split into *phases* (roots that are realized together).  Between phases the gradients that are
-  already complete go out through ``ormi_b200_allreduce_sum_f32`` on the second stream, so the all-reduce of the
-  last layer's gradients overlaps the GEMMs that produce the first layer's;
+  already complete go out through ``ormi_b200_allreduce_sum_f32`` on the second stream, and the compute stream
+  waits for each bucket only where its sums are first read (``ormi_b200_comm_mark`` / ``ormi_b200_comm_wait``);
 * each phase is flattened once; every later step patches the device pointers of its inputs into the flattened
   graph and hands it to the backend again (plan and kernels come from the caches), so a step costs a few C calls;
 * parameters ping-pong: the update phase returns fresh buffers that become the next step's leaves.
@@ -101,6 +101,17 @@ class MLPTrainer:
 
     x, t: this rank's rows.  w1, b1, w2, b2: replicated parameters (numpy arrays).  The gradient all-reduce runs
     only when ``world > 1`` (the communicator must have been initialised on ``dev``).
+
+    Schedule of one step with ``world > 1`` (plain SGD, only the order of independent work is chosen):
+
+        F   h = gelu(x W1 + b1)                      beside the all-reduce of the previous step's dW2, db2
+        U2  W2, b2 -= lr * (dW2, db2 of the previous step)         after that all-reduce
+        B1  loss, dW1, db1                           -> all-reduce bucket 1 on the second stream
+        B2  dW2, db2                                 beside bucket 1 -> all-reduce bucket 2
+        U1  W1, b1 -= lr * (dW1, db1)                after bucket 1
+
+    so bucket 1 hides behind the dW2 GEMM and bucket 2 behind the next step's first GEMM.  `flush` applies the
+    update that is still pending after the last step.
     """
 
     def __init__(self, dev, x, t, w1, b1, w2, b2, lr: float, global_batch: int | None = None, world: int = 1,
@@ -114,7 +125,8 @@ class MLPTrainer:
         params = {k: dev.leaf(v, True) for k, v in (("w1", w1), ("b1", b1), ("w2", w2), ("b2", b2))}
         for k, n in (("x", xn), ("t", tn), *params.items()):
             p.external(k, n)
-        loss = W.mlp_loss(xn, params["w1"], params["b1"], params["w2"], params["b2"], tn, scale=scale)
+        taps: dict = {}
+        loss = W.mlp_loss(xn, params["w1"], params["b1"], params["w2"], params["b2"], tn, scale=scale, taps=taps)
         G.compute_gradients(loss)
         self.names = ["w1", "b1", "w2", "b2"]
         grads = {k: params[k].grad for k in self.names}
@@ -122,63 +134,106 @@ class MLPTrainer:
             ups = [W.sgd_update(params[k], lr) for k in self.names]
             p.add_phase([loss] + ups)
         else:
-            # backward in two phases so the last layer's gradients travel while the first layer's are computed
-            p.add_phase([loss, grads["w2"], grads["b2"]])
-            p.add_phase([grads["w1"], grads["b1"]])
-            g_leaves = {}
-            for k in self.names:           # the update reads the summed gradients as plain inputs
-                g_leaves[k] = G.Node(G.OpEnum.LEAF, data=grads[k].data)
-                p.produced[id(g_leaves[k])] = p.produced[id(grads[k])]
-            self._grad_ids = {k: id(grads[k]) for k in self.names}
-            self._gleaf_ids = {k: id(g_leaves[k]) for k in self.names}
+            # the updates read the summed gradients as plain inputs; until a step has produced some they are zero
+            self._zero = {}
+            g_leaf = {}
+            for k in self.names:
+                g_leaf[k] = dev.leaf(np.zeros(params[k].shape, dtype=np.float32))
+                p.external("g" + k, g_leaf[k])
+                self._zero[k] = p.ext_ptr["g" + k]
             lr_c = dev.const(lr)
-            ups = [G.sub(params[k], G.mul(lr_c, g_leaves[k])) for k in self.names]
-            p.add_phase(ups)
-        self._loss_id = id(loss)
+            up = {k: G.sub(params[k], G.mul(lr_c, g_leaf[k])) for k in self.names}
+            p.add_phase([taps["h"]])                             # F
+            p.add_phase([up["w2"], up["b2"]])                    # U2
+            p.add_phase([loss, grads["w1"], grads["b1"]])        # B1
+            p.add_phase([grads["w2"], grads["b2"]])              # B2
+            p.add_phase([up["w1"], up["b1"]])                    # U1
+            self._pending = None          # (dW2, db2) of the last step, still to be applied
         self.loss_ptr = None
-        self.steps_done = 0
+        self._initial = set(self.names)   # parameters still in the buffers the constructor uploaded
         # the build pass above already ran one step worth of kernels but did not move the parameters
         dev.sync()
 
-    def _allreduce(self, entries, overlap):
+    def _allreduce(self, entries, slot):
         n = len(entries)
         bufs = (ctypes.c_void_p * n)(*[e[0] for e in entries])
         counts = (ctypes.c_size_t * n)(*[e[1] // 4 for e in entries])
-        check(lib.ormi_b200_allreduce_sum_f32(self.dev.handle, bufs, counts, n, 1 if overlap else 0))
+        check(lib.ormi_b200_allreduce_sum_f32(self.dev.handle, bufs, counts, n, 1 if self.overlap else 0))
+        if self.overlap:
+            check(lib.ormi_b200_comm_mark(self.dev.handle, slot))
+
+    def _wait(self, slot):
+        if self.overlap:
+            check(lib.ormi_b200_comm_wait(self.dev.handle, slot))
+
+    def _replace(self, name, new):
+        """Parameter `name` now lives in `new`; its old buffer goes back to the pool unless the constructor's
+        leaf still owns it."""
+        p = self.prog
+        if name in self._initial:
+            self._initial.discard(name)
+        else:
+            self.dev.free(*p.ext_ptr[name])
+        p.ext_ptr[name] = new
+
+    def _apply_pending(self, outs):
+        """U2: the second layer's update with the gradients the previous step left behind."""
+        p = self.prog
+        self._wait(2)
+        res = p.run_phase(1, outs)
+        self._replace("w2", res[0])
+        self._replace("b2", res[1])
+        if self._pending is not None:
+            for buf in self._pending:
+                self.dev.free(*buf)
+            self._pending = None
+        p.ext_ptr["gw2"], p.ext_ptr["gb2"] = self._zero["w2"], self._zero["b2"]
+        return {res[0][0], res[1][0]}
 
     def step(self):
         p, dev = self.prog, self.dev
         outs: dict = {}
         if self.world == 1:
             res = p.run_phase(0, outs)
-            new_params = {k: res[1 + i] for i, k in enumerate(self.names)}
             loss = res[0]
+            keep = {loss[0]}
+            for i, k in enumerate(self.names):
+                self._replace(k, res[1 + i])
+                keep.add(res[1 + i][0])
         else:
-            res0 = p.run_phase(0, outs)
-            loss = res0[0]
-            self._allreduce([res0[1], res0[2], loss], self.overlap)
-            res1 = p.run_phase(1, outs)
-            self._allreduce([res1[0], res1[1]], self.overlap)
-            if self.overlap:
-                check(lib.ormi_b200_comm_join(dev.handle))
-            for k in self.names:
-                outs[self._gleaf_ids[k]] = outs[self._grad_ids[k]]
-            res2 = p.run_phase(2, outs)
-            new_params = {k: res2[i] for i, k in enumerate(self.names)}
-        # parameters ping-pong; everything else this step produced goes back to the pool
-        keep = {v[0] for v in new_params.values()} | {loss[0]}
-        for k in self.names:
-            old = p.ext_ptr[k]
-            if self.steps_done > 0:
-                dev.free(*old)
-            p.ext_ptr[k] = new_params[k]
+            p.run_phase(0, outs)                                   # F
+            keep = self._apply_pending(outs)                       # U2
+            res = p.run_phase(2, outs)                             # B1
+            loss, dw1, db1 = res[0], res[1], res[2]
+            self._allreduce([dw1, db1, loss], 1)
+            res = p.run_phase(3, outs)                             # B2
+            dw2, db2 = res[0], res[1]
+            self._allreduce([dw2, db2], 2)
+            self._wait(1)
+            p.ext_ptr["gw1"], p.ext_ptr["gb1"] = dw1, db1
+            res = p.run_phase(4, outs)                             # U1
+            self._replace("w1", res[0])
+            self._replace("b1", res[1])
+            self._pending = (dw2, db2)
+            p.ext_ptr["gw2"], p.ext_ptr["gb2"] = dw2, db2
+            keep |= {res[0][0], res[1][0], dw2[0], db2[0], loss[0]}
+        # everything else this step produced goes back to the pool (stream-ordered: kernels already queued finish first)
         for ptr, nbytes in outs.get("owned", []):
             if ptr not in keep:
                 dev.free(ptr, nbytes)
         if self.loss_ptr is not None:
             dev.free(*self.loss_ptr)
         self.loss_ptr = loss
-        self.steps_done += 1
+        self.steps_done = getattr(self, "steps_done", 0) + 1
+
+    def flush(self):
+        """Applies the update a multi-rank step leaves pending (W2, b2), so that `parameter` sees step-complete values."""
+        if self.world > 1 and self._pending is not None:
+            outs: dict = {}
+            keep = self._apply_pending(outs)
+            for ptr, nbytes in outs.get("owned", []):
+                if ptr not in keep:
+                    self.dev.free(ptr, nbytes)
 
     def loss(self) -> float:
         """Global loss of the last step (already summed over ranks when world > 1)."""
@@ -187,6 +242,7 @@ class MLPTrainer:
         return float(out[0])
 
     def parameter(self, name: str) -> np.ndarray:
+        self.flush()
         ptr, nbytes = self.prog.ext_ptr[name]
         out = np.empty(nbytes // 4, dtype=np.float32)
         self.dev.d2h(out, ptr)

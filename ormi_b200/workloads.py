@@ -51,11 +51,13 @@ def gelu_tanh(u):
     return G.mul(G.mul(C(0.5), u), G.add(C(1.0), th))
 
 
-def mlp_loss(x, w1, b1, w2, b2, t, scale=None):
+def mlp_loss(x, w1, b1, w2, b2, t, scale=None, taps=None):
     """loss = mean((gelu(x@W1 + b1) @ W2 + b2 - t)^2); ``scale`` overrides 1/(B*D) (batch-sharded runs
-    divide by the global batch)."""
+    divide by the global batch).  ``taps``, a dict, receives the hidden activation node under "h"."""
     u = G.add(G.matmul(x, w1), b1)
     h = gelu_tanh(u)
+    if taps is not None:
+        taps["h"] = h
     out = G.add(G.matmul(h, w2), b2)
     d = G.sub(out, t)
     if scale is None:
