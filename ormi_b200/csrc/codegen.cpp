@@ -37,7 +37,15 @@ std::string device_prelude() {
 __device__ __forceinline__ float ormi_pow(float x, float y) {
     if (y == 0.5f) return sqrtf(x);
     if (y == 2.0f) return __fmul_rn(x, x);
-    if (y == 3.0f) return (float)((double)x * (double)x * (double)x);
+    if (y == 3.0f) {
+        // x*x = x2 + e2 and x2*x = hi + e3 exactly (fused multiply-add residuals), so hi + (e3 + e2*x) is the cube to
+        // about 2^-46 before the last rounding — no trip through fp64 and its conversion pipe.
+        const float x2 = __fmul_rn(x, x), e2 = __fmaf_rn(x, x, -x2);
+        const float hi = __fmul_rn(x2, x), e3 = __fmaf_rn(x2, x, -hi);
+        const float ah = fabsf(hi);
+        if (ah > 1e-25f && ah < 1e38f) return __fadd_rn(hi, __fmaf_rn(e2, x, e3));
+        return (float)((double)x * (double)x * (double)x);      // residuals under- or overflow out here
+    }
     if (y == 1.0f) return x;
     if (y == -1.0f) return __fdiv_rn(1.0f, x);
     return powf(x, y);

@@ -22,7 +22,7 @@
 // of 16 row-blocks so that concurrently running blocks share A and B panels in L2.
 //
 // Tiles are handed out dynamically: the producer lane takes the next tile index from a counter in global memory
-// (zeroed before every launch) and passes it to the other roles through a 4-slot ring in shared memory.  A block
+// (left at zero by the previous launch) and passes it to the other roles through a 4-slot ring in shared memory.  A block
 // that becomes resident late — another stream's kernel, a collective for one, holds some SMs — then finds
 // only what is left instead of a fixed share the others would have to wait for.
 //
@@ -189,7 +189,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (;;) {
                 if (!mbar_wait(sempty_bar(q), qphase ^ 1u, abort_flag, err, 5)) break;
                 int t = atomicAdd(tile_counter, 1);
-                if (t >= num_tiles) t = -1;
+                if (t >= num_tiles) {
+                    // Every block draws exactly one index past the end; the block that draws the last one leaves the
+                    // counter pair zeroed for the next launch on the stream.
+                    t = -1;
+                    if (atomicAdd(tile_counter + 1, 1) == (int)gridDim.x - 1) { tile_counter[1] = 0; __threadfence(); atomicExch(tile_counter, 0); }
+                }
                 sched_tile[q] = t;
                 mbar_arrive(sfull_bar(q));                    // release: the slot is visible to whoever sees this phase
                 if (++q == SCHED) { q = 0; qphase ^= 1u; }
@@ -299,29 +304,91 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // dst[row * Kp + k] = bf16(src[row * s_row + k * s_k]) for row < rows, k < K; zero for K <= k < Kp.
-// A 32x32 tile goes through shared memory so that both the read (along whichever source axis is contiguous) and the
-// write (along k) are coalesced.
-template <bool SRC_K_CONTIG>
+// One block converts a 64 x 64 tile; every thread ends up writing eight consecutive k of one row as one 16-byte
+// store, eight lanes covering a whole 128-byte line of dst.
+//   source contiguous along k:    two float4 loads per thread, no shared memory;
+//   source contiguous along rows: float4 loads along the rows, transposed through shared memory;
+//   anything else (or unaligned): scalar loads through shared memory.
+// One launch serves both operands of a GEMM: the first `a.blocks` blocks work on job a, the rest on job b.
+struct CvtJob {
+    const float* src; long long s_row, s_k; int rows, K, Kp; __nv_bfloat16* dst;
+    int blocks_x, blocks;        // 64 x 64 tiles along k, and in total
+    int mode;                    // 0 k-contiguous vector path, 1 row-contiguous vector path, 2 scalar
+};
+
+constexpr int CT = 64;           // tile edge
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
 __global__ void __launch_bounds__(256)
-cvt_kmajor(const float* __restrict__ src, long long s_row, long long s_k, int rows, int K, int Kp, __nv_bfloat16* __restrict__ dst) {
-    __shared__ float tile[32][33];
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // 32 x 8
-    const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
-    #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        if (SRC_K_CONTIG) {
-            const int r = r0 + ty + 8 * j, k = k0 + tx;
-            tile[ty + 8 * j][tx] = (r < rows && k < K) ? src[r * s_row + k * s_k] : 0.0f;
-        } else {
-            const int r = r0 + tx, k = k0 + ty + 8 * j;
-            tile[tx][ty + 8 * j] = (r < rows && k < K) ? src[r * s_row + k * s_k] : 0.0f;
+cvt_kmajor(const CvtJob a, const CvtJob b) {
+    __shared__ float tile[CT][CT + 1];                           // [k][row]
+    int bid = blockIdx.x;
+    const bool second = bid >= a.blocks;
+    const CvtJob& j = second ? b : a;
+    if (second) bid -= a.blocks;
+    const int r0 = (bid / j.blocks_x) * CT, k0 = (bid % j.blocks_x) * CT;
+    const float* __restrict__ src = j.src;
+    const int tid = threadIdx.x;
+    const int kseg = tid & 7;                                    // which 8 k of the 64
+    const int rsub = tid >> 3;                                   // 0..31; rows rsub and rsub + 32
+
+    if (j.mode == 0) {
+        #pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = r0 + rsub + 32 * h, k = k0 + 8 * kseg;
+            if (r >= j.rows) continue;
+            float v[8];
+            if (k + 8 <= j.K) {
+                const float4 p = *reinterpret_cast<const float4*>(src + r * j.s_row + k);
+                const float4 q = *reinterpret_cast<const float4*>(src + r * j.s_row + k + 4);
+                v[0] = p.x; v[1] = p.y; v[2] = p.z; v[3] = p.w; v[4] = q.x; v[5] = q.y; v[6] = q.z; v[7] = q.w;
+            } else {
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = (k + i < j.K) ? src[r * j.s_row + k + i] : 0.0f;
+            }
+            uint4 o = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+            *reinterpret_cast<uint4*>(j.dst + (size_t)r * j.Kp + k) = o;
+        }
+        return;
+    }
+
+    if (j.mode == 1) {                                           // 16 lanes x float4 = 64 rows of one k; 16 k per pass
+        const int rq = (tid & 15) * 4, kk = tid >> 4;
+        #pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+            const int kt = kk + 16 * pass, k = k0 + kt, r = r0 + rq;
+            float4 p = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (k < j.K) {
+                if (r + 4 <= j.rows) p = *reinterpret_cast<const float4*>(src + r + k * j.s_k);
+                else {
+                    if (r < j.rows) p.x = src[r + k * j.s_k];
+                    if (r + 1 < j.rows) p.y = src[r + 1 + k * j.s_k];
+                    if (r + 2 < j.rows) p.z = src[r + 2 + k * j.s_k];
+                }
+            }
+            tile[kt][rq] = p.x; tile[kt][rq + 1] = p.y; tile[kt][rq + 2] = p.z; tile[kt][rq + 3] = p.w;
+        }
+    } else {
+        for (int e = tid; e < CT * CT; e += 256) {
+            const int kt = e / CT, rt = e % CT;
+            const int k = k0 + kt, r = r0 + rt;
+            tile[kt][rt] = (r < j.rows && k < j.K) ? src[r * j.s_row + k * j.s_k] : 0.0f;
         }
     }
     __syncthreads();
     #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int r = r0 + ty + 8 * j, k = k0 + tx;
-        if (r < rows && k < Kp) dst[(size_t)r * Kp + k] = __float2bfloat16_rn(tile[ty + 8 * j][tx]);
+    for (int h = 0; h < 2; ++h) {
+        const int rt = rsub + 32 * h, r = r0 + rt;
+        if (r >= j.rows) continue;
+        float v[8];
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = tile[8 * kseg + i][rt];
+        uint4 o = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        *reinterpret_cast<uint4*>(j.dst + (size_t)r * j.Kp + k0 + 8 * kseg) = o;
     }
 }
 
@@ -373,10 +440,17 @@ void convert_tf32(ormi_b200_ctx* ctx, const float* src, long long s_row, long lo
     ctx->counters["launches"]++;
 }
 
-void convert(ormi_b200_ctx* ctx, const float* src, long long s_row, long long s_k, int rows, int K, int Kp, __nv_bfloat16* dst) {
-    dim3 grid((Kp + 31) / 32, (rows + 31) / 32);
-    if (s_k == 1) cvt_kmajor<true><<<grid, 256, 0, ctx->stream>>>(src, s_row, s_k, rows, K, Kp, dst);
-    else cvt_kmajor<false><<<grid, 256, 0, ctx->stream>>>(src, s_row, s_k, rows, K, Kp, dst);
+CvtJob cvt_job(const float* src, long long s_row, long long s_k, int rows, int K, int Kp, __nv_bfloat16* dst) {
+    CvtJob j{src, s_row, s_k, rows, K, Kp, dst, (Kp + CT - 1) / CT, 0, 2};
+    j.blocks = j.blocks_x * ((rows + CT - 1) / CT);
+    const bool aligned = ((uintptr_t)src & 15) == 0;
+    if (s_k == 1 && aligned && s_row % 4 == 0) j.mode = 0;
+    else if (s_row == 1 && aligned && s_k % 4 == 0) j.mode = 1;
+    return j;
+}
+
+void convert(ormi_b200_ctx* ctx, const CvtJob& a, const CvtJob& b) {
+    cvt_kmajor<<<a.blocks + b.blocks, 256, 0, ctx->stream>>>(a, b);
     ORMI_CUDA(cudaGetLastError());
     ctx->counters["launches"]++;
 }
@@ -411,8 +485,8 @@ void gemm_bf16(ormi_b200_ctx* ctx, const GemmArgs& g) {
     __nv_bfloat16* a16 = (__nv_bfloat16*)stage_buffer(ctx, 0, (size_t)g.M * Kp * 2);
     __nv_bfloat16* b16 = (__nv_bfloat16*)stage_buffer(ctx, 1, (size_t)g.N * Kp * 2);
     // A(m,k) = A[m*lda + k] (or A[k*lda + m] when stored transposed); B(k,n) = B[k*ldb + n] (or B[n*ldb + k])
-    convert(ctx, g.A, g.trans_a ? 1 : g.lda, g.trans_a ? g.lda : 1, g.M, g.K, Kp, a16);
-    convert(ctx, g.B, g.trans_b ? g.ldb : 1, g.trans_b ? 1 : g.ldb, g.N, g.K, Kp, b16);
+    convert(ctx, cvt_job(g.A, g.trans_a ? 1 : g.lda, g.trans_a ? g.lda : 1, g.M, g.K, Kp, a16),
+            cvt_job(g.B, g.trans_b ? g.ldb : 1, g.trans_b ? 1 : g.ldb, g.N, g.K, Kp, b16));
 
     gemm_bf16_kmajor(ctx, a16, b16, g.C, g.M, g.N, Kp);
 }
@@ -432,7 +506,6 @@ void gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, floa
     }
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
     const int grid = std::min(tiles_m * tiles_n, ctx->num_sms);
-    ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err + kTileCounterWord, 0, sizeof(int), ctx->stream));
     gemm_tc_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(map_a, map_b, C, M, N, Kp / BK, tiles_m, tiles_n, ctx->gemm_err,
                                                                            ctx->gemm_err + kTileCounterWord);
     ORMI_CUDA(cudaGetLastError());
@@ -463,7 +536,6 @@ void gemm_tf32(ormi_b200_ctx* ctx, const GemmArgs& g, int parts) {
     }
     const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
     const int grid = std::min(tiles_m * tiles_n, ctx->num_sms);
-    ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err + kTileCounterWord, 0, sizeof(int), ctx->stream));
     gemm_tc_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, ctx->stream>>>(map_a, map_b, g.C, g.M, g.N, (int)(ld / KB), tiles_m, tiles_n, ctx->gemm_err,
                                                                           ctx->gemm_err + kTileCounterWord);
     ORMI_CUDA(cudaGetLastError());
@@ -474,7 +546,8 @@ void gemm_tf32(ormi_b200_ctx* ctx, const GemmArgs& g, int parts) {
 
 // dst[row][k] = bf16(src[row * s_row + k * s_k]), rows x Kp bf16 with Kp = K rounded up to 64 (zero padded).
 void cvt_bf16_kmajor(ormi_b200_ctx* ctx, const float* src, long long s_row, long long s_k, int rows, int K, void* dst) {
-    convert(ctx, src, s_row, s_k, rows, K, (K + BK - 1) / BK * BK, (__nv_bfloat16*)dst);
+    CvtJob none{};
+    convert(ctx, cvt_job(src, s_row, s_k, rows, K, (K + BK - 1) / BK * BK, (__nv_bfloat16*)dst), none);
 }
 
 // Called at host-visible boundaries (sync, device -> host copies): a bounded wait that ran out inside the tensor-core
@@ -486,7 +559,8 @@ void check_gemm_error(ormi_b200_ctx* ctx) {
     ORMI_CUDA(cudaStreamSynchronize(ctx->stream));
     ctx->gemm_err_pending = false;
     if (code != 0) {
-        ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err, 0, sizeof(int), ctx->stream));
+        // a block that gave up may not have drawn its last index: put the tile counter pair back to zero as well
+        ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err, 0, kErrorWords * sizeof(int), ctx->stream));
         throw Error("a bounded device-side wait ran out (code " + std::to_string(code) +
                     ": tensor-core GEMM 1 producer, 2 accumulator, 3 operands, 4 epilogue, 5-7 tile ring; 101 staged row kernel)");
     }
