@@ -629,10 +629,16 @@ GeneratedKernel generate_finalize(int parts, int64_t width, const std::string& n
           << "    if (threadIdx.x == 0) { float t = 0.0f; for (int w = 0; w < 8; ++w) t = __fadd_rn(t, sm[w]); out[0] = t; }\n}\n";
         g.step.grid = 1;
     } else {
+        // 32 columns per block; the 8 warps split the partials (warp w takes p = w, w + 8, ...), so a column's chain of
+        // dependent additions is parts / 8 long and every load is a full 128-byte line; the 8 sub-sums are added in order.
         s << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const float* __restrict__ part, float* __restrict__ out) {\n"
-          << "    const int c = blockIdx.x * 256 + threadIdx.x;\n    if (c >= " << width << ") return;\n"
-          << "    float a = 0.0f;\n    for (int p = 0; p < " << parts << "; ++p) a = __fadd_rn(a, part[p * " << width << " + c]);\n    out[c] = a;\n}\n";
-        g.step.grid = (int)((width + 255) / 256);
+          << "    __shared__ float sm[8][32];\n"
+          << "    const int c = blockIdx.x * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;\n"
+          << "    float a = 0.0f;\n"
+          << "    if (c < " << width << ") for (int p = w; p < " << parts << "; p += 8) a = __fadd_rn(a, part[(long long)p * " << width << " + c]);\n"
+          << "    sm[w][threadIdx.x & 31] = a;\n    __syncthreads();\n"
+          << "    if (w == 0 && c < " << width << ") { float t = sm[0][threadIdx.x]; for (int k = 1; k < 8; ++k) t = __fadd_rn(t, sm[k][threadIdx.x]); out[c] = t; }\n}\n";
+        g.step.grid = (int)((width + 31) / 32);
     }
     g.step.block = 256;
     g.step.name = name;

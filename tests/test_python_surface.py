@@ -1,0 +1,167 @@
+"""The Python binding surface: ormi-core's own pybind11 module (built unchanged on top of the B200 backend) under
+the ``Tensor`` layer of ormi_b200/tensor.py.
+
+Without a GPU the module's CPU device runs (that is ormi-core's CPU backend, unmodified): these cases pin the host
+logic of the Tensor layer.  With a GPU every case also runs on ``device="cuda"`` — graphs go through
+``execute_graph`` -> the execute_jit seam -> ``ormi_b200_realize`` — and is compared with the CPU device of the
+same module on identical inputs.  Topics follow ormi-core/tests/test_tensor.py:5-81.
+"""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+try:
+    from ormi_b200.tensor import Tensor, DeviceMismatchError, backend
+except ImportError as e:          # a checkout without the ormi-core sources cannot build the module
+    pytest.skip(str(e), allow_module_level=True)
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DEVICES = ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)]
+PW_TOL, REDUCE_TOL = 1e-6, 1e-5
+
+
+def rel(a, b):
+    return float(np.abs(np.asarray(a, np.float64) - np.asarray(b, np.float64)).max() / max(1e-30, np.abs(b).max()))
+
+
+@pytest.mark.parametrize("dev", DEVICES)
+def test_leaf_attributes(dev):
+    t = Tensor([[1.0, 2.0], [3.0, 4.0]], device=dev, requires_grad=True)
+    assert t.shape == (2, 2) and t.requires_grad and t.op.name == "LEAF"
+    assert t.device.type.name.lower() == dev
+    assert t.grad is None
+    np.testing.assert_array_equal(t.numpy(), [[1.0, 2.0], [3.0, 4.0]])
+    assert "realized" in repr(t) and "LEAF" in repr(t)
+
+
+@pytest.mark.parametrize("dev", DEVICES)
+def test_arithmetic_and_scalar_promotion(dev):
+    a, b = Tensor([8.0, 9.0, -3.0], device=dev), Tensor([2.0, 3.0, 4.0], device=dev)
+    np.testing.assert_allclose((a + b).numpy(), [10.0, 12.0, 1.0])
+    np.testing.assert_allclose((a - b).numpy(), [6.0, 6.0, -7.0])
+    np.testing.assert_allclose((a * b).numpy(), [16.0, 27.0, -12.0])
+    np.testing.assert_allclose((a / b).numpy(), [4.0, 3.0, -0.75])
+    np.testing.assert_allclose((-a).numpy(), [-8.0, -9.0, 3.0])
+    np.testing.assert_allclose((b ** 3.0).numpy(), [8.0, 27.0, 64.0])
+    # a scalar on the left goes through the reflected operators
+    np.testing.assert_allclose((1.0 + b).numpy(), [3.0, 4.0, 5.0])
+    np.testing.assert_allclose((1.0 - b).numpy(), [-1.0, -2.0, -3.0])
+    np.testing.assert_allclose((3.0 * b).numpy(), [6.0, 9.0, 12.0])
+    np.testing.assert_allclose((12.0 / b).numpy(), [6.0, 4.0, 3.0])
+    lazy = a * b + 1.0
+    assert "lazy" in repr(lazy)
+    lazy.realize()
+    assert "realized" in repr(lazy)
+
+
+@pytest.mark.parametrize("dev", DEVICES)
+def test_matmul_and_operand_check(dev):
+    a = Tensor([[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]], device=dev)
+    b = Tensor([[1.0, 0.0], [0.0, 1.0], [2.0, 2.0]], device=dev)
+    c = a @ b
+    assert c.shape == (2, 2)
+    np.testing.assert_allclose(c.numpy(), [[7.0, 8.0], [16.0, 17.0]])
+    with pytest.raises(TypeError):
+        _ = a @ 3.0
+
+
+@pytest.mark.parametrize("dev", DEVICES)
+def test_views(dev):
+    a = Tensor(np.arange(12, dtype=np.float32).reshape(3, 4), device=dev)
+    np.testing.assert_array_equal(a.reshape((2, 6)).numpy(), np.arange(12).reshape(2, 6))
+    np.testing.assert_array_equal(a.transpose().numpy(), np.arange(12).reshape(3, 4).T)
+    row = Tensor([1.0, 2.0, 3.0, 4.0], device=dev)
+    np.testing.assert_array_equal((a + row.expand((3, 4))).numpy(), np.arange(12).reshape(3, 4) + [1, 2, 3, 4])
+    np.testing.assert_array_equal((a.transpose() * 2.0).numpy(), 2 * np.arange(12).reshape(3, 4).T)
+
+
+@pytest.mark.parametrize("dev", DEVICES)
+def test_backward_and_zero_grad(dev):
+    a = Tensor([2.0, 3.0], device=dev, requires_grad=True)
+    b = Tensor([4.0, 5.0], device=dev, requires_grad=True)
+    z = a * b + a * a            # dz/da = b + 2a, dz/db = a
+    z.backward()
+    np.testing.assert_allclose(a.grad.numpy(), [8.0, 11.0])
+    np.testing.assert_allclose(b.grad.numpy(), [2.0, 3.0])
+    a.zero_grad()
+    assert a.grad is None and b.grad is not None
+    z.zero_grad_graph()
+    assert b.grad is None
+    with pytest.raises(RuntimeError):
+        Tensor([1.0], device=dev).backward()
+
+
+def test_device_errors():
+    with pytest.raises(DeviceMismatchError):
+        Tensor([1.0], device="tpu")
+    with pytest.raises(DeviceMismatchError):
+        Tensor([1.0], device=3)
+    a = Tensor([1.0], device="cpu")
+    assert a.device.type == backend.DeviceEnum.CPU and Tensor([1.0]).device.type == backend.DeviceEnum.CPU
+
+
+def _softmax(x):
+    e = x.exp()
+    return e / e.sum([1], True)
+
+
+def _layernorm(x, g, b, eps=1e-5):
+    n = float(x.shape[1])
+    mu = x.sum([1], True) / n
+    d = x - mu
+    var = (d * d).sum([1], True) / n
+    return d / (var + eps) ** 0.5 * g + b
+
+
+def _run_graphs(dev, seed=0):
+    rng = np.random.default_rng(seed)
+    R, C = 64, 96
+    x_h = (rng.standard_normal((R, C)) * 1.5).astype(np.float32)
+    g_h, b_h = rng.uniform(0.5, 1.5, C).astype(np.float32), (rng.standard_normal(C) * 0.1).astype(np.float32)
+    w_h = (rng.standard_normal((C, 32)) / np.sqrt(C)).astype(np.float32)
+    x, g, b = (Tensor(v, device=dev, requires_grad=True) for v in (x_h, g_h, b_h))
+    w = Tensor(w_h, device=dev, requires_grad=True)
+    loss = ((_layernorm(x, g, b) @ w) * _softmax(x @ w)).sum()
+    loss.backward()
+    return [t.numpy().copy() for t in (loss, x.grad, g.grad, b.grad, w.grad)]
+
+
+def test_fused_graphs_on_cpu_device():
+    """The CPU device of the module against numpy in fp64: the Tensor layer builds the graph it should."""
+    rng = np.random.default_rng(0)
+    x_h = (rng.standard_normal((64, 96)) * 1.5).astype(np.float32)
+    y = _softmax(Tensor(x_h, device="cpu")).numpy()
+    e = np.exp(x_h.astype(np.float64))
+    assert rel(y, e / e.sum(1, keepdims=True)) <= REDUCE_TOL
+    assert len(_run_graphs("cpu")) == 5
+
+
+@pytest.mark.gpu
+def test_fused_graphs_cuda_against_cpu_device():
+    """layernorm -> matmul, softmax, a product, a global sum and the whole backward: the CUDA device of the module (the
+    fusion scheduler behind execute_graph) against its CPU device (ormi-core's CPU backend) on the same inputs."""
+    want, got = _run_graphs("cpu"), _run_graphs("cuda")
+    for w, g in zip(want, got):
+        assert w.shape == g.shape
+        assert rel(g, w) <= 3 * REDUCE_TOL
+
+
+@pytest.mark.skipif(not os.path.isdir("/root/reference/ormi-core/tests"), reason="needs the ormi checkout")
+def test_ormi_core_python_tests_on_cpu_device():
+    """ormi-core's own Python package and tests (read where they lie, CPU device only here) on top of the module built
+    in this repository."""
+    code = (
+        "import sys; sys.dont_write_bytecode = True\n"
+        f"sys.path[:0] = ['/root/reference/ormi-core/src', {ROOT!r}]\n"
+        "from ormi_b200 import tensor as T\n"
+        "sys.modules['ormi_core._ext.ormi_backend'] = T.backend\n"
+        "import pytest\n"
+        "sys.exit(pytest.main(['/root/reference/ormi-core/tests/test_tensor.py', '-q', '-k', 'cpu', '-p', 'no:cacheprovider',"
+        " '--rootdir', '/tmp', '-c', '/dev/null']))\n"
+    )
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd="/tmp")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert " passed" in out.stdout
