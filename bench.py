@@ -313,6 +313,13 @@ def run_only(args):
     if args.only == "rowsum":
         a, b, c = (dev.leaf(W.normal(i, (args.rows, C))) for i in range(3))
         roots, nbytes = [W.fused_rowsum(a, b, c)], 3 * args.rows * C * 4 + args.rows * 4
+    elif args.only == "softmax_stable":
+        # extension op MAX: the row maximum is subtracted first; forward + autograd backward, still one kernel
+        x = dev.leaf(W.normal(0, (args.rows, C), math.sqrt(2.0)), True)
+        y = W.softmax_stable(x)
+        y.grad = dev.leaf(W.normal(1, (args.rows, C)))
+        G.compute_gradients(y)
+        roots, nbytes = [y, x.grad], 4 * args.rows * C * 4
     else:
         sm, ln, _ = build_graphs(G, W, lambda a, rg=False: dev.leaf(a, rg), rows=args.rows)
         roots = sm if args.only == "softmax" else ln
@@ -332,7 +339,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, choices=["softmax", "layernorm", "rowsum", "gemm_bf16", "gemm_fp32", "mlp_bf16", "mlp_fp32"],
+    ap.add_argument("--only", default=None, choices=["softmax", "softmax_stable", "layernorm", "rowsum", "gemm_bf16", "gemm_fp32", "mlp_bf16", "mlp_fp32"],
                     help="profiling aid: run just this graph --steps times on --rows rows and exit")
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--no-extras", action="store_true", help="skip the matmul sweep and the MLP training steps")

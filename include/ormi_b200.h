@@ -31,7 +31,11 @@ enum ormi_b200_op {
     ORMI_OP_ADD = 7, ORMI_OP_SUB = 8, ORMI_OP_MUL = 9, ORMI_OP_DIV = 10, ORMI_OP_POW = 11,
     ORMI_OP_MATMUL = 12,
     ORMI_OP_SUM = 13, ORMI_OP_TRANSPOSE = 14, ORMI_OP_RESHAPE = 15, ORMI_OP_EXPAND = 16,
-    ORMI_OP_FRAC_DERIV = 17
+    ORMI_OP_FRAC_DERIV = 17,
+    /* Extension ops: no counterpart in ormi::ops::OpEnum (the reference cannot express a maximum).  Additive; the
+     * values stay clear of the reference's range.  MAXIMUM and GE are binary pointwise ops that broadcast like ADD
+     * (GE yields 1.0f where a >= b, else 0.0f); MAX is a reduction with SUM's axes / keepdims rules. */
+    ORMI_OP_MAXIMUM = 100, ORMI_OP_GE = 101, ORMI_OP_MAX = 102
 };
 
 /* Node flags (in). */

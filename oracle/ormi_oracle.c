@@ -19,6 +19,11 @@
  * 0.3.15 in this image); it is restated from its definition C = A*B with fp32 accumulation over k in
  * ascending order, so matmul parity with the reference is to rounding, not bit-exact.
  *
+ * EXTENSION, parity unpinned: ORMI_OP_MAXIMUM, ORMI_OP_GE and ORMI_OP_MAX have no counterpart in the reference, so
+ * nothing of the reference can pin them.  They are evaluated in the same style (one node at a time over realized
+ * parents; MAX walks the input exactly like eval_sum and keeps the larger value) and tests/test_oracle.py checks
+ * them against compositions the reference CAN run (max(a,b) = (a + b + sqrt((a-b)^2)) / 2 to rounding).
+ *
  * Because the reference realizes every parent before a node (runtime.cpp:16-18), each pointwise node
  * is evaluated on its own over realized parents; results are rounded to fp32 after every op, exactly
  * like the register file of the reference's interpreter.
@@ -61,6 +66,8 @@ static float apply(int op, float a, float b) {
         case ORMI_OP_LOG: return logf(a);
         case ORMI_OP_SIN: return sinf(a);
         case ORMI_OP_COS: return cosf(a);
+        case ORMI_OP_MAXIMUM: return a >= b ? a : b;            /* extension */
+        case ORMI_OP_GE: return a >= b ? 1.0f : 0.0f;           /* extension */
     }
     return NAN;
 }
@@ -119,6 +126,8 @@ static int eval_sum(const ormi_b200_node* nodes, slot_t* slots, int i) {
     int64_t out_elems = numel(n);
     float* out = (float*)calloc((size_t)(out_elems > 0 ? out_elems : 1), sizeof(float));   /* zeros(), sum.cpp:15 */
     if (!out) { snprintf(g_err, sizeof g_err, "out of memory"); return 1; }
+    const int is_max = (n->op == ORMI_OP_MAX);                   /* extension: same walk, keep the larger value */
+    if (is_max) for (int64_t e = 0; e < out_elems; ++e) out[e] = -INFINITY;
     int ostr[ORMI_B200_MAX_DIMS];
     for (int d = n->ndim - 1, acc = 1; d >= 0; --d) { ostr[d] = acc; acc *= n->shape[d]; }
     for (int d = 0; d < in->ndim; ++d) {
@@ -144,7 +153,8 @@ static int eval_sum(const ormi_b200_node* nodes, slot_t* slots, int i) {
             snprintf(g_err, sizeof g_err, "the reference SUM writes out of bounds here (un-broadcast of a middle dimension, adjoint.cpp:22-31)");
             return 1;
         }
-        out[out_flat] += is->ptr[e];
+        if (is_max) { if (is->ptr[e] > out[out_flat]) out[out_flat] = is->ptr[e]; }
+        else out[out_flat] += is->ptr[e];
     }
     slots[i].ptr = out; slots[i].elems = out_elems; slots[i].owned = 1;
     return 0;
@@ -221,9 +231,9 @@ int oracle_port_run(const ormi_b200_node* nodes, int n, const int32_t* out_nodes
         if (nd->data) { slots[i].ptr = (float*)nd->data; slots[i].elems = nd->data_bytes / 4; continue; }
         if (nd->op == ORMI_OP_LEAF) { snprintf(g_err, sizeof g_err, "leaf %d has no data", i); rc = 1; break; }
         if (is_view(nd->op)) { slots[i] = slots[nd->parents[0]]; slots[i].owned = 0; continue; }   /* runtime.cpp:20-23 */
-        if (nd->op == ORMI_OP_SUM) rc = eval_sum(nodes, slots, i);
+        if (nd->op == ORMI_OP_SUM || nd->op == ORMI_OP_MAX) rc = eval_sum(nodes, slots, i);
         else if (nd->op == ORMI_OP_MATMUL) rc = eval_matmul(nodes, slots, i);
-        else if (nd->op >= ORMI_OP_NEG && nd->op <= ORMI_OP_POW) rc = eval_pointwise(nodes, slots, i);
+        else if ((nd->op >= ORMI_OP_NEG && nd->op <= ORMI_OP_POW) || nd->op == ORMI_OP_MAXIMUM || nd->op == ORMI_OP_GE) rc = eval_pointwise(nodes, slots, i);
         else { snprintf(g_err, sizeof g_err, "op %d has no CPU lowering", nd->op); rc = 1; }
     }
     if (seconds) *seconds = now_s() - t0;

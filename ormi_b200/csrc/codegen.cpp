@@ -54,6 +54,12 @@ __device__ __forceinline__ float ormi_warp_sum(float v, int width) {
     for (int o = width >> 1; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
+__device__ __forceinline__ float ormi_max(float a, float b) { return b > a ? b : a; }
+__device__ __forceinline__ float ormi_warp_max(float v, int width) {
+    for (int o = width >> 1; o > 0; o >>= 1) v = ormi_max(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+#define ORMI_NEG_INF __int_as_float(0xff800000)
 #ifndef ORMI_EMULATE
 // Rows staged in shared memory by bulk asynchronous copies (the TMA engine), completion counted on an mbarrier.
 #define ORMI_DYN_SMEM(name) extern __shared__ __align__(1024) unsigned char name[]
@@ -112,10 +118,17 @@ std::string op_expr(int op, const std::string& a, const std::string& b) {
         case ORMI_OP_LOG: return "logf(" + a + ")";
         case ORMI_OP_SIN: return "sinf(" + a + ")";
         case ORMI_OP_COS: return "cosf(" + a + ")";
+        case ORMI_OP_MAXIMUM: return "(" + a + " >= " + b + " ? " + a + " : " + b + ")";
+        case ORMI_OP_GE: return "(" + a + " >= " + b + " ? 1.0f : 0.0f)";
         case KNode::OP_ID: return a;
     }
     return "0.0f /* unknown op */";
 }
+
+// identity element, combining expression and warp reduction of a reduction (sum, or maximum for ORMI_OP_MAX)
+std::string red_ident(bool is_max) { return is_max ? "ORMI_NEG_INF" : "0.0f"; }
+std::string red_comb(bool is_max, const std::string& a, const std::string& b) { return (is_max ? "ormi_max(" : "__fadd_rn(") + a + ", " + b + ")"; }
+std::string red_warp(bool is_max) { return is_max ? "ormi_warp_max" : "ormi_warp_sum"; }
 
 int ceil_pow2(int64_t v) { int p = 1; while (p < v) p <<= 1; return p; }
 
@@ -175,7 +188,7 @@ GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
         scalar[l] = std::all_of(lst[l].begin(), lst[l].end(), [](int64_t v) { return v == 0; });
         if (scalar[l]) s << "    const float S" << l << " = in" << l << "[0];\n";
     }
-    for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) s << "    float gacc" << o << " = 0.0f;\n";
+    for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) s << "    float gacc" << o << " = " << red_ident(spec.outputs[o].is_max) << ";\n";
     s << "    for (int i = blockIdx.x * " << NT << " + threadIdx.x; i < " << nvec << "; i += gridDim.x * " << NT << ") {\n";
     s << "        const int e0 = i * " << V << ";\n";
     if (cd > 1) {
@@ -220,7 +233,7 @@ GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
             return "v" + std::to_string(ko.value.id) + "[" + std::to_string(j) + "]";
         };
         if (ko.kind == KOutput::GLOBALSUM) {
-            for (int j = 0; j < V; ++j) s << "        gacc" << o << " = __fadd_rn(gacc" << o << ", " << val(j) << ");\n";
+            for (int j = 0; j < V; ++j) s << "        gacc" << o << " = " << red_comb(ko.is_max, "gacc" + std::to_string(o), val(j)) << ";\n";
         } else if (V == 4) {
             s << "        *reinterpret_cast<float4*>(out" << o << " + e0) = make_float4(" << val(0) << ", " << val(1) << ", " << val(2) << ", " << val(3) << ");\n";
         } else {
@@ -232,14 +245,14 @@ GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
         s << "    __shared__ float gsm[" << n_global << "][" << NT / 32 << "];\n";
         int gi = 0;
         for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) {
-            s << "    gacc" << o << " = ormi_warp_sum(gacc" << o << ", 32);\n";
+            s << "    gacc" << o << " = " << red_warp(spec.outputs[o].is_max) << "(gacc" << o << ", 32);\n";
             s << "    if ((threadIdx.x & 31) == 0) gsm[" << gi << "][threadIdx.x >> 5] = gacc" << o << ";\n";
             ++gi;
         }
         s << "    __syncthreads();\n    if (threadIdx.x == 0) {\n";
         gi = 0;
         for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) {
-            s << "        { float a = 0.0f; for (int w = 0; w < " << NT / 32 << "; ++w) a = __fadd_rn(a, gsm[" << gi << "][w]); out" << o << "[blockIdx.x] = a; }\n";
+            s << "        { float a = " << red_ident(spec.outputs[o].is_max) << "; for (int w = 0; w < " << NT / 32 << "; ++w) a = " << red_comb(spec.outputs[o].is_max, "a", "gsm[" + std::to_string(gi) + "][w]") << "; out" << o << "[blockIdx.x] = a; }\n";
             ++gi;
         }
         s << "    }\n";
@@ -409,8 +422,9 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         else emit_array_load(l, "0", "    ", false);
     }
     for (size_t o = 0; o < spec.outputs.size(); ++o) {
-        if (spec.outputs[o].kind == KOutput::COLSUM) { s << "    float cacc" << o << "[" << VPT << "];\n    #pragma unroll\n    for (int j = 0; j < " << VPT << "; ++j) cacc" << o << "[j] = 0.0f;\n"; }
-        if (spec.outputs[o].kind == KOutput::GLOBALSUM) s << "    float gacc" << o << " = 0.0f;\n";
+        const std::string ident = red_ident(spec.outputs[o].is_max);
+        if (spec.outputs[o].kind == KOutput::COLSUM) { s << "    float cacc" << o << "[" << VPT << "];\n    #pragma unroll\n    for (int j = 0; j < " << VPT << "; ++j) cacc" << o << "[j] = " << ident << ";\n"; }
+        if (spec.outputs[o].kind == KOutput::GLOBALSUM) s << "    float gacc" << o << " = " << ident << ";\n";
     }
     if (stages) {
         s << "    ORMI_DYN_SMEM(dsm);\n    float* const ring = reinterpret_cast<float*>(dsm);\n";
@@ -505,22 +519,22 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         std::vector<const KNode*> sums;
         for (const KNode& kn : spec.nodes) if (kn.op == KNode::OP_ROWSUM && level[kn.node] == lv + 1) sums.push_back(&kn);
         if (!sums.empty()) {
-            for (auto* kn : sums) s << "        float v" << kn->node << " = 0.0f;\n";
+            for (auto* kn : sums) s << "        float v" << kn->node << " = " << red_ident(kn->is_max) << ";\n";
             s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) {\n";
             std::string ok = ok_expr("j");
             if (!ok.empty()) s << "            const bool ok = " << ok << ";\n";
             for (auto* kn : sums) {
                 std::string val = ref(kn->operands[0], "j");
-                s << "            v" << kn->node << " = __fadd_rn(v" << kn->node << ", " << (ok.empty() ? val : "ok ? " + val + " : 0.0f") << ");\n";
+                s << "            v" << kn->node << " = " << red_comb(kn->is_max, "v" + std::to_string(kn->node), ok.empty() ? val : "(ok ? " + val + " : " + red_ident(kn->is_max) + ")") << ";\n";
             }
             s << "        }\n";
-            for (auto* kn : sums) s << "        v" << kn->node << " = ormi_warp_sum(v" << kn->node << ", " << std::min(T, 32) << ");\n";
+            for (auto* kn : sums) s << "        v" << kn->node << " = " << red_warp(kn->is_max) << "(v" << kn->node << ", " << std::min(T, 32) << ");\n";
             if (NW > 1) {
                 s << "        if ((threadIdx.x & 31) == 0) {";
                 for (size_t i = 0; i < sums.size(); ++i) s << " red[" << i << "][grp][tid >> 5] = v" << sums[i]->node << ";";
                 s << " }\n        __syncthreads();\n";
                 for (size_t i = 0; i < sums.size(); ++i)
-                    s << "        { float a = 0.0f; for (int w = 0; w < " << NW << "; ++w) a = __fadd_rn(a, red[" << i << "][grp][w]); v" << sums[i]->node << " = a; }\n";
+                    s << "        { float a = " << red_ident(sums[i]->is_max) << "; for (int w = 0; w < " << NW << "; ++w) a = " << red_comb(sums[i]->is_max, "a", "red[" + std::to_string(i) + "][grp][w]") << "; v" << sums[i]->node << " = a; }\n";
                 s << "        __syncthreads();\n";
             }
         }
@@ -542,12 +556,12 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         } else if (ko.kind == KOutput::ROW) {
             s << "        if (tid == 0" << (row_pred ? " && rok" : "") << ") out" << o << "[r] = " << ref(ko.value, "0") << ";\n";
         } else if (ko.kind == KOutput::COLSUM) {
-            s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) cacc" << o << "[j] = __fadd_rn(cacc" << o << "[j], "
-              << (row_pred ? "rok ? " + ref(ko.value, "j") + " : 0.0f" : ref(ko.value, "j")) << ");\n";
+            s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) cacc" << o << "[j] = "
+              << red_comb(ko.is_max, "cacc" + std::to_string(o) + "[j]", row_pred ? "(rok ? " + ref(ko.value, "j") + " : " + red_ident(ko.is_max) + ")" : ref(ko.value, "j")) << ";\n";
         } else {
             s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) {\n";
             std::string ok = ok_expr("j");
-            s << "            gacc" << o << " = __fadd_rn(gacc" << o << ", " << (ok.empty() ? ref(ko.value, "j") : "(" + ok + ") ? " + ref(ko.value, "j") + " : 0.0f") << ");\n        }\n";
+            s << "            gacc" << o << " = " << red_comb(ko.is_max, "gacc" + std::to_string(o), ok.empty() ? ref(ko.value, "j") : "((" + ok + ") ? " + ref(ko.value, "j") + " : " + red_ident(ko.is_max) + ")") << ";\n        }\n";
         }
     }
     s << "    }\n";
@@ -558,7 +572,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
             if (spec.outputs[o].kind != KOutput::COLSUM) continue;
             if (G > 1) {
                 s << "    #pragma unroll\n    for (int j = 0; j < " << VPT << "; ++j) csm[grp][j * " << T << " + tid] = cacc" << o << "[j];\n    __syncthreads();\n";
-                s << "    if (grp == 0) {\n        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) { float a = 0.0f; for (int g = 0; g < " << G << "; ++g) a = __fadd_rn(a, csm[g][j * " << T << " + tid]); cacc" << o << "[j] = a; }\n    }\n    __syncthreads();\n";
+                s << "    if (grp == 0) {\n        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) { float a = " << red_ident(spec.outputs[o].is_max) << "; for (int g = 0; g < " << G << "; ++g) a = " << red_comb(spec.outputs[o].is_max, "a", "csm[g][j * " + std::to_string(T) + " + tid]") << "; cacc" << o << "[j] = a; }\n    }\n    __syncthreads();\n";
             }
             s << "    if (grp == 0) {\n        #pragma unroll\n        for (int q = 0; q < " << NV << "; ++q) {\n            const int col = " << col_of("q", "0") << ";\n";
             s << "            " << (col_pred ? "if (col < " + std::to_string(C) + ") " : "");
@@ -571,13 +585,13 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         s << "    __shared__ float gsm[" << n_glob << "][" << NT / 32 << "];\n";
         int gi = 0;
         for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) {
-            s << "    gacc" << o << " = ormi_warp_sum(gacc" << o << ", 32);\n    if ((threadIdx.x & 31) == 0) gsm[" << gi << "][threadIdx.x >> 5] = gacc" << o << ";\n";
+            s << "    gacc" << o << " = " << red_warp(spec.outputs[o].is_max) << "(gacc" << o << ", 32);\n    if ((threadIdx.x & 31) == 0) gsm[" << gi << "][threadIdx.x >> 5] = gacc" << o << ";\n";
             ++gi;
         }
         s << "    __syncthreads();\n    if (threadIdx.x == 0) {\n";
         gi = 0;
         for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) {
-            s << "        { float a = 0.0f; for (int w = 0; w < " << NT / 32 << "; ++w) a = __fadd_rn(a, gsm[" << gi << "][w]); out" << o << "[blockIdx.x] = a; }\n";
+            s << "        { float a = " << red_ident(spec.outputs[o].is_max) << "; for (int w = 0; w < " << NT / 32 << "; ++w) a = " << red_comb(spec.outputs[o].is_max, "a", "gsm[" + std::to_string(gi) + "][w]") << "; out" << o << "[blockIdx.x] = a; }\n";
             ++gi;
         }
         s << "    }\n";
@@ -617,16 +631,17 @@ GeneratedKernel generate_kernel(const KernelSpec& spec, const std::string& name,
     return g;
 }
 
-GeneratedKernel generate_finalize(int parts, int64_t width, const std::string& name) {
+GeneratedKernel generate_finalize(int parts, int64_t width, const std::string& name, bool is_max) {
     GeneratedKernel g;
     std::ostringstream s;
+    const std::string ident = red_ident(is_max);
     s << device_prelude();
     if (width == 1) {
         s << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const float* __restrict__ part, float* __restrict__ out) {\n"
-          << "    __shared__ float sm[8];\n    float a = 0.0f;\n"
-          << "    for (int p = threadIdx.x; p < " << parts << "; p += 256) a = __fadd_rn(a, part[p]);\n"
-          << "    a = ormi_warp_sum(a, 32);\n    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = a;\n    __syncthreads();\n"
-          << "    if (threadIdx.x == 0) { float t = 0.0f; for (int w = 0; w < 8; ++w) t = __fadd_rn(t, sm[w]); out[0] = t; }\n}\n";
+          << "    __shared__ float sm[8];\n    float a = " << ident << ";\n"
+          << "    for (int p = threadIdx.x; p < " << parts << "; p += 256) a = " << red_comb(is_max, "a", "part[p]") << ";\n"
+          << "    a = " << red_warp(is_max) << "(a, 32);\n    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = a;\n    __syncthreads();\n"
+          << "    if (threadIdx.x == 0) { float t = " << ident << "; for (int w = 0; w < 8; ++w) t = " << red_comb(is_max, "t", "sm[w]") << "; out[0] = t; }\n}\n";
         g.step.grid = 1;
     } else {
         // 32 columns per block; the 8 warps split the partials (warp w takes p = w, w + 8, ...), so a column's chain of
@@ -634,24 +649,24 @@ GeneratedKernel generate_finalize(int parts, int64_t width, const std::string& n
         s << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const float* __restrict__ part, float* __restrict__ out) {\n"
           << "    __shared__ float sm[8][32];\n"
           << "    const int c = blockIdx.x * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;\n"
-          << "    float a = 0.0f;\n"
-          << "    if (c < " << width << ") for (int p = w; p < " << parts << "; p += 8) a = __fadd_rn(a, part[(long long)p * " << width << " + c]);\n"
+          << "    float a = " << ident << ";\n"
+          << "    if (c < " << width << ") for (int p = w; p < " << parts << "; p += 8) a = " << red_comb(is_max, "a", "part[(long long)p * " + std::to_string(width) + " + c]") << ";\n"
           << "    sm[w][threadIdx.x & 31] = a;\n    __syncthreads();\n"
-          << "    if (w == 0 && c < " << width << ") { float t = sm[0][threadIdx.x]; for (int k = 1; k < 8; ++k) t = __fadd_rn(t, sm[k][threadIdx.x]); out[c] = t; }\n}\n";
+          << "    if (w == 0 && c < " << width << ") { float t = sm[0][threadIdx.x]; for (int k = 1; k < 8; ++k) t = " << red_comb(is_max, "t", "sm[k][threadIdx.x]") << "; out[c] = t; }\n}\n";
         g.step.grid = (int)((width + 31) / 32);
     }
     g.step.block = 256;
     g.step.name = name;
     g.step.source = s.str();
     g.step.key = std::to_string(fnv1a(g.step.source));
-    g.step.what = "finalize[parts=" + std::to_string(parts) + ",width=" + std::to_string(width) + "]";
+    g.step.what = std::string(is_max ? "finalize_max" : "finalize") + "[parts=" + std::to_string(parts) + ",width=" + std::to_string(width) + "]";
     g.step.bytes_read = (int64_t)parts * width * 4;
     g.step.bytes_written = width * 4;
     return g;
 }
 
 GeneratedKernel generate_generic_sum(const std::vector<int>& shape, const std::vector<int>& strides,
-                                     const std::vector<bool>& reduced, const std::string& name) {
+                                     const std::vector<bool>& reduced, const std::string& name, bool is_max) {
     GeneratedKernel g;
     int64_t n_out = 1, n_red = 1;
     for (size_t d = 0; d < shape.size(); ++d) (reduced[d] ? n_red : n_out) *= shape[d];
@@ -660,9 +675,9 @@ GeneratedKernel generate_generic_sum(const std::vector<int>& shape, const std::v
     s << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const float* __restrict__ in, float* __restrict__ out) {\n"
       << "    const int o = blockIdx.x * 256 + threadIdx.x;\n    if (o >= " << n_out << ") return;\n    int base = 0;\n    {\n        int rem = o;\n";
     for (size_t d = shape.size(); d-- > 0;) if (!reduced[d]) s << "        base += (rem % " << shape[d] << ") * " << strides[d] << "; rem /= " << shape[d] << ";\n";
-    s << "    }\n    float a = 0.0f;\n    for (int e = 0; e < " << n_red << "; ++e) {\n        int rem = e, off = base;\n";
+    s << "    }\n    float a = " << red_ident(is_max) << ";\n    for (int e = 0; e < " << n_red << "; ++e) {\n        int rem = e, off = base;\n";
     for (size_t d = shape.size(); d-- > 0;) if (reduced[d]) s << "        off += (rem % " << shape[d] << ") * " << strides[d] << "; rem /= " << shape[d] << ";\n";
-    s << "        a = __fadd_rn(a, in[off]);\n    }\n    out[o] = a;\n}\n";
+    s << "        a = " << red_comb(is_max, "a", "in[off]") << ";\n    }\n    out[o] = a;\n}\n";
     g.step.grid = (int)((n_out + 255) / 256);
     g.step.block = 256;
     g.step.name = name;

@@ -32,7 +32,8 @@ namespace ormi_b200 {
 namespace {
 
 bool is_view_op(int op) { return op == ORMI_OP_TRANSPOSE || op == ORMI_OP_RESHAPE || op == ORMI_OP_EXPAND; }
-bool is_pw_op(int op) { return op >= ORMI_OP_NEG && op <= ORMI_OP_POW; }
+bool is_pw_op(int op) { return (op >= ORMI_OP_NEG && op <= ORMI_OP_POW) || op == ORMI_OP_MAXIMUM || op == ORMI_OP_GE; }
+bool is_reduce_op(int op) { return op == ORMI_OP_SUM || op == ORMI_OP_MAX; }
 
 enum Kind { K_NONE, K_INPUT, K_VIEW, K_PW, K_IDSUM, K_ROWSUM, K_COLSUM, K_GLOBALSUM, K_GENSUM, K_MATMUL };
 
@@ -126,7 +127,7 @@ struct Scheduler {
                 continue;
             }
             if (nd.op == ORMI_OP_MATMUL) { if (nd.n_parents != 2) return fail("MATMUL needs two parents"); I.kind = K_MATMUL; continue; }
-            if (nd.op == ORMI_OP_SUM) { if (nd.n_parents != 1) return fail("SUM needs one parent"); if (!classify_sum(i)) return false; continue; }
+            if (is_reduce_op(nd.op)) { if (nd.n_parents != 1) return fail("SUM needs one parent"); if (!classify_sum(i)) return false; continue; }
             if (is_pw_op(nd.op)) {
                 int want = (nd.op <= ORMI_OP_COS) ? 1 : 2;
                 if (nd.n_parents != want) return fail("pointwise op with a wrong operand count");
@@ -359,6 +360,7 @@ struct Scheduler {
         const Info& I = info[m];
         KOutput o;
         o.node = m;
+        o.is_max = nodes[m].op == ORMI_OP_MAX;
         if (I.kind == K_PW || I.kind == K_IDSUM || I.kind == K_ROWSUM) {
             o.kind = I.row_cls ? KOutput::ROW : KOutput::FULL;
             o.value = enter(w, m, discover);
@@ -583,7 +585,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
             std::vector<bool> red(sh.size(), nodes[m].n_axes == 0);
             for (int a = 0; a < nodes[m].n_axes; ++a) red[nodes[m].axes[a]] = true;
             if (info[src].kind == K_INPUT && nodes[src].data_bytes == 4) std::fill(st.begin(), st.end(), 0);
-            GeneratedKernel gk = generate_generic_sum(sh, st, red, "ormi_sum_" + std::to_string(kernel_serial++));
+            GeneratedKernel gk = generate_generic_sum(sh, st, red, "ormi_sum_" + std::to_string(kernel_serial++), nodes[m].op == ORMI_OP_MAX);
             Step stp; stp.type = Step::Kernel; stp.k = gk.step;
             stp.k.args = {buffer_for(src), buffer_for(m)};
             plan.steps.push_back(stp);
@@ -603,6 +605,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
             kn.node = q;
             kn.op = info[q].kind == K_PW ? nodes[q].op : (info[q].kind == K_ROWSUM ? KNode::OP_ROWSUM : KNode::OP_ID);
             kn.row = info[q].row_cls;
+            kn.is_max = info[q].kind == K_ROWSUM && nodes[q].op == ORMI_OP_MAX;
             kn.scalar = (info[q].kind == K_PW || info[q].kind == K_IDSUM) && info[q].numel == 1 && !w.D.empty();
             kn.operands = w.operands[q];
             ks.nodes.push_back(kn);
@@ -640,7 +643,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
         for (auto& f : finals) {
             const KOutput& o = ks.outputs[f.second];
             int64_t per = o.kind == KOutput::COLSUM ? gk.cols : 1;
-            GeneratedKernel fk = generate_finalize(gk.step.grid, per, "ormi_finalize_" + std::to_string(kernel_serial++));
+            GeneratedKernel fk = generate_finalize(gk.step.grid, per, "ormi_finalize_" + std::to_string(kernel_serial++), o.is_max);
             Step fs; fs.type = Step::Kernel; fs.k = fk.step;
             fs.k.args = {f.first, buffer_for(o.node)};
             plan.steps.push_back(fs);

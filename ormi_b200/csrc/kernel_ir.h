@@ -25,6 +25,7 @@ struct KNode {
     int op;                     // ormi_b200_op of a pointwise node, OP_ROWSUM or OP_ID
     bool row;                   // one value per row (row sum or pointwise work on row sums)
     bool scalar = false;        // one value for the whole domain (arithmetic on rank-0 operands)
+    bool is_max = false;        // OP_ROWSUM only: the reduction keeps the maximum instead of adding (ORMI_OP_MAX)
     std::vector<KRef> operands;
 };
 
@@ -32,6 +33,7 @@ struct KOutput {
     enum Kind { FULL, ROW, COLSUM, GLOBALSUM } kind;
     int node;                   // materialized node (-1: anonymous gather target)
     KRef value;                 // what is stored (FULL/ROW) or accumulated (COLSUM/GLOBALSUM)
+    bool is_max = false;        // COLSUM/GLOBALSUM: keep the maximum instead of adding (ORMI_OP_MAX)
 };
 
 struct KernelSpec {
@@ -61,9 +63,9 @@ struct GeneratedKernel {
 // (FULL/ROW: the output buffer; COLSUM/GLOBALSUM: a scratch buffer of grid x {cols|1} partials).
 GeneratedKernel generate_kernel(const KernelSpec& spec, const std::string& name, const ormi_b200_node* nodes);
 // out[c] = sum over p < parts of partial[p * width + c]   (fixed order: deterministic)
-GeneratedKernel generate_finalize(int parts, int64_t width, const std::string& name);
+GeneratedKernel generate_finalize(int parts, int64_t width, const std::string& name, bool is_max = false);
 // One thread per output element, serial sum over the reduced coordinates, arbitrary input strides.
 GeneratedKernel generate_generic_sum(const std::vector<int>& shape, const std::vector<int>& strides,
-                                     const std::vector<bool>& reduced, const std::string& name);
+                                     const std::vector<bool>& reduced, const std::string& name, bool is_max = false);
 
 }  // namespace ormi_b200

@@ -46,11 +46,18 @@ class OpEnum(enum.IntEnum):
     RESHAPE = 15
     EXPAND = 16
     FRAC_DERIV = 17
+    # Extension ops (no counterpart in ormi::ops::OpEnum; values kept clear of the reference's range).  They exist in
+    # this module, in the C ABI, in the backend and in the extended part of the CPU oracle port only.
+    MAXIMUM = 100      # pointwise max(a, b), broadcasting like ADD
+    GE = 101           # pointwise a >= b ? 1 : 0 (no gradient)
+    MAX = 102          # reduction over axes, same axes / keepdims rules as SUM
 
 
 VIEW_OPS = (OpEnum.TRANSPOSE, OpEnum.RESHAPE, OpEnum.EXPAND)
 UNARY_OPS = (OpEnum.NEG, OpEnum.EXP, OpEnum.LOG, OpEnum.SIN, OpEnum.COS)
 BINARY_OPS = (OpEnum.ADD, OpEnum.SUB, OpEnum.MUL, OpEnum.DIV, OpEnum.POW)
+EXT_BINARY_OPS = (OpEnum.MAXIMUM, OpEnum.GE)
+REDUCE_OPS = (OpEnum.SUM, OpEnum.MAX)
 
 NODE_KEEP = 1
 NODE_OWNED = 2
@@ -174,11 +181,11 @@ def _infer_shape(node: Node, target: Sequence[int] | None) -> list[int]:
     op, ps = node.op, node.parents
     if op in UNARY_OPS:
         return list(ps[0].shape)                                   # shape.cpp:57-59
-    if op in BINARY_OPS:
+    if op in BINARY_OPS or op in EXT_BINARY_OPS:
         return broadcast_shapes(ps[0].shape, ps[1].shape)           # shape.cpp:61-63
     if op == OpEnum.MATMUL:
         return _infer_matmul_shape(ps)
-    if op == OpEnum.SUM:
+    if op in REDUCE_OPS:
         return _infer_sum_shape(ps[0].shape, node.axes, node.keepdims)
     if op == OpEnum.TRANSPOSE:
         if len(ps[0].shape) != len(node.axes):
@@ -321,6 +328,30 @@ def sum_(a: Node, axes: Iterable[int] = (), keepdims=False) -> Node:
     return Node(OpEnum.SUM, [a], axes=list(axes), keepdims=keepdims)
 
 
+def maximum(a: Node, b: Node) -> Node:
+    """Extension: pointwise max(a, b)."""
+    return Node(OpEnum.MAXIMUM, [a, b])
+
+
+def ge(a: Node, b: Node) -> Node:
+    """Extension: 1.0 where a >= b, else 0.0; carries no gradient."""
+    n = Node(OpEnum.GE, [a, b])
+    n.requires_grad = False
+    return n
+
+
+def max_(a: Node, axes: Iterable[int] = (), keepdims=False) -> Node:
+    """Extension: maximum over ``axes`` (all axes when empty), shaped like ``sum_``."""
+    return Node(OpEnum.MAX, [a], axes=list(axes), keepdims=keepdims)
+
+
+def mean(a: Node, axes: Iterable[int] = (), keepdims=False) -> Node:
+    """Extension (a composition, no new op): SUM over ``axes`` times 1 / (number of reduced elements)."""
+    axes = list(axes)
+    count = numel(a.shape) if not axes else numel([a.shape[d] for d in axes])
+    return Node(OpEnum.MUL, [sum_(a, axes, keepdims), const(1.0 / count)])
+
+
 def transpose(a: Node, axes: Sequence[int]) -> Node:
     return Node(OpEnum.TRANSPOSE, [a], axes=list(axes))
 
@@ -455,6 +486,39 @@ def _adj_sum(n):                                                    # reduce/sum
     _accumulate(x, Node(OpEnum.EXPAND, [dz], shape=list(x.shape)))
 
 
+def _adj_maximum(n):
+    """Extension: the gradient goes to the larger operand; on a tie to the first one."""
+    a, b = n.parents
+    first = Node(OpEnum.GE, [a, b])
+    first.requires_grad = False
+    if a.requires_grad:
+        _accumulate(a, unbroadcast(Node(OpEnum.MUL, [n.grad, first]), a.shape))
+    if b.requires_grad:
+        second = Node(OpEnum.SUB, [const(1.0), first])
+        _accumulate(b, unbroadcast(Node(OpEnum.MUL, [n.grad, second]), b.shape))
+
+
+def _adj_max(n):
+    """Extension: the gradient flows to every element equal to the maximum of its group (ties share nothing: each tied
+    element receives the full gradient, the derivative of max along each of them)."""
+    x = n.parents[0]
+    if not x.requires_grad:
+        return
+    dz, m = n.grad, n
+    if not n.keepdims:
+        target = list(x.shape)
+        if not n.axes:
+            target = [1] * len(target)
+        else:
+            for a in n.axes:
+                target[a] = 1
+        dz = Node(OpEnum.RESHAPE, [dz], shape=target)
+        m = Node(OpEnum.RESHAPE, [n], shape=target)
+    hit = Node(OpEnum.GE, [x, Node(OpEnum.EXPAND, [m], shape=list(x.shape))])
+    hit.requires_grad = False
+    _accumulate(x, Node(OpEnum.MUL, [Node(OpEnum.EXPAND, [dz], shape=list(x.shape)), hit]))
+
+
 def _adj_matmul(n):                                                 # blas/matmul.cpp:71-135
     x, y = n.parents
     dz = n.grad
@@ -500,6 +564,7 @@ _ADJOINTS = {
     OpEnum.POW: _adj_pow, OpEnum.NEG: _adj_neg, OpEnum.EXP: _adj_exp, OpEnum.LOG: _adj_log,
     OpEnum.SIN: _adj_sin, OpEnum.COS: _adj_cos, OpEnum.SUM: _adj_sum, OpEnum.MATMUL: _adj_matmul,
     OpEnum.TRANSPOSE: _adj_transpose, OpEnum.RESHAPE: _adj_reshape, OpEnum.EXPAND: _adj_expand,
+    OpEnum.MAXIMUM: _adj_maximum, OpEnum.MAX: _adj_max, OpEnum.GE: lambda n: None,
 }
 
 

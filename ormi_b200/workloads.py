@@ -34,6 +34,17 @@ def softmax(x):
     return G.div(e, G.sum_(e, [1], True))
 
 
+def softmax_stable(x):
+    """Row softmax with the row maximum subtracted first (extension op MAX): e = exp(x - max); e / sum(e)."""
+    e = G.exp(G.sub(x, G.max_(x, [1], True)))
+    return G.div(e, G.sum_(e, [1], True))
+
+
+def relu_max(z):
+    """relu(z) = maximum(z, 0) (extension op MAXIMUM)."""
+    return G.maximum(z, C(0.0))
+
+
 def layernorm(x, g, b, eps=1e-5):
     n = x.shape[-1]
     inv_n = C(1.0 / n)

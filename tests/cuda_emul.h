@@ -7,6 +7,7 @@
 #include <pthread.h>
 
 #include <cmath>
+#include <cstring>
 #include <thread>
 #include <vector>
 
@@ -29,6 +30,7 @@ static inline float __fadd_rn(float a, float b) { return a + b; }
 static inline float __fsub_rn(float a, float b) { return a - b; }
 static inline float __fmul_rn(float a, float b) { return a * b; }
 static inline float __fmaf_rn(float a, float b, float c) { return fmaf(a, b, c); }
+static inline float __int_as_float(unsigned int v) { float f; std::memcpy(&f, &v, 4); return f; }
 static inline float __fdiv_rn(float a, float b) { return a / b; }
 static inline float __frcp_rn(float a) { return 1.0f / a; }
 static inline void __syncthreads() { pthread_barrier_wait(&emul_barrier); }
