@@ -48,6 +48,9 @@ struct CompiledKernel {
 struct CachedPlan {
     Plan plan;
     std::vector<CompiledKernel*> kernels;   // per step (nullptr for GEMM steps)
+    // liveness of the scratch (Temp) buffers: the step that first touches buffer b and the step after which nothing
+    // reads it; -1 for buffers that are not scratch
+    std::vector<int> first_use, last_use;
 };
 
 enum class MatmulMode { FP32, BF16, TF32, TF32X3 };

@@ -173,6 +173,22 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
         fresh->plan = build_plan(nodes, n_nodes, roots, n_roots, opt);
         if (!fresh->plan.error.empty()) throw Error(fresh->plan.error);
         for (const Step& s : fresh->plan.steps) fresh->kernels.push_back(s.type == Step::Kernel ? get_kernel(ctx, s.k) : nullptr);
+        // Scratch buffers live from their first to their last step only: they are taken from the pool right before
+        // the one and go back right after the other (the pool is ordered by the stream, so a later step of the same
+        // realize call may get the same block), instead of all being held for the whole call.
+        const Plan& p = fresh->plan;
+        fresh->first_use.assign(p.buffers.size(), -1);
+        fresh->last_use.assign(p.buffers.size(), -1);
+        for (size_t si = 0; si < p.steps.size(); ++si) {
+            const Step& s = p.steps[si];
+            std::vector<int> used = s.type == Step::Kernel ? s.k.args : std::vector<int>{s.g.a, s.g.b, s.g.c};
+            for (int b : used) {
+                if (b < 0 || p.buffers[b].kind != BufKind::Temp) continue;
+                if (fresh->first_use[b] < 0) fresh->first_use[b] = (int)si;
+                fresh->last_use[b] = (int)si;
+            }
+        }
+        for (const NodeResult& r : p.results) { fresh->first_use[r.buffer] = -1; fresh->last_use[r.buffer] = -1; }   // handed out: never scratch
         cp = fresh.get();
         ctx->plan_cache[key] = std::move(fresh);
     }
@@ -191,11 +207,13 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
             } else {
                 if (preassigned && pb.kind == BufKind::NodeOut)
                     for (auto& pr : *preassigned) if (pr.first == pb.node) { bufs[b] = pr.second; handed[b] = true; }
-                if (!bufs[b]) bufs[b] = pool_alloc(ctx, (size_t)pb.bytes);
+                if (!bufs[b] && cp->first_use[b] < 0) bufs[b] = pool_alloc(ctx, (size_t)pb.bytes);   // scratch comes later
             }
         }
         for (size_t s = 0; s < plan.steps.size(); ++s) {
             const Step& st = plan.steps[s];
+            for (size_t b = 0; b < plan.buffers.size(); ++b)
+                if (cp->first_use[b] == (int)s) bufs[b] = pool_alloc(ctx, (size_t)plan.buffers[b].bytes);
             if (st.type == Step::Kernel) {
                 std::vector<void*> args;
                 for (int a : st.k.args) args.push_back(bufs[a]);
@@ -212,6 +230,8 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
                 std::memcpy(g.bstride, st.g.bstride, sizeof g.bstride);
                 gemm_dispatch(ctx, g);
             }
+            for (size_t b = 0; b < plan.buffers.size(); ++b)
+                if (cp->last_use[b] == (int)s && bufs[b]) { pool_free(ctx, bufs[b], (size_t)plan.buffers[b].bytes); bufs[b] = nullptr; handed[b] = true; }
         }
     } catch (...) {
         for (size_t b = 0; b < plan.buffers.size(); ++b)

@@ -13,6 +13,7 @@ import pytest
 import make_golden
 from ormi_b200 import graph as G
 from ormi_b200 import workloads as W
+from ormi_b200 import runtime as RT
 from oracle import oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -346,3 +347,28 @@ def test_wide_hidden_layer_schedule(device):
     # the loss is a sum of 524288 positive terms: the oracle adds them serially in fp32 and is itself 2e-4 away from the
     # fp64 value, the tree sum on the GPU is not — so the scalar is compared with a bound that covers the oracle's error
     assert abs(float(device.numpy(loss)) - float(want)) <= 1e-3 * abs(float(want))
+
+
+def test_scratch_buffers_are_reused_inside_one_realize():
+    """Three column sums in a chain need three 1 MiB partial buffers with disjoint lifetimes: the executor takes each
+    from the pool at its first step and returns it after its last, so a fresh context allocates that size once."""
+    from ormi_b200.runtime import Device
+    dev = Device(0)
+    try:
+        a, b, c = (dev.leaf(W.normal(i, (512, 1024))) for i in range(3))
+        y1 = G.sum_(a, [0], False)
+        y2 = G.sum_(G.mul(b, y1), [0], False)
+        y3 = G.sum_(G.mul(c, y2), [0], False)
+        plan = RT.plan([y3], host_pointers=False)
+        temps = [bf["bytes"] for bf in plan["buffers"] if bf["kind"] == "temp"]
+        assert temps == [1 << 20] * 3
+        before = dev.counter("bytes_allocated")
+        dev.realize([y3])
+        grown = dev.counter("bytes_allocated") - before
+        outs = 3 * 4096                                   # y1, y2, y3 are materialized and handed back
+        assert grown == (1 << 20) + outs, grown
+        (want,), _ = O.port_run([G.sum_(G.mul(G.leaf(W.normal(2, (512, 1024))), G.sum_(G.mul(G.leaf(W.normal(1, (512, 1024))),
+                                 G.sum_(G.leaf(W.normal(0, (512, 1024))), [0], False)), [0], False)), [0], False)])
+        assert rel(dev.numpy(y3), want) <= 3 * REDUCE_TOL
+    finally:
+        dev.close()
