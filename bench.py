@@ -154,7 +154,7 @@ class StepRunner:
         return outs
 
 
-def timed(dev, torch, fn, steps, dist=None):
+def timed(dev, torch, fn, steps, dist=None, after=None):
     stream = torch.cuda.ExternalStream(dev.stream)
     if dist is not None:
         dist.barrier()
@@ -163,6 +163,8 @@ def timed(dev, torch, fn, steps, dist=None):
     e0.record(stream)
     for _ in range(steps):
         fn()
+    if after is not None:
+        after()             # still inside the timed region (e.g. the wait for the last step's all-reduce)
     e1.record(stream)
     e1.synchronize()
     torch.cuda.synchronize()
@@ -390,16 +392,30 @@ def main():
             return obj[0]
         init_comm(dev, rank, world, bcast)
 
-    def step():
-        outs = runner.run(keep=dist is not None)
-        if dist is not None:
-            # cross-shard combine: dg, db (the last two roots of the layernorm graph) are summed over the ranks, in
-            # place, by NCCL on the compute stream (no host synchronisation inside a step)
-            bufs = (ctypes.c_void_p * 2)(outs[-2][0], outs[-1][0])
-            counts = (ctypes.c_size_t * 2)(C, C)
-            check(lib.ormi_b200_allreduce_sum_f32(dev.handle, bufs, counts, 2, 0))
-            for ptr, nbytes in outs:
+    pending = []        # results of the previous step whose all-reduce may still be in flight on the second stream
+
+    def settle():
+        """The compute stream waits for the previous step's all-reduce; its buffers go back to the pool."""
+        if pending:
+            check(lib.ormi_b200_comm_join(dev.handle))
+            for ptr, nbytes in pending:
                 dev.free(ptr, nbytes)
+            pending.clear()
+
+    def step():
+        if dist is None:
+            runner.run()
+            return
+        # cross-shard combine: dg, db (the last two roots of the layernorm graph) are summed over the ranks, in place,
+        # by NCCL on the second stream.  Nothing of the next step reads them, so the all-reduce (a latency of some
+        # 25 us for 2 x 16 KB) runs beside the next step's first kernel; the step after waits for it.  No host
+        # synchronisation inside a step.
+        settle()
+        outs = runner.run(keep=True)
+        bufs = (ctypes.c_void_p * 2)(outs[-2][0], outs[-1][0])
+        counts = (ctypes.c_size_t * 2)(C, C)
+        check(lib.ormi_b200_allreduce_sum_f32(dev.handle, bufs, counts, 2, 1))
+        pending.extend(outs)
 
     for _ in range(warmup):
         step()
@@ -410,17 +426,19 @@ def main():
     if rank == 0:
         sampler.start()
     load_steps = max(1, int(1.2 / 0.0008))
-    for _ in range(load_steps if dist is None else 200):
+    for _ in range(load_steps):
         step()
+    settle()
     dev.sync()
     launches0 = dev.counter("launches")
-    ms_total = timed(dev, torch, step, args.steps, dist)
+    ms_total = timed(dev, torch, step, args.steps, dist, after=settle)
     launches = dev.counter("launches") - launches0
     # dominant kernel alone (the fused layernorm forward+backward kernel and its two finalize launches)
     ms_ln = timed(dev, torch, lambda: runner.run(which=1), args.steps, dist)
     ms_sm = timed(dev, torch, lambda: runner.run(which=0), args.steps, dist)
-    for _ in range(300 if dist is None else 50):
+    for _ in range(300):
         step()
+    settle()
     dev.sync()
     clocks = sampler.stop() if rank == 0 else None
 
@@ -435,6 +453,10 @@ def main():
         for k, node in inputs.items():
             dev.h2d(node.data.dev_ptr, pinned[k].numpy())
         outs = runner.run(keep=True)
+        if dist is not None:      # the cross-shard sums of dg, db, before they are read back
+            bufs = (ctypes.c_void_p * 2)(outs[-2][0], outs[-1][0])
+            counts = (ctypes.c_size_t * 2)(C, C)
+            check(lib.ormi_b200_allreduce_sum_f32(dev.handle, bufs, counts, 2, 0))
         for (ptr, nbytes), host in zip(outs, out_host):
             dev.d2h(host.numpy(), ptr)
             dev.free(ptr, nbytes)
