@@ -372,3 +372,23 @@ def test_scratch_buffers_are_reused_inside_one_realize():
         assert rel(dev.numpy(y3), want) <= 3 * REDUCE_TOL
     finally:
         dev.close()
+
+
+def test_limits_fail_loudly_on_the_device_path(device):
+    a = G.leaf(np.zeros((0, 5), np.float32))
+    with pytest.raises(RuntimeError, match="empty or negative dimension"):
+        device.realize([G.add(a, a)])
+    # the context is still usable afterwards
+    b = G.leaf(np.full((4,), 2.0, np.float32))
+    np.testing.assert_array_equal(device.numpy(G.mul(b, b)), np.full((4,), 4.0, np.float32))
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (1, 7), (7, 1), (3, 33), (33, 3), (2, 1025), (129, 5), (5, 12289)])
+def test_ragged_shapes(device, shape):
+    R, C = shape
+    x = G.leaf(W.normal(0, (R, C)), True)
+    g, b = G.leaf(W.uniform(1, (C,), 0.5, 1.5), True), G.leaf(W.normal(2, (C,), 0.1), True)
+    y = W.layernorm(x, g, b)
+    y.grad = G.leaf(W.normal(3, (R, C)))
+    G.compute_gradients(y)
+    check(device, [y, x.grad, g.grad, b.grad, W.softmax(x), G.sum_(x, [0], False), G.sum_(x, [1], True), G.sum_(x, [], False)], 5 * REDUCE_TOL)

@@ -217,3 +217,31 @@ def test_full_size_schedules_compile_with_nvrtc():
     # algorithmic traffic of the layernorm backward+forward kernel: x, gy in; y, dx out (+ small vectors and partials)
     big = plans[1]["steps"][0]
     assert big["bytes_read"] >= 2 * 16384 * 4096 * 4 and big["bytes_written"] >= 2 * 16384 * 4096 * 4
+
+
+# ---------------------------------------------------------------------------- limits the backend states out loud
+def test_empty_dimension_is_rejected_with_a_message():
+    """A zero-sized dimension has no defined meaning in the reference (its broadcast rule turns (0, 5) + (5,) into
+    (1, 5)); the backend refuses it instead of guessing."""
+    a = G.leaf(np.zeros((0, 5), np.float32))
+    for root in (G.add(a, a), G.sum_(a, [0], False), G.matmul(a, G.leaf(np.ones((5, 3), np.float32)))):
+        assert "empty or negative dimension" in RT.plan([root])["error"]
+
+
+def test_more_than_2_31_elements_is_rejected_with_a_message():
+    """Index arithmetic is 32-bit like the reference's: a tensor of 2^31 elements is refused at plan time."""
+    big = G.Node(G.OpEnum.LEAF, data=G.Buffer((1 << 16, 1 << 15), host=np.zeros(1, np.float32)))
+    assert "2^31" in RT.plan([G.add(big, big)])["error"]
+    ok = G.Node(G.OpEnum.LEAF, data=G.Buffer((1 << 15, 1 << 15), host=np.zeros(1, np.float32)))     # 2^30: the largest power of two
+    assert not RT.plan([G.add(ok, ok)])["error"]
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (1, 7), (7, 1), (3, 33), (33, 3), (2, 1025), (129, 5)])
+def test_ragged_shapes_softmax_layernorm_and_sums(shape):
+    R, C = shape
+    x = G.leaf(W.normal(0, (R, C)), True)
+    g, b = G.leaf(W.uniform(1, (C,), 0.5, 1.5), True), G.leaf(W.normal(2, (C,), 0.1), True)
+    y = W.layernorm(x, g, b)
+    y.grad = G.leaf(W.normal(3, (R, C)))
+    G.compute_gradients(y)
+    compare([y, x.grad, g.grad, b.grad, W.softmax(x), G.sum_(x, [0], False), G.sum_(x, [1], True), G.sum_(x, [], False)], 5 * REDUCE_TOL)
