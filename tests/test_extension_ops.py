@@ -201,3 +201,52 @@ def test_stable_softmax_full_size_rows_on_gpu(device):
         assert rel(y_h[r], p) <= REDUCE_TOL
         g = gy_h[r].astype(np.float64)
         assert rel(dx_h[r], p * (g - (p * g).sum())) <= 3 * REDUCE_TOL
+
+
+def _random_graph(rng):
+    unary = [G.neg, G.exp, G.sin, G.cos]
+    binary = [G.add, G.sub, G.mul, G.maximum, G.ge]
+    R, Cn = int(rng.integers(1, 9)), int(rng.choice([1, 4, 12, 33, 64, 130]))
+    pool = [G.leaf(rng.uniform(-1.5, 1.5, size=s).astype(np.float32)) for s in ((R, Cn), (R, Cn), (Cn,), (R, 1), ())]
+    for _ in range(int(rng.integers(3, 14))):
+        u = rng.random()
+        if u < 0.3:
+            pool.append(unary[int(rng.integers(len(unary)))](pool[int(rng.integers(len(pool)))]))
+        elif u < 0.7:
+            x, y = pool[int(rng.integers(len(pool)))], pool[int(rng.integers(len(pool)))]
+            try:
+                pool.append(binary[int(rng.integers(len(binary)))](x, y))
+            except RuntimeError:      # shapes that do not broadcast
+                pass
+        else:
+            x = pool[int(rng.integers(len(pool)))]
+            if len(x.shape) == 2 and x.op not in G.VIEW_OPS:
+                axes = [[1], [0], []][int(rng.integers(3))]
+                red = G.max_ if rng.random() < 0.6 else G.sum_
+                pool.append(red(x, axes, bool(rng.integers(2))))
+    return [n for n in pool[-3:] if not n.is_realized]
+
+
+def test_random_graphs_with_extension_ops_on_the_emulator():
+    rng = np.random.default_rng(4321)
+    ran = 0
+    for _ in range(25):
+        roots = _random_graph(rng)
+        if roots:
+            _emulated(roots, 5 * REDUCE_TOL)
+            ran += 1
+    assert ran >= 15
+
+
+@pytest.mark.gpu
+def test_random_graphs_with_extension_ops_on_gpu(device):
+    rng = np.random.default_rng(987)
+    for _ in range(40):
+        roots = _random_graph(rng)
+        if not roots:
+            continue
+        ref, _ = O.port_run(roots)
+        for r, w in zip(roots, ref):
+            g = device.numpy(r)
+            assert g.shape == w.shape
+            assert rel(g, w) <= 5 * REDUCE_TOL
