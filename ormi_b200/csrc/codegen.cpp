@@ -402,7 +402,11 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     s << ") {\n";
     s << "    // rows=" << R << " cols=" << C << " threads/row=" << T << " rows/block=" << G << " elems/thread=" << VPT << " vec=" << V << "\n";
     s << "    const int tid = threadIdx.x % " << T << ";\n    const int grp = threadIdx.x / " << T << ";\n";
-    if (max_sums_per_level && NW > 1) s << "    __shared__ float red[" << max_sums_per_level << "][" << G << "][" << NW << "];\n";
+    // Per-warp partials of the row reductions: one array per level and per row parity, so that a level needs ONE block
+    // barrier (write, barrier, read).  The next write to the same array is two rows later, and every row has at least
+    // one barrier of its own in between, so no second barrier is needed to protect the reads.
+    const bool use_red = max_sums_per_level && NW > 1;
+    if (use_red) s << "    __shared__ float red[2][" << std::max(1, max_level) << "][" << max_sums_per_level << "][" << G << "][" << NW << "];\n    int rpar = 0;\n";
     auto col_of = [&](const std::string& q, const std::string& e) { return "((" + q + ") * " + std::to_string(T) + " + tid) * " + std::to_string(V) + " + (" + e + ")"; };
     auto emit_array_load = [&](size_t l, const std::string& ro, const std::string& ind, bool rowp) {
         std::string L = "L" + std::to_string(l), P = "in" + std::to_string(l);
@@ -537,11 +541,10 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
             for (auto* kn : sums) s << "        v" << kn->node << " = " << red_warp(kn->is_max) << "(v" << kn->node << ", " << std::min(T, 32) << ");\n";
             if (NW > 1) {
                 s << "        if ((threadIdx.x & 31) == 0) {";
-                for (size_t i = 0; i < sums.size(); ++i) s << " red[" << i << "][grp][tid >> 5] = v" << sums[i]->node << ";";
+                for (size_t i = 0; i < sums.size(); ++i) s << " red[rpar][" << lv << "][" << i << "][grp][tid >> 5] = v" << sums[i]->node << ";";
                 s << " }\n        __syncthreads();\n";
                 for (size_t i = 0; i < sums.size(); ++i)
-                    s << "        { float a = " << red_ident(sums[i]->is_max) << "; for (int w = 0; w < " << NW << "; ++w) a = " << red_comb(sums[i]->is_max, "a", "red[" + std::to_string(i) + "][grp][w]") << "; v" << sums[i]->node << " = a; }\n";
-                s << "        __syncthreads();\n";
+                    s << "        { float a = " << red_ident(sums[i]->is_max) << "; for (int w = 0; w < " << NW << "; ++w) a = " << red_comb(sums[i]->is_max, "a", "red[rpar][" + std::to_string(lv) + "][" + std::to_string(i) + "][grp][w]") << "; v" << sums[i]->node << " = a; }\n";
             }
         }
     }
@@ -570,6 +573,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
             s << "            gacc" << o << " = " << red_comb(ko.is_max, "gacc" + std::to_string(o), ok.empty() ? ref(ko.value, "j") : "((" + ok + ") ? " + ref(ko.value, "j") + " : " + red_ident(ko.is_max) + ")") << ";\n        }\n";
         }
     }
+    if (use_red) s << "        rpar ^= 1;\n";
     s << "    }\n";
     // epilogue: one partial per block
     if (n_col) {
