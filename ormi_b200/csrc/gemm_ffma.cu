@@ -8,9 +8,13 @@
 // matmul.cu:47-52) is a template parameter of the global->shared copy.
 //
 // Tiling: 128x128 output tile per 256-thread block, K sliced by 16, each thread an 8x8 register tile
-// (two 4-wide strips per axis so shared-memory reads are 128-bit and conflict-free), double-buffered
-// shared memory with the next slice prefetched into registers while the current one is multiplied.
+// (two 4-wide strips per axis so shared-memory reads are 128-bit and conflict-free).
 // Accumulation over k is in ascending order inside a thread: deterministic, no split-K, no atomics.
+// Two kernels with identical arithmetic:
+//   sgemm_pipe_kernel  operands whose rows move in 16-byte pieces: cp.async into a 4-stage ring, one barrier per
+//                      slice, packed fma.rn.f32x2 on pairs of accumulators;
+//   sgemm_kernel       everything else (odd leading dimensions, unaligned views): scalar loads staged through
+//                      registers into double-buffered shared memory.
 #include "context.h"
 
 namespace ormi_b200 {
@@ -181,6 +185,183 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Pipelined variant for operands whose rows can be moved in 16-byte pieces (the common case): cp.async straight from
+// global into a 4-stage shared-memory ring, no staging registers and no transposing stores.  Each operand keeps the
+// layout it has in memory:
+//   contiguous along k  (A not transposed / B transposed):  Xs[row][k], 20 floats per row; a thread reads one float4
+//                                                           (4 consecutive k) per row of its micro-tile;
+//   contiguous along m/n (A transposed / B not transposed): Xs[k][128]; a thread reads two float4 per k.
+// When B is contiguous along k a thread's 8 columns are tx + 16 j instead of two runs of 4, which keeps the float4
+// reads of 8 neighbouring threads on different banks (row stride 20 floats).
+// One block barrier per k-slice; k ascending inside a thread, fused multiply-add: bit-identical to sgemm_kernel.
+constexpr int PSTAGES = 4, LDK = BK + 4;
+constexpr int P_OPERAND_FLOATS = BM * LDK;                     // 2560 floats; the [k][128] layout needs 2048
+constexpr int P_SMEM_BYTES = PSTAGES * 2 * P_OPERAND_FLOATS * 4;
+
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gsrc, int src_bytes) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ float f4(const float4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+template <bool A_KMAJOR, bool B_NMAJOR>
+__global__ void __launch_bounds__(NTHREADS)
+sgemm_pipe_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
+                  int M, int N, int K, int lda, int ldb, BatchMap bm) {
+    extern __shared__ __align__(16) float psm[];
+    {
+        int b = blockIdx.z;
+        long long oa = 0, ob = 0;
+        for (int d = bm.nbatch - 1; d >= 0; --d) {
+            int c = b % bm.bshape[d];
+            b /= bm.bshape[d];
+            oa += c * bm.astride[d];
+            ob += c * bm.bstride[d];
+        }
+        A += oa; B += ob;
+        C += (long long)blockIdx.z * M * N;
+    }
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tx = tid % 16, ty = tid / 16;
+    auto a_stage = [&](int st) { return psm + (st * 2) * P_OPERAND_FLOATS; };
+    auto b_stage = [&](int st) { return psm + (st * 2 + 1) * P_OPERAND_FLOATS; };
+
+    // one operand tile = 512 pieces of 16 bytes, two per thread
+    auto issue = [&](int slice) {
+        const int st = slice % PSTAGES, k0 = slice * BK;
+        float* as = a_stage(st);
+        float* bs = b_stage(st);
+        #pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int c = tid + it * NTHREADS;
+            if (A_KMAJOR) {
+                const int r = c >> 2, kq = (c & 3) * 4;
+                const int gm = m0 + r, gk = k0 + kq;
+                const int n_ok = gm < M ? max(0, min(4, K - gk)) : 0;
+                cp_async16(as + r * LDK + kq, n_ok ? A + (long long)gm * lda + gk : A, n_ok * 4);
+            } else {
+                const int k = c >> 5, mq = (c & 31) * 4;
+                const int gk = k0 + k, gm = m0 + mq;
+                const int n_ok = gk < K ? max(0, min(4, M - gm)) : 0;
+                cp_async16(as + k * BM + mq, n_ok ? A + (long long)gk * lda + gm : A, n_ok * 4);
+            }
+            if (B_NMAJOR) {
+                const int k = c >> 5, nq = (c & 31) * 4;
+                const int gk = k0 + k, gn = n0 + nq;
+                const int n_ok = gk < K ? max(0, min(4, N - gn)) : 0;
+                cp_async16(bs + k * BN + nq, n_ok ? B + (long long)gk * ldb + gn : B, n_ok * 4);
+            } else {
+                const int r = c >> 2, kq = (c & 3) * 4;
+                const int gn = n0 + r, gk = k0 + kq;
+                const int n_ok = gn < N ? max(0, min(4, K - gk)) : 0;
+                cp_async16(bs + r * LDK + kq, n_ok ? B + (long long)gn * ldb + gk : B, n_ok * 4);
+            }
+        }
+    };
+
+    // Accumulators in pairs of neighbouring columns: one packed fma.rn.f32x2 (two independent, individually rounded
+    // fp32 fused multiply-adds) per pair halves the instructions and the register-file reads of the inner product.
+    float2 acc[8][4];
+    #pragma unroll
+    for (int i = 0; i < 8; ++i)
+        #pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = make_float2(0.0f, 0.0f);
+
+    const int nslices = (K + BK - 1) / BK;
+    #pragma unroll
+    for (int p = 0; p < PSTAGES - 1; ++p) {
+        if (p < nslices) issue(p);
+        cp_async_commit();
+    }
+    for (int s = 0; s < nslices; ++s) {
+        cp_async_wait<PSTAGES - 2>();            // slice s has landed (for this thread's copies)
+        __syncthreads();                         // ... and everybody's; everybody is also done with slice s - 1
+        if (s + PSTAGES - 1 < nslices) issue(s + PSTAGES - 1);     // into the buffer slice s - 1 used
+        cp_async_commit();
+        const float* as = a_stage(s % PSTAGES);
+        const float* bs = b_stage(s % PSTAGES);
+        #pragma unroll
+        for (int k4 = 0; k4 < BK / 4; ++k4) {
+            float4 a4[8], b4[8];
+            if (A_KMAJOR) {
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) a4[i] = *reinterpret_cast<const float4*>(as + ((i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4)) * LDK + k4 * 4);
+            }
+            if (!B_NMAJOR) {
+                #pragma unroll
+                for (int j = 0; j < 8; ++j) b4[j] = *reinterpret_cast<const float4*>(bs + (tx + 16 * j) * LDK + k4 * 4);
+            }
+            #pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                const int k = k4 * 4 + kk;
+                float a[8], b[8];
+                if (A_KMAJOR) {
+                    #pragma unroll
+                    for (int i = 0; i < 8; ++i) a[i] = f4(a4[i], kk);
+                } else {
+                    const float4 a0 = *reinterpret_cast<const float4*>(as + k * BM + ty * 4);
+                    const float4 a1 = *reinterpret_cast<const float4*>(as + k * BM + 64 + ty * 4);
+                    a[0] = a0.x; a[1] = a0.y; a[2] = a0.z; a[3] = a0.w; a[4] = a1.x; a[5] = a1.y; a[6] = a1.z; a[7] = a1.w;
+                }
+                if (B_NMAJOR) {
+                    const float4 b0 = *reinterpret_cast<const float4*>(bs + k * BN + tx * 4);
+                    const float4 b1 = *reinterpret_cast<const float4*>(bs + k * BN + 64 + tx * 4);
+                    b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+                } else {
+                    #pragma unroll
+                    for (int j = 0; j < 8; ++j) b[j] = f4(b4[j], kk);
+                }
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float2 aa = make_float2(a[i], a[i]);
+                    #pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[i][j] = __ffma2_rn(aa, make_float2(b[2 * j], b[2 * j + 1]), acc[i][j]);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    #pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+        if (gm >= M) continue;
+        float* crow = C + (long long)gm * N;
+        if (B_NMAJOR) {
+            #pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int gn = n0 + h * 64 + tx * 4;
+                const float v[4] = {acc[i][2 * h].x, acc[i][2 * h].y, acc[i][2 * h + 1].x, acc[i][2 * h + 1].y};
+                if (gn + 3 < N) *reinterpret_cast<float4*>(crow + gn) = make_float4(v[0], v[1], v[2], v[3]);
+                else {
+                    #pragma unroll
+                    for (int e = 0; e < 4; ++e) if (gn + e < N) crow[gn + e] = v[e];
+                }
+            }
+        } else {
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) { const int gn = n0 + tx + 16 * j; if (gn < N) crow[gn] = (j & 1) ? acc[i][j >> 1].y : acc[i][j >> 1].x; }
+        }
+    }
+}
+
+template <bool AK, bool BN_>
+void launch_pipe(ormi_b200_ctx* ctx, const GemmArgs& g, const BatchMap& bm) {
+    static bool attr_set = false;      // per instantiation
+    if (!attr_set) {
+        ORMI_CUDA(cudaFuncSetAttribute(sgemm_pipe_kernel<AK, BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES));
+        attr_set = true;
+    }
+    dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM, g.batch);
+    sgemm_pipe_kernel<AK, BN_><<<grid, NTHREADS, P_SMEM_BYTES, ctx->stream>>>(g.A, g.B, g.C, g.M, g.N, g.K, g.lda, g.ldb, bm);
+    ORMI_CUDA(cudaGetLastError());
+}
+
 template <bool AK, bool BN_, bool VEC>
 void launch(ormi_b200_ctx* ctx, const GemmArgs& g, const BatchMap& bm) {
     dim3 grid((g.N + BN - 1) / BN, (g.M + BM - 1) / BM, g.batch);
@@ -200,11 +381,11 @@ void gemm_ffma(ormi_b200_ctx* ctx, const GemmArgs& g) {
     for (int d = 0; d < g.nbatch; ++d) if (g.astride[d] % 4 || g.bstride[d] % 4) vec = false;
     if ((long long)g.M * g.N % 4) vec = false;
     const bool ak = !g.trans_a, bn = !g.trans_b;
-    if (vec) {
-        if (ak && bn) launch<true, true, true>(ctx, g, bm);
-        else if (ak && !bn) launch<true, false, true>(ctx, g, bm);
-        else if (!ak && bn) launch<false, true, true>(ctx, g, bm);
-        else launch<false, false, true>(ctx, g, bm);
+    if (vec) {           // rows movable in 16-byte pieces: the pipelined kernel
+        if (ak && bn) launch_pipe<true, true>(ctx, g, bm);
+        else if (ak && !bn) launch_pipe<true, false>(ctx, g, bm);
+        else if (!ak && bn) launch_pipe<false, true>(ctx, g, bm);
+        else launch_pipe<false, false>(ctx, g, bm);
     } else {
         if (ak && bn) launch<true, true, false>(ctx, g, bm);
         else if (ak && !bn) launch<true, false, false>(ctx, g, bm);
