@@ -187,29 +187,63 @@ sgemm_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __
 
 // ---------------------------------------------------------------------------------------------------------------------
 // Pipelined variant for operands whose rows can be moved in 16-byte pieces (the common case): cp.async straight from
-// global into a 4-stage shared-memory ring, no staging registers and no transposing stores.  Each operand keeps the
-// layout it has in memory:
-//   contiguous along k  (A not transposed / B transposed):  Xs[row][k], 20 floats per row; a thread reads one float4
-//                                                           (4 consecutive k) per row of its micro-tile;
-//   contiguous along m/n (A transposed / B not transposed): Xs[k][128]; a thread reads two float4 per k.
-// When B is contiguous along k a thread's 8 columns are tx + 16 j instead of two runs of 4, which keeps the float4
-// reads of 8 neighbouring threads on different banks (row stride 20 floats).
-// One block barrier per k-slice; k ascending inside a thread, fused multiply-add: bit-identical to sgemm_kernel.
-constexpr int PSTAGES = 4, LDK = BK + 4;
-constexpr int P_OPERAND_FLOATS = BM * LDK;                     // 2560 floats; the [k][128] layout needs 2048
+// global into a 4-stage shared-memory ring, no staging registers.  Layouts in shared memory:
+//   operand contiguous along m / n (A transposed, B not transposed): Xs[k][128 (+4)], filled by 16-byte cp.async, read
+//       with two float4 per k;
+//   B contiguous along k (B transposed): the same Xs[k][132]; the 16 bytes of global memory go out as four 4-byte
+//       cp.async to four different k rows — the transposition happens in the copy, not in registers.  Within a warp 16
+//       lanes take 16 neighbouring rows and the two halves neighbouring k quads: the writes cover all 32 banks;
+//   A contiguous along k (A not transposed): As[m][16 (+4)], filled by 16-byte cp.async, read with one scalar load per
+//       row of the micro-tile (all lanes of a warp that share a row read the same word: a broadcast, no conflict) —
+//       the packed multiply-add leaves the issue slots for them.
+// One block barrier per k-slice; k ascending inside a thread; packed fma.rn.f32x2 on pairs of accumulators (two
+// independent, individually rounded fp32 fused multiply-adds): bit-identical to sgemm_kernel.
+constexpr int PSTAGES = 4, LDP = BM + 4, LDK = BK + 4;
+constexpr int P_OPERAND_FLOATS = BM * LDK;                     // 2560 floats; Xs[k][132] needs 2112
 constexpr int P_SMEM_BYTES = PSTAGES * 2 * P_OPERAND_FLOATS * 4;
 
 __device__ __forceinline__ void cp_async16(float* smem_dst, const float* gsrc, int src_bytes) {
     unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(src_bytes) : "memory");
 }
+__device__ __forceinline__ void cp_async4(float* smem_dst, const float* gsrc, int src_bytes) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gsrc), "r"(src_bytes) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-__device__ __forceinline__ float f4(const float4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+// One operand tile (16 k x 128 rows) of slice k0 into Xs[k][row].  X(row, k) = X[row * ld + k] when K_CONTIG, else
+// X[k * ld + row]; rows past `rows` and k past K arrive as zeros.
+// K_CONTIG && DIRECT keeps the memory layout instead: Xs[row][k], 20 floats per row.
+template <bool K_CONTIG, bool DIRECT>
+__device__ __forceinline__ void fill_operand(float* xs, const float* __restrict__ X, int ld, int r0, int rows, int k0, int K, int tid) {
+    #pragma unroll
+    for (int it = 0; it < 2; ++it) {
+        const int c = tid + it * NTHREADS;                      // 512 pieces of 16 bytes
+        if (K_CONTIG && DIRECT) {
+            const int r = c >> 2, kq = (c & 3) * 4;
+            const int gr = r0 + r, gk = k0 + kq;
+            const int n_ok = gr < rows ? max(0, min(4, K - gk)) : 0;
+            cp_async16(xs + r * LDK + kq, n_ok ? X + (long long)gr * ld + gk : X, n_ok * 4);
+        } else if (K_CONTIG) {
+            const int r = (c & 15) | ((c >> 6) << 4), kq = ((c >> 4) & 3) * 4;
+            const int gr = r0 + r, gk = k0 + kq;
+            const int n_ok = gr < rows ? max(0, min(4, K - gk)) : 0;
+            const float* src = n_ok ? X + (long long)gr * ld + gk : X;
+            #pragma unroll
+            for (int e = 0; e < 4; ++e) cp_async4(xs + (kq + e) * LDP + r, e < n_ok ? src + e : X, e < n_ok ? 4 : 0);
+        } else {
+            const int k = c >> 5, rq = (c & 31) * 4;
+            const int gk = k0 + k, gr = r0 + rq;
+            const int n_ok = gk < K ? max(0, min(4, rows - gr)) : 0;
+            cp_async16(xs + k * LDP + rq, n_ok ? X + (long long)gk * ld + gr : X, n_ok * 4);
+        }
+    }
+}
 
 template <bool A_KMAJOR, bool B_NMAJOR>
-__global__ void __launch_bounds__(NTHREADS)
+__global__ void __launch_bounds__(NTHREADS, 2)
 sgemm_pipe_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
                   int M, int N, int K, int lda, int ldb, BatchMap bm) {
     extern __shared__ __align__(16) float psm[];
@@ -230,42 +264,14 @@ sgemm_pipe_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
     const int tx = tid % 16, ty = tid / 16;
     auto a_stage = [&](int st) { return psm + (st * 2) * P_OPERAND_FLOATS; };
     auto b_stage = [&](int st) { return psm + (st * 2 + 1) * P_OPERAND_FLOATS; };
-
-    // one operand tile = 512 pieces of 16 bytes, two per thread
     auto issue = [&](int slice) {
         const int st = slice % PSTAGES, k0 = slice * BK;
-        float* as = a_stage(st);
-        float* bs = b_stage(st);
-        #pragma unroll
-        for (int it = 0; it < 2; ++it) {
-            const int c = tid + it * NTHREADS;
-            if (A_KMAJOR) {
-                const int r = c >> 2, kq = (c & 3) * 4;
-                const int gm = m0 + r, gk = k0 + kq;
-                const int n_ok = gm < M ? max(0, min(4, K - gk)) : 0;
-                cp_async16(as + r * LDK + kq, n_ok ? A + (long long)gm * lda + gk : A, n_ok * 4);
-            } else {
-                const int k = c >> 5, mq = (c & 31) * 4;
-                const int gk = k0 + k, gm = m0 + mq;
-                const int n_ok = gk < K ? max(0, min(4, M - gm)) : 0;
-                cp_async16(as + k * BM + mq, n_ok ? A + (long long)gk * lda + gm : A, n_ok * 4);
-            }
-            if (B_NMAJOR) {
-                const int k = c >> 5, nq = (c & 31) * 4;
-                const int gk = k0 + k, gn = n0 + nq;
-                const int n_ok = gk < K ? max(0, min(4, N - gn)) : 0;
-                cp_async16(bs + k * BN + nq, n_ok ? B + (long long)gk * ldb + gn : B, n_ok * 4);
-            } else {
-                const int r = c >> 2, kq = (c & 3) * 4;
-                const int gn = n0 + r, gk = k0 + kq;
-                const int n_ok = gn < N ? max(0, min(4, K - gk)) : 0;
-                cp_async16(bs + r * LDK + kq, n_ok ? B + (long long)gn * ldb + gk : B, n_ok * 4);
-            }
-        }
+        fill_operand<A_KMAJOR, true>(a_stage(st), A, lda, m0, M, k0, K, tid);
+        fill_operand<!B_NMAJOR, false>(b_stage(st), B, ldb, n0, N, k0, K, tid);
     };
 
-    // Accumulators in pairs of neighbouring columns: one packed fma.rn.f32x2 (two independent, individually rounded
-    // fp32 fused multiply-adds) per pair halves the instructions and the register-file reads of the inner product.
+    // Accumulators in pairs of neighbouring columns: one packed instruction per pair halves the instructions and the
+    // register-file reads of the inner product.
     float2 acc[8][4];
     #pragma unroll
     for (int i = 0; i < 8; ++i)
@@ -286,42 +292,24 @@ sgemm_pipe_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
         const float* as = a_stage(s % PSTAGES);
         const float* bs = b_stage(s % PSTAGES);
         #pragma unroll
-        for (int k4 = 0; k4 < BK / 4; ++k4) {
-            float4 a4[8], b4[8];
+        for (int k = 0; k < BK; ++k) {
+            float a[8];
             if (A_KMAJOR) {
                 #pragma unroll
-                for (int i = 0; i < 8; ++i) a4[i] = *reinterpret_cast<const float4*>(as + ((i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4)) * LDK + k4 * 4);
+                for (int i = 0; i < 8; ++i) a[i] = as[(i < 4 ? ty * 4 + i : 64 + ty * 4 + i - 4) * LDK + k];
+            } else {
+                const float4 a0 = *reinterpret_cast<const float4*>(as + k * LDP + ty * 4);
+                const float4 a1 = *reinterpret_cast<const float4*>(as + k * LDP + 64 + ty * 4);
+                a[0] = a0.x; a[1] = a0.y; a[2] = a0.z; a[3] = a0.w; a[4] = a1.x; a[5] = a1.y; a[6] = a1.z; a[7] = a1.w;
             }
-            if (!B_NMAJOR) {
-                #pragma unroll
-                for (int j = 0; j < 8; ++j) b4[j] = *reinterpret_cast<const float4*>(bs + (tx + 16 * j) * LDK + k4 * 4);
-            }
+            const float4 b0 = *reinterpret_cast<const float4*>(bs + k * LDP + tx * 4);
+            const float4 b1 = *reinterpret_cast<const float4*>(bs + k * LDP + 64 + tx * 4);
+            const float2 b2[4] = {make_float2(b0.x, b0.y), make_float2(b0.z, b0.w), make_float2(b1.x, b1.y), make_float2(b1.z, b1.w)};
             #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-                const int k = k4 * 4 + kk;
-                float a[8], b[8];
-                if (A_KMAJOR) {
-                    #pragma unroll
-                    for (int i = 0; i < 8; ++i) a[i] = f4(a4[i], kk);
-                } else {
-                    const float4 a0 = *reinterpret_cast<const float4*>(as + k * BM + ty * 4);
-                    const float4 a1 = *reinterpret_cast<const float4*>(as + k * BM + 64 + ty * 4);
-                    a[0] = a0.x; a[1] = a0.y; a[2] = a0.z; a[3] = a0.w; a[4] = a1.x; a[5] = a1.y; a[6] = a1.z; a[7] = a1.w;
-                }
-                if (B_NMAJOR) {
-                    const float4 b0 = *reinterpret_cast<const float4*>(bs + k * BN + tx * 4);
-                    const float4 b1 = *reinterpret_cast<const float4*>(bs + k * BN + 64 + tx * 4);
-                    b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w; b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
-                } else {
-                    #pragma unroll
-                    for (int j = 0; j < 8; ++j) b[j] = f4(b4[j], kk);
-                }
+            for (int i = 0; i < 8; ++i) {
+                const float2 aa = make_float2(a[i], a[i]);
                 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float2 aa = make_float2(a[i], a[i]);
-                    #pragma unroll
-                    for (int j = 0; j < 4; ++j) acc[i][j] = __ffma2_rn(aa, make_float2(b[2 * j], b[2 * j + 1]), acc[i][j]);
-                }
+                for (int j = 0; j < 4; ++j) acc[i][j] = __ffma2_rn(aa, b2[j], acc[i][j]);
             }
         }
     }
@@ -332,20 +320,15 @@ sgemm_pipe_kernel(const float* __restrict__ A, const float* __restrict__ B, floa
         const int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
         if (gm >= M) continue;
         float* crow = C + (long long)gm * N;
-        if (B_NMAJOR) {
-            #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int gn = n0 + h * 64 + tx * 4;
-                const float v[4] = {acc[i][2 * h].x, acc[i][2 * h].y, acc[i][2 * h + 1].x, acc[i][2 * h + 1].y};
-                if (gn + 3 < N) *reinterpret_cast<float4*>(crow + gn) = make_float4(v[0], v[1], v[2], v[3]);
-                else {
-                    #pragma unroll
-                    for (int e = 0; e < 4; ++e) if (gn + e < N) crow[gn + e] = v[e];
-                }
+        #pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int gn = n0 + h * 64 + tx * 4;
+            const float v[4] = {acc[i][2 * h].x, acc[i][2 * h].y, acc[i][2 * h + 1].x, acc[i][2 * h + 1].y};
+            if (gn + 3 < N) *reinterpret_cast<float4*>(crow + gn) = make_float4(v[0], v[1], v[2], v[3]);
+            else {
+                #pragma unroll
+                for (int e = 0; e < 4; ++e) if (gn + e < N) crow[gn + e] = v[e];
             }
-        } else {
-            #pragma unroll
-            for (int j = 0; j < 8; ++j) { const int gn = n0 + tx + 16 * j; if (gn < N) crow[gn] = (j & 1) ? acc[i][j >> 1].y : acc[i][j >> 1].x; }
         }
     }
 }
