@@ -301,12 +301,12 @@ def run_only(args):
         emit((dict(res, only=args.only, rows=args.rows)))
         dev.close()
         return
-    if args.only in ("gemm_bf16", "gemm_fp32"):
+    if args.only.startswith("gemm_"):
         # C = A @ B at M = N = K = --rows (default 8192 is too long under a profiler: use --rows 4096)
         n = args.rows
         a = dev.leaf(W.normal(0, (n, n), 1 / math.sqrt(n)))
         b = dev.leaf(W.normal(1, (n, n), 1 / math.sqrt(n)))
-        dev.set_option("matmul", "bf16" if args.only == "gemm_bf16" else "fp32")
+        dev.set_option("matmul", args.only[len("gemm_"):])      # fp32 | bf16 | tf32 | 3xtf32
         runner = StepRunner(dev, G, [[G.matmul(a, b)]])
         for _ in range(args.warmup):
             runner.run()
@@ -344,7 +344,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, choices=["softmax", "softmax_stable", "layernorm", "rowsum", "gemm_bf16", "gemm_fp32", "mlp_bf16", "mlp_fp32"],
+    ap.add_argument("--only", default=None, choices=["softmax", "softmax_stable", "layernorm", "rowsum", "gemm_bf16", "gemm_fp32", "gemm_tf32", "gemm_3xtf32", "mlp_bf16", "mlp_fp32"],
                     help="profiling aid: run just this graph --steps times on --rows rows and exit")
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--no-extras", action="store_true", help="skip the matmul sweep and the MLP training steps")

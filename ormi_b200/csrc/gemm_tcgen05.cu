@@ -311,9 +311,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 //   anything else (or unaligned): scalar loads through shared memory.
 // One launch serves both operands of a GEMM: the first `a.blocks` blocks work on job a, the rest on job b.
 struct CvtJob {
-    const float* src; long long s_row, s_k; int rows, K, Kp; __nv_bfloat16* dst;
+    const float* src; long long s_row, s_k; int rows, K, Kp; void* dst;
     int blocks_x, blocks;        // 64 x 64 tiles along k, and in total
     int mode;                    // 0 k-contiguous vector path, 1 row-contiguous vector path, 2 scalar
+    int is_b;                    // tf32 split only: a B operand stores (hi, lo, hi), an A operand (hi, hi, lo)
 };
 
 constexpr int CT = 64;           // tile edge
@@ -323,6 +324,33 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ float to_tf32(float x) { uint32_t r; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x)); return __uint_as_float(r); }
+
+// Eight consecutive k of row r, starting at k.  PARTS = 0: bf16, one 16-byte store.  PARTS = 1: fp32 words rounded to
+// tf32.  PARTS = 3 (the "3xTF32" split): hi = tf32(x), lo = tf32(x - hi) stored at k, Kp + k, 2 Kp + k as (hi, hi, lo)
+// for an A operand and (hi, lo, hi) for a B operand, so that one GEMM over 3 Kp columns adds up
+// A_hi B_hi + A_hi B_lo + A_lo B_hi — fp32 products to about 2^-22.
+template <int PARTS>
+__device__ __forceinline__ void store8(const CvtJob& j, int r, int k, const float* v) {
+    if (PARTS == 0) {
+        uint4 o = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(j.dst) + (size_t)r * j.Kp + k) = o;
+    } else {
+        if (k >= j.Kp) return;                                   // Kp is a multiple of 32 here, the tile is 64 wide
+        float* row = static_cast<float*>(j.dst) + (size_t)r * j.Kp * PARTS + k;
+        float hi[8], lo[8];
+        #pragma unroll
+        for (int i = 0; i < 8; ++i) { hi[i] = to_tf32(v[i]); lo[i] = PARTS == 3 ? to_tf32(v[i] - hi[i]) : 0.0f; }
+        auto put = [&](float* p, const float* w) {
+            *reinterpret_cast<float4*>(p) = make_float4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<float4*>(p + 4) = make_float4(w[4], w[5], w[6], w[7]);
+        };
+        put(row, hi);
+        if (PARTS == 3) { put(row + j.Kp, j.is_b ? lo : hi); put(row + 2 * j.Kp, j.is_b ? hi : lo); }
+    }
+}
+
+template <int PARTS>
 __global__ void __launch_bounds__(256)
 cvt_kmajor(const CvtJob a, const CvtJob b) {
     __shared__ float tile[CT][CT + 1];                           // [k][row]
@@ -350,8 +378,7 @@ cvt_kmajor(const CvtJob a, const CvtJob b) {
                 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = (k + i < j.K) ? src[r * j.s_row + k + i] : 0.0f;
             }
-            uint4 o = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-            *reinterpret_cast<uint4*>(j.dst + (size_t)r * j.Kp + k) = o;
+            store8<PARTS>(j, r, k, v);
         }
         return;
     }
@@ -387,61 +414,12 @@ cvt_kmajor(const CvtJob a, const CvtJob b) {
         float v[8];
         #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = tile[8 * kseg + i][rt];
-        uint4 o = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-        *reinterpret_cast<uint4*>(j.dst + (size_t)r * j.Kp + k0 + 8 * kseg) = o;
+        store8<PARTS>(j, r, k0 + 8 * kseg, v);
     }
 }
 
-// tf32 staging: dst is rows x ld fp32 words.  PARTS = 1: dst[r][k] = tf32(x).  PARTS = 3 (the "3xTF32" split):
-// hi = tf32(x), lo = tf32(x - hi); an A operand stores (hi, hi, lo) and a B operand (hi, lo, hi) at k, Kp + k, 2 Kp + k, so
-// that one GEMM over 3 Kp columns adds up  A_hi B_hi + A_hi B_lo + A_lo B_hi  — fp32 products to about 2^-22.
-__device__ __forceinline__ float to_tf32(float x) { uint32_t r; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x)); return __uint_as_float(r); }
-
-template <bool SRC_K_CONTIG>
-__global__ void __launch_bounds__(256)
-cvt_kmajor_tf32(const float* __restrict__ src, long long s_row, long long s_k, int rows, int K, int Kp, float* __restrict__ dst,
-                int parts, int is_b) {
-    __shared__ float tile[32][33];
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const int r0 = blockIdx.y * 32, k0 = blockIdx.x * 32;
-    #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        if (SRC_K_CONTIG) {
-            const int r = r0 + ty + 8 * j, k = k0 + tx;
-            tile[ty + 8 * j][tx] = (r < rows && k < K) ? src[r * s_row + k * s_k] : 0.0f;
-        } else {
-            const int r = r0 + tx, k = k0 + ty + 8 * j;
-            tile[tx][ty + 8 * j] = (r < rows && k < K) ? src[r * s_row + k * s_k] : 0.0f;
-        }
-    }
-    __syncthreads();
-    const size_t ld = (size_t)Kp * parts;
-    #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int r = r0 + ty + 8 * j, k = k0 + tx;
-        if (r >= rows || k >= Kp) continue;
-        const float x = tile[ty + 8 * j][tx];
-        const float hi = to_tf32(x);
-        float* row = dst + (size_t)r * ld;
-        row[k] = hi;
-        if (parts == 3) {
-            const float lo = to_tf32(x - hi);
-            row[Kp + k] = is_b ? lo : hi;
-            row[2 * Kp + k] = is_b ? hi : lo;
-        }
-    }
-}
-
-void convert_tf32(ormi_b200_ctx* ctx, const float* src, long long s_row, long long s_k, int rows, int K, int Kp, float* dst, int parts, int is_b) {
-    dim3 grid((Kp + 31) / 32, (rows + 31) / 32);
-    if (s_k == 1) cvt_kmajor_tf32<true><<<grid, 256, 0, ctx->stream>>>(src, s_row, s_k, rows, K, Kp, dst, parts, is_b);
-    else cvt_kmajor_tf32<false><<<grid, 256, 0, ctx->stream>>>(src, s_row, s_k, rows, K, Kp, dst, parts, is_b);
-    ORMI_CUDA(cudaGetLastError());
-    ctx->counters["launches"]++;
-}
-
-CvtJob cvt_job(const float* src, long long s_row, long long s_k, int rows, int K, int Kp, __nv_bfloat16* dst) {
-    CvtJob j{src, s_row, s_k, rows, K, Kp, dst, (Kp + CT - 1) / CT, 0, 2};
+CvtJob cvt_job(const float* src, long long s_row, long long s_k, int rows, int K, int Kp, void* dst, int is_b = 0) {
+    CvtJob j{src, s_row, s_k, rows, K, Kp, dst, (Kp + CT - 1) / CT, 0, 2, is_b};
     j.blocks = j.blocks_x * ((rows + CT - 1) / CT);
     const bool aligned = ((uintptr_t)src & 15) == 0;
     if (s_k == 1 && aligned && s_row % 4 == 0) j.mode = 0;
@@ -449,8 +427,10 @@ CvtJob cvt_job(const float* src, long long s_row, long long s_k, int rows, int K
     return j;
 }
 
-void convert(ormi_b200_ctx* ctx, const CvtJob& a, const CvtJob& b) {
-    cvt_kmajor<<<a.blocks + b.blocks, 256, 0, ctx->stream>>>(a, b);
+void convert(ormi_b200_ctx* ctx, const CvtJob& a, const CvtJob& b, int parts = 0) {
+    if (parts == 0) cvt_kmajor<0><<<a.blocks + b.blocks, 256, 0, ctx->stream>>>(a, b);
+    else if (parts == 1) cvt_kmajor<1><<<a.blocks + b.blocks, 256, 0, ctx->stream>>>(a, b);
+    else cvt_kmajor<3><<<a.blocks + b.blocks, 256, 0, ctx->stream>>>(a, b);
     ORMI_CUDA(cudaGetLastError());
     ctx->counters["launches"]++;
 }
@@ -523,8 +503,8 @@ void gemm_tf32(ormi_b200_ctx* ctx, const GemmArgs& g, int parts) {
     const size_t ld = (size_t)Kp * parts;
     float* a32 = (float*)stage_buffer(ctx, 0, (size_t)g.M * ld * 4);
     float* b32 = (float*)stage_buffer(ctx, 1, (size_t)g.N * ld * 4);
-    convert_tf32(ctx, g.A, g.trans_a ? 1 : g.lda, g.trans_a ? g.lda : 1, g.M, g.K, Kp, a32, parts, 0);
-    convert_tf32(ctx, g.B, g.trans_b ? g.ldb : 1, g.trans_b ? 1 : g.ldb, g.N, g.K, Kp, b32, parts, 1);
+    convert(ctx, cvt_job(g.A, g.trans_a ? 1 : g.lda, g.trans_a ? g.lda : 1, g.M, g.K, Kp, a32, 0),
+            cvt_job(g.B, g.trans_b ? g.ldb : 1, g.trans_b ? 1 : g.ldb, g.N, g.K, Kp, b32, 1), parts);
     CUtensorMap map_a, map_b;
     make_map(ctx, &map_a, a32, g.M, (int)ld, BM, true);
     make_map(ctx, &map_b, b32, g.N, (int)ld, BN, true);
