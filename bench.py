@@ -35,9 +35,9 @@ WORKLOAD = "configs[1]: row softmax + layernorm, forward + autograd backward, x[
 BYTES_SOFTMAX = 4 * R * C * 4
 BYTES_LAYERNORM = 4 * R * C * 4 + 4 * C * 4
 BYTES_STEP = BYTES_SOFTMAX + BYTES_LAYERNORM
-# DRAM traffic of the dominant kernel from its ncu capture (profiles/rows_layernorm_fwd_bwd_8192x4096.md): 270.5 MB read +
-# 227.1 MB written per launch over 8192 rows; the traffic is proportional to the rows, the bench launch covers 16384.
-LN_TRAFFIC_BYTES = 2 * (270_478_080 + 227_138_048)
+# DRAM traffic of the dominant kernel from its ncu capture (profiles/rows_layernorm_fwd_bwd_8192x4096.md): 269.5 MB read +
+# 225.4 MB written per launch over 8192 rows; the traffic is proportional to the rows, the bench launch covers 16384.
+LN_TRAFFIC_BYTES = 2 * (269_485_568 + 225_356_800)
 
 
 _REAL_STDOUT = None
@@ -518,7 +518,7 @@ def main():
             "roofline": {"bound": "hbm", "kernel": "fused layernorm forward+backward (rows template) + 2 finalize launches",
                          "achieved": ln_gbps, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": ln_gbps / peak,
                          "traffic": LN_TRAFFIC_BYTES, "traffic_unit": "bytes per launch",
-                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 8192 rows (497.6 MB), times 2 for 16384 rows",
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 8192 rows (494.8 MB), times 2 for 16384 rows",
                          "algorithmic_bytes": BYTES_LAYERNORM, "softmax_kernel_gbps": sm_gbps},
             "cpu_baseline": {"value": cpu_gbps, "unit": UNIT, "cores": cores, "kind": kind,
                              "sample": f"2048 of {R} rows, one run ({cpu_secs:.1f} s), autograd + realize on the reference CPU backend"},
