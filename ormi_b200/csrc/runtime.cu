@@ -14,6 +14,9 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <sys/stat.h>
+#include <unistd.h>
+
 #include "context.h"
 
 namespace ormi_b200 {
@@ -106,10 +109,66 @@ std::vector<char> compile_cubin(const std::string& source, std::string* log_out)
     return cubin;
 }
 
+// On-disk cache of compiled kernels, so that a new process does not pay NVRTC (some 0.3-1 s per generated kernel) for
+// sources an earlier process already compiled.  Directory: $ORMI_B200_CACHE_DIR ("off" disables the cache), else
+// $XDG_CACHE_HOME/ormi_b200, else $HOME/.cache/ormi_b200.  A file is named after two independent hashes of the source,
+// its length and the compiler version; it is written to a temporary name and renamed, so readers never see half a file.
+static std::string cubin_cache_dir() {
+    const char* d = std::getenv("ORMI_B200_CACHE_DIR");
+    if (d) return std::string(d) == "off" ? std::string() : std::string(d);
+    if (const char* x = std::getenv("XDG_CACHE_HOME")) return std::string(x) + "/ormi_b200";
+    if (const char* h = std::getenv("HOME")) return std::string(h) + "/.cache/ormi_b200";
+    return std::string();
+}
+
+static std::string cubin_cache_path(const std::string& source) {
+    const std::string dir = cubin_cache_dir();
+    if (dir.empty()) return dir;
+    uint64_t h2 = 0x9e3779b97f4a7c15ull;                       // a second, different mix of the same bytes
+    for (unsigned char c : source) { h2 = (h2 ^ c) * 0x100000001b3ull; h2 ^= h2 >> 29; }
+    int major = 0, minor = 0;
+    nvrtcVersion(&major, &minor);
+    char name[160];
+    snprintf(name, sizeof name, "/k_%016llx_%016llx_%zu_nvrtc%d.%d_sm100a_v1.cubin", (unsigned long long)fnv1a(source),
+             (unsigned long long)h2, source.size(), major, minor);
+    return dir + name;
+}
+
+static bool read_file(const std::string& path, std::vector<char>& out) {
+    FILE* f = fopen(path.c_str(), "rb");
+    if (!f) return false;
+    fseek(f, 0, SEEK_END);
+    long n = ftell(f);
+    fseek(f, 0, SEEK_SET);
+    bool ok = n > 0;
+    if (ok) { out.resize((size_t)n); ok = fread(out.data(), 1, (size_t)n, f) == (size_t)n; }
+    fclose(f);
+    return ok;
+}
+
+static void write_file_atomically(const std::string& path, const std::vector<char>& data) {
+    const std::string dir = path.substr(0, path.rfind('/'));
+    for (size_t i = 1; i <= dir.size(); ++i)                    // mkdir -p
+        if (i == dir.size() || dir[i] == '/') mkdir(dir.substr(0, i).c_str(), 0755);
+    const std::string tmp = path + ".tmp" + std::to_string((long long)getpid());
+    FILE* f = fopen(tmp.c_str(), "wb");
+    if (!f) return;                                            // the cache is best effort: a read-only home is not an error
+    const bool ok = fwrite(data.data(), 1, data.size(), f) == data.size();
+    fclose(f);
+    if (!ok || rename(tmp.c_str(), path.c_str()) != 0) remove(tmp.c_str());
+}
+
 CompiledKernel* get_kernel(ormi_b200_ctx* ctx, const KernelStep& k) {
     auto it = ctx->kernel_cache.find(k.key + ":" + k.name);
     if (it != ctx->kernel_cache.end()) { ctx->counters["kernel_cache_hits"]++; return &it->second; }
-    std::vector<char> cubin = compile_cubin(k.source);
+    std::vector<char> cubin;
+    const std::string disk = std::getenv("ORMI_B200_NVRTC_LOG") ? std::string() : cubin_cache_path(k.source);
+    if (!disk.empty() && read_file(disk, cubin)) ctx->counters["cubin_disk_hits"]++;
+    else {
+        cubin = compile_cubin(k.source);
+        ctx->counters["nvrtc_compiles"]++;
+        if (!disk.empty()) write_file_atomically(disk, cubin);
+    }
     CompiledKernel ck;
     ctx->drv.check(ctx->drv.ModuleLoadData(&ck.module, cubin.data()), "cuModuleLoadData");
     ctx->drv.check(ctx->drv.ModuleGetFunction(&ck.func, ck.module, k.name.c_str()), "cuModuleGetFunction");

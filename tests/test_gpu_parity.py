@@ -392,3 +392,34 @@ def test_ragged_shapes(device, shape):
     y.grad = G.leaf(W.normal(3, (R, C)))
     G.compute_gradients(y)
     check(device, [y, x.grad, g.grad, b.grad, W.softmax(x), G.sum_(x, [0], False), G.sum_(x, [1], True), G.sum_(x, [], False)], 5 * REDUCE_TOL)
+
+
+def test_compiled_kernels_are_cached_on_disk(tmp_path, monkeypatch):
+    """A second context (a new process would be the same) finds the cubins of the first on disk and does not call NVRTC."""
+    import os
+    from ormi_b200.runtime import Device
+    monkeypatch.setenv("ORMI_B200_CACHE_DIR", str(tmp_path / "cubins"))
+    x_h = W.normal(0, (48, 160), math.sqrt(2.0))
+
+    def run():
+        dev = Device(0)
+        try:
+            x = dev.leaf(x_h, requires_grad=True)
+            y = W.softmax(x)
+            y.grad = dev.leaf(W.normal(1, (48, 160)))
+            G.compute_gradients(y)
+            out = [dev.numpy(y).copy(), dev.numpy(x.grad).copy()]
+            return out, dev.counter("nvrtc_compiles"), dev.counter("cubin_disk_hits")
+        finally:
+            dev.close()
+
+    first, compiled1, hits1 = run()
+    files = os.listdir(tmp_path / "cubins")
+    assert compiled1 >= 1 and hits1 == 0 and len(files) == compiled1 and all(f.endswith(".cubin") for f in files)
+    second, compiled2, hits2 = run()
+    assert compiled2 == 0 and hits2 == compiled1
+    for a, b in zip(first, second):
+        np.testing.assert_array_equal(a, b)
+    monkeypatch.setenv("ORMI_B200_CACHE_DIR", "off")
+    _, compiled3, hits3 = run()
+    assert compiled3 == compiled1 and hits3 == 0
