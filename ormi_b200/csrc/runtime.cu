@@ -170,7 +170,13 @@ CompiledKernel* get_kernel(ormi_b200_ctx* ctx, const KernelStep& k) {
         if (!disk.empty()) write_file_atomically(disk, cubin);
     }
     CompiledKernel ck;
-    ctx->drv.check(ctx->drv.ModuleLoadData(&ck.module, cubin.data()), "cuModuleLoadData");
+    if (ctx->drv.ModuleLoadData(&ck.module, cubin.data()) != CUDA_SUCCESS) {
+        // a file from the disk cache that the driver does not take (another driver, a damaged file): compile afresh
+        cubin = compile_cubin(k.source);
+        ctx->counters["nvrtc_compiles"]++;
+        if (!disk.empty()) write_file_atomically(disk, cubin);
+        ctx->drv.check(ctx->drv.ModuleLoadData(&ck.module, cubin.data()), "cuModuleLoadData");
+    }
     ctx->drv.check(ctx->drv.ModuleGetFunction(&ck.func, ck.module, k.name.c_str()), "cuModuleGetFunction");
     if (k.dyn_smem > 0)     // static shared memory counts against the 48 KB default too: always raise the limit
         ctx->drv.check(ctx->drv.FuncSetAttribute(ck.func, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, k.dyn_smem), "cuFuncSetAttribute");
