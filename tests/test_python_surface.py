@@ -19,6 +19,7 @@ except ImportError as e:          # a checkout without the ormi-core sources can
     pytest.skip(str(e), allow_module_level=True)
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.environ.get("ORMI_REFERENCE", "/root/reference")      # the ormi checkout, where there is one
 DEVICES = ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)]
 PW_TOL, REDUCE_TOL = 1e-6, 1e-5
 
@@ -149,17 +150,17 @@ def test_fused_graphs_cuda_against_cpu_device():
         assert rel(g, w) <= 3 * REDUCE_TOL
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/ormi-core/tests"), reason="needs the ormi checkout")
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "ormi-core", "tests")), reason="needs the ormi checkout")
 def test_ormi_core_python_tests_on_cpu_device():
     """ormi-core's own Python package and tests (read where they lie, CPU device only here) on top of the module built
     in this repository."""
     code = (
         "import sys; sys.dont_write_bytecode = True\n"
-        f"sys.path[:0] = ['/root/reference/ormi-core/src', {ROOT!r}]\n"
+        f"sys.path[:0] = [{os.path.join(REF, 'ormi-core', 'src')!r}, {ROOT!r}]\n"
         "from ormi_b200 import tensor as T\n"
         "sys.modules['ormi_core._ext.ormi_backend'] = T.backend\n"
         "import pytest\n"
-        "sys.exit(pytest.main(['/root/reference/ormi-core/tests/test_tensor.py', '-q', '-k', 'cpu', '-p', 'no:cacheprovider',"
+        f"sys.exit(pytest.main([{os.path.join(REF, 'ormi-core', 'tests', 'test_tensor.py')!r}, '-q', '-k', 'cpu', '-p', 'no:cacheprovider',"
         " '--rootdir', '/tmp', '-c', '/dev/null']))\n"
     )
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd="/tmp")
