@@ -166,3 +166,20 @@ def test_ormi_core_python_tests_on_cpu_device():
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd="/tmp")
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
     assert " passed" in out.stdout
+
+
+@pytest.mark.gpu
+def test_example_scenarios_on_cuda():
+    """The scenarios of ormi-core's example scripts (example/test_graph.py:5-15: a pointwise chain over an odd-sized
+    [2029, 1202] tensor; example/test_matmul.py:7-18: a [2, 3] @ [3, 1] graph break), on device="cuda"."""
+    rng = np.random.default_rng(5)
+    x_h, w_h, b_h = (rng.random((2029, 1202)).astype(np.float32) for _ in range(3))
+    X, Wt, b = (Tensor(v, device="cuda") for v in (x_h, w_h, b_h))
+    Z = (Wt * (X ** 2.0)) + b
+    Z.realize()
+    assert rel(Z.numpy(), w_h.astype(np.float64) * x_h.astype(np.float64) ** 2 + b_h) <= PW_TOL
+    Wm = Tensor(np.array([[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]], dtype=np.float32), device="cuda")
+    Xm = Tensor(np.array([[1.0], [2.0], [3.0]], dtype=np.float32), device="cuda")
+    Zm = Wm @ Xm
+    assert Zm.shape == (2, 1)
+    np.testing.assert_array_equal(Zm.numpy(), [[14.0], [32.0]])
