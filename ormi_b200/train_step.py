@@ -150,6 +150,7 @@ class MLPTrainer:
             p.add_phase([up["w1"], up["b1"]])                    # U1
             self._pending = None          # (dW2, db2) of the last step, still to be applied
         self.loss_ptr = None
+        self.steps_done = 0
         self._initial = set(self.names)   # parameters still in the buffers the constructor uploaded
         # the build pass above already ran one step worth of kernels but did not move the parameters
         dev.sync()
@@ -224,7 +225,7 @@ class MLPTrainer:
         if self.loss_ptr is not None:
             dev.free(*self.loss_ptr)
         self.loss_ptr = loss
-        self.steps_done = getattr(self, "steps_done", 0) + 1
+        self.steps_done += 1
 
     def flush(self):
         """Applies the update a multi-rank step leaves pending (W2, b2), so that `parameter` sees step-complete values."""
