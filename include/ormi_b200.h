@@ -190,6 +190,13 @@ int ormi_b200_colsum_static(const float* in, int64_t rows, int64_t cols, float* 
 /* Matmul arithmetic used by ormi_b200_realize / ormi_b200_matmul (additive knob; the reference has none):
  * "fp32" (SIMT FFMA, default), "bf16" (tcgen05, fp32 accumulate), "tf32", "3xtf32". Key "matmul".
  * Key "fusion": "on" (default) / "off" (one kernel per node, like the reference scheduler). */
+/* Self-test of the device-side bounded waits (no counterpart in the reference): queues a one-warp kernel that waits on a
+ * barrier nobody arrives on, with a limit of `limit_ms` (1..1000).  The wait gives up, the kernel returns, and the next
+ * ormi_b200_sync / ormi_b200_memcpy_d2h fails once with "a bounded device-side wait ran out (code 9 ...)"; the
+ * context stays usable.  This is how the error path of the tensor-core GEMM and of the staged row kernels is exercised
+ * without faulting or hanging a GPU. */
+int ormi_b200_selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms);
+
 int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value);
 
 /* Counters since init: "kernels_compiled", "kernel_cache_hits", "plan_cache_hits", "launches",

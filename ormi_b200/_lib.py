@@ -50,6 +50,7 @@ _SIGNATURES = {
     "ormi_b200_comm_mark": (c_int, [c_void_p, c_int]),
     "ormi_b200_comm_wait": (c_int, [c_void_p, c_int]),
     "ormi_b200_comm_destroy": (c_int, [c_void_p]),
+    "ormi_b200_selftest_wait_timeout": (c_int, [c_void_p, c_int]),
     "ormi_b200_set_option": (c_int, [c_void_p, c_char_p, c_char_p]),
     "ormi_b200_get_counter": (c_int, [c_void_p, c_char_p, P(ctypes.c_int64)]),
 }

@@ -276,6 +276,10 @@ int ormi_b200_comm_destroy(ormi_b200_ctx* ctx) {
     return guarded([&] { need(ctx != nullptr, "ctx is NULL"); comm_destroy(ctx); });
 }
 
+int ormi_b200_selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms) {
+    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); ORMI_CUDA(cudaSetDevice(ctx->device)); selftest_wait_timeout(ctx, limit_ms); });
+}
+
 int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value) {
     return guarded([&] {
         need(ctx && key && value, "ormi_b200_set_option: NULL argument");

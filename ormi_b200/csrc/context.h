@@ -111,6 +111,7 @@ void gemm_ffma(ormi_b200_ctx* ctx, const GemmArgs& g);
 void gemm_dispatch(ormi_b200_ctx* ctx, const GemmArgs& g);
 void gemm_bf16(ormi_b200_ctx* ctx, const GemmArgs& g);
 void gemm_tf32(ormi_b200_ctx* ctx, const GemmArgs& g, int parts);   // parts = 1: tf32, 3: 3xTF32 split
+void selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms);   // queues a wait that must run out (code 9)
 void check_gemm_error(ormi_b200_ctx* ctx);   // throws when the tensor-core kernel reported a wait that ran out
 void gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, float* C, int M, int N, int Kp);
 void cvt_bf16_kmajor(ormi_b200_ctx* ctx, const float* src, long long s_row, long long s_k, int rows, int K, void* dst);

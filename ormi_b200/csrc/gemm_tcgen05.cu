@@ -66,14 +66,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false when the block is aborting (this wait ran out, or another role's did).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
         for (int i = 0; i < 64; ++i) if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (global_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; atomicCAS(err, 0, code); return false; }
+        if (global_ns() - t0 > limit_ns) { *abort_flag = 1; atomicCAS(err, 0, code); return false; }
     }
+}
+
+// Self-test of the bounded wait: a barrier nobody ever arrives on.  The wait gives up after `limit_ns`, leaves code 9 in
+// the error word and the kernel returns; nothing faults and the context stays usable.
+__global__ void wait_timeout_selftest_kernel(int* err, unsigned long long limit_ns) {
+    __shared__ unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0u, &abort_flag, err, 9, limit_ns);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
@@ -530,6 +545,14 @@ void cvt_bf16_kmajor(ormi_b200_ctx* ctx, const float* src, long long s_row, long
     convert(ctx, cvt_job(src, s_row, s_k, rows, K, (K + BK - 1) / BK * BK, (__nv_bfloat16*)dst), none);
 }
 
+void selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms) {
+    if (limit_ms < 1 || limit_ms > 1000) throw Error("selftest_wait_timeout: limit must be 1..1000 ms");
+    int* err = device_error_word(ctx);
+    wait_timeout_selftest_kernel<<<1, 32, 0, ctx->stream>>>(err, (unsigned long long)limit_ms * 1000000ull);
+    ORMI_CUDA(cudaGetLastError());
+    ctx->gemm_err_pending = true;
+}
+
 // Called at host-visible boundaries (sync, device -> host copies): a bounded wait that ran out inside the tensor-core
 // kernel left a code in the error word.
 void check_gemm_error(ormi_b200_ctx* ctx) {
@@ -542,7 +565,7 @@ void check_gemm_error(ormi_b200_ctx* ctx) {
         // a block that gave up may not have drawn its last index: put the tile counter pair back to zero as well
         ORMI_CUDA(cudaMemsetAsync(ctx->gemm_err, 0, kErrorWords * sizeof(int), ctx->stream));
         throw Error("a bounded device-side wait ran out (code " + std::to_string(code) +
-                    ": tensor-core GEMM 1 producer, 2 accumulator, 3 operands, 4 epilogue, 5-7 tile ring; 101 staged row kernel)");
+                    ": tensor-core GEMM 1 producer, 2 accumulator, 3 operands, 4 epilogue, 5-7 tile ring; 9 self-test; 101 staged row kernel)");
     }
 }
 

@@ -423,3 +423,21 @@ def test_compiled_kernels_are_cached_on_disk(tmp_path, monkeypatch):
     monkeypatch.setenv("ORMI_B200_CACHE_DIR", "off")
     _, compiled3, hits3 = run()
     assert compiled3 == compiled1 and hits3 == 0
+
+
+def test_bounded_wait_gives_up_and_reports(device):
+    """A device-side wait that nothing completes runs out after its limit: the kernel returns, the next sync reports it
+    once, and the context keeps working.  (The same routine guards every mbarrier wait of the tensor-core GEMM.)"""
+    import time
+    from ormi_b200._lib import lib, check
+    check(lib.ormi_b200_selftest_wait_timeout(device.handle, 50))
+    t0 = time.perf_counter()
+    with pytest.raises(RuntimeError, match="bounded device-side wait ran out \\(code 9"):
+        device.sync()
+    assert 0.03 <= time.perf_counter() - t0 <= 1.0
+    device.sync()                                  # reported once; the word is clear again
+    a = G.leaf(W.normal(0, (256, 512)))
+    check_ = G.matmul(a, G.transpose(a, [1, 0]))
+    (want,), _ = O.port_run([check_])
+    assert rel(device.numpy(check_), want) <= REDUCE_TOL
+    assert lib.ormi_b200_selftest_wait_timeout(device.handle, 5000) != 0      # limits outside 1..1000 ms are refused
