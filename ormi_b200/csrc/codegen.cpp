@@ -398,7 +398,14 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     s << "extern \"C\" __global__ void __launch_bounds__(" << NT << (minb > 0 ? ", " + std::to_string(minb) : "") << ") " << name << "(";
     for (size_t l = 0; l < spec.loads.size(); ++l) s << (l ? ", " : "") << "const float* __restrict__ in" << l;
     for (size_t o = 0; o < spec.outputs.size(); ++o) s << ((spec.loads.size() + o) ? ", " : "") << "float* __restrict__ out" << o;
-    if (stages) s << ", int* __restrict__ err";
+    // Rows handed out dynamically (an atomic counter in the context's word buffer, the next index fetched one row ahead):
+    // a block that becomes resident late, because a collective of the second stream holds its SM for a while, takes what
+    // is left instead of a fixed share the others would have to wait for.  Only for kernels whose outputs do not depend
+    // on which block handled which row (no column / global partials — those stay bit-reproducible with fixed shares)
+    // and only when the row loop has a block barrier of its own to publish the next index.
+    const bool dyn_rows = !stages && n_col == 0 && n_glob == 0 && max_sums_per_level > 0 && NW > 1 &&
+                          (getenv("ORMI_B200_ROWS_DYNAMIC") && atoi(getenv("ORMI_B200_ROWS_DYNAMIC")) == 1);   // opt-in until measured
+    if (stages || dyn_rows) s << ", int* __restrict__ err";
     s << ") {\n";
     s << "    // rows=" << R << " cols=" << C << " threads/row=" << T << " rows/block=" << G << " elems/thread=" << VPT << " vec=" << V << "\n";
     s << "    const int tid = threadIdx.x % " << T << ";\n    const int grp = threadIdx.x / " << T << ";\n";
@@ -453,7 +460,14 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         s << "        const int stg = it % " << stages << ";\n";
         s << "        const bool arrived = ormi_mbar_wait(&fullbar[stg], (unsigned)(it / " << stages << ") & 1u);\n";
     } else {
-        s << "    for (int rb = blockIdx.x * " << G << "; rb < " << R << "; rb += gridDim.x * " << G << ") {\n";
+        if (dyn_rows) {
+            s << "    __shared__ int nextrb[2];\n    int* const rowctr = err + " << kRowCounterWord << ";\n";
+            s << "    if (threadIdx.x == 0) nextrb[0] = atomicAdd(rowctr, " << G << ");\n    __syncthreads();\n";
+            s << "    for (int it = 0;; ++it) {\n        const int rb = nextrb[it & 1];\n        if (rb >= " << R << ") break;\n";
+            s << "        if (threadIdx.x == 0) nextrb[(it + 1) & 1] = atomicAdd(rowctr, " << G << ");     // visible after this row's barriers\n";
+        } else {
+            s << "    for (int rb = blockIdx.x * " << G << "; rb < " << R << "; rb += gridDim.x * " << G << ") {\n";
+        }
         s << "        const int r = rb + grp;\n";
     }
     if (row_pred) s << "        const bool rok = r < " << R << ";\n";
@@ -575,6 +589,8 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     }
     if (use_red) s << "        rpar ^= 1;\n";
     s << "    }\n";
+    if (dyn_rows)   // every block drew exactly one index past the end; the last one to say so leaves the pair at zero
+        s << "    if (threadIdx.x == 0 && atomicAdd(rowctr + 1, 1) == (int)gridDim.x - 1) { rowctr[1] = 0; __threadfence(); atomicExch(rowctr, 0); }\n";
     // epilogue: one partial per block
     if (n_col) {
         if (G > 1) s << "    __shared__ float csm[" << G << "][" << T * VPT << "];\n";
@@ -613,10 +629,10 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     out.step.grid = grid;
     out.step.block = NT;
     out.step.dyn_smem = stages ? (int)(stages * (int64_t)staged.size() * C * 4) : 0;
-    out.step.err_arg = stages > 0;
+    out.step.err_arg = stages > 0 || dyn_rows;
     out.cols = C;
     std::ostringstream w;
-    w << "rows[R=" << R << ",C=" << C << ",T=" << T << ",G=" << G << ",VPT=" << VPT << ",V=" << V << ",levels=" << max_level << ",stages=" << stages << "] nodes=" << spec.nodes.size()
+    w << "rows[R=" << R << ",C=" << C << ",T=" << T << ",G=" << G << ",VPT=" << VPT << ",V=" << V << ",levels=" << max_level << ",stages=" << stages << (dyn_rows ? ",dyn" : "") << "] nodes=" << spec.nodes.size()
       << " loads=" << spec.loads.size() << " outs=";
     for (auto& o : spec.outputs) w << (o.kind == KOutput::FULL ? "F" : o.kind == KOutput::ROW ? "R" : o.kind == KOutput::COLSUM ? "C" : "G");
     out.step.what = w.str();

@@ -11,6 +11,10 @@
 
 namespace ormi_b200 {
 
+// Word of the context's error-word buffer where generated row kernels keep their row counter pair (the tensor-core GEMM
+// keeps its tile counter in another line of the same buffer).
+constexpr int kRowCounterWord = 48;
+
 enum class BufKind { External, NodeOut, Temp, ErrorWord /* the context's device error word */ };
 
 struct PlanBuffer {

@@ -57,6 +57,8 @@ static inline int __syncthreads_or(int pred) {
     return r;
 }
 static inline int atomicExch(int* p, int v) { return __atomic_exchange_n(p, v, __ATOMIC_SEQ_CST); }
+static inline int atomicAdd(int* p, int v) { return __atomic_fetch_add(p, v, __ATOMIC_SEQ_CST); }
+static inline void __threadfence() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
 static inline void ormi_mbar_init(unsigned long long*, unsigned) {}
 static inline void ormi_mbar_fence_init() {}
 static inline void ormi_async_fence() {}

@@ -42,7 +42,7 @@ def run_plan(plan: dict) -> dict:
     bufs = []
     for b in plan["buffers"]:
         if b["kind"] == "error":
-            bufs.append(np.zeros(1, dtype=np.float32))     # the device error word (an int, never set here)
+            bufs.append(np.zeros(64, dtype=np.float32))    # the device word buffer: error word, counters (ints; all-zero bits)
         elif b["kind"] == "external":
             host = order[b["node"]].data.host
             bufs.append(np.ascontiguousarray(host, dtype=np.float32).reshape(-1))
