@@ -404,7 +404,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     // on which block handled which row (no column / global partials — those stay bit-reproducible with fixed shares)
     // and only when the row loop has a block barrier of its own to publish the next index.
     const bool dyn_rows = !stages && n_col == 0 && n_glob == 0 && max_sums_per_level > 0 && NW > 1 &&
-                          (getenv("ORMI_B200_ROWS_DYNAMIC") && atoi(getenv("ORMI_B200_ROWS_DYNAMIC")) == 1);   // opt-in until measured
+                          !(getenv("ORMI_B200_ROWS_DYNAMIC") && atoi(getenv("ORMI_B200_ROWS_DYNAMIC")) == 0);
     if (stages || dyn_rows) s << ", int* __restrict__ err";
     s << ") {\n";
     s << "    // rows=" << R << " cols=" << C << " threads/row=" << T << " rows/block=" << G << " elems/thread=" << VPT << " vec=" << V << "\n";
