@@ -408,10 +408,11 @@ def main():
             return
         # cross-shard combine: dg, db (the last two roots of the layernorm graph) are summed over the ranks, in place,
         # by NCCL on the second stream.  Nothing of the next step reads them, so the all-reduce (a latency of some
-        # 25 us for 2 x 16 KB) runs beside the next step's first kernel; the step after waits for it.  No host
-        # synchronisation inside a step.
+        # 25 us for 2 x 16 KB) runs beside the next step's softmax kernel; the compute stream waits for it after that
+        # kernel has been queued.  No host synchronisation inside a step.
+        outs = runner.run(which=0, keep=True)
         settle()
-        outs = runner.run(keep=True)
+        outs += runner.run(which=1, keep=True)
         bufs = (ctypes.c_void_p * 2)(outs[-2][0], outs[-1][0])
         counts = (ctypes.c_size_t * 2)(C, C)
         check(lib.ormi_b200_allreduce_sum_f32(dev.handle, bufs, counts, 2, 1))
