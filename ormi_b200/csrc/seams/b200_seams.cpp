@@ -162,6 +162,19 @@ IAllocator* get_cuda_allocator() {
     return &instance;
 }
 
+// Additive, for hosts above ormi-core (the Python module loads this library anyway): the backend's options
+// ("matmul" = fp32 | bf16 | tf32 | 3xtf32, "fusion" = on | off) and counters of the process-wide context.  The
+// reference has no runtime options.  Both return non-zero / -1 when there is no GPU.
+extern "C" int ormi_engine_b200_set_option(const char* key, const char* value) {
+    try { return ormi_b200_set_option(ctx(), key, value); } catch (...) { return 1; }
+}
+extern "C" long long ormi_engine_b200_counter(const char* name) {
+    try {
+        int64_t v = 0;
+        return ormi_b200_get_counter(ctx(), name, &v) == 0 ? (long long)v : -1;
+    } catch (...) { return -1; }
+}
+
 namespace cuda {
 
 // ---------------------------------------------------------------------------------------------- seam 2

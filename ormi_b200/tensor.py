@@ -35,6 +35,29 @@ def _load_backend():
 
 
 backend = _load_backend()
+
+
+def _engine():
+    import ctypes
+    lib = ctypes.CDLL(os.path.join(_BUILD_DIR, "libormi_engine_b200.so"))
+    lib.ormi_engine_b200_set_option.argtypes = [ctypes.c_char_p, ctypes.c_char_p]
+    lib.ormi_engine_b200_counter.argtypes = [ctypes.c_char_p]
+    lib.ormi_engine_b200_counter.restype = ctypes.c_longlong
+    return lib
+
+
+def set_option(key: str, value: str) -> None:
+    """Backend knobs of the CUDA device ("matmul": fp32 | bf16 | tf32 | 3xtf32, "fusion": on | off); additive, ormi-core
+    itself has none.  Raises without a GPU or for an unknown option."""
+    if _engine().ormi_engine_b200_set_option(key.encode(), value.encode()) != 0:
+        raise RuntimeError(f"cannot set backend option {key}={value} (no GPU, or unknown option)")
+
+
+def counter(name: str) -> int:
+    """A counter of the CUDA device's context (launches, gemm_launches, kernels_compiled, plan_cache_hits, ...)."""
+    return int(_engine().ormi_engine_b200_counter(name.encode()))
+
+
 OpEnum, DeviceEnum, Device, Node = backend.OpEnum, backend.DeviceEnum, backend.Device, backend.Node
 
 

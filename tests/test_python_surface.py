@@ -183,3 +183,43 @@ def test_example_scenarios_on_cuda():
     Zm = Wm @ Xm
     assert Zm.shape == (2, 1)
     np.testing.assert_array_equal(Zm.numpy(), [[14.0], [32.0]])
+
+
+def test_backend_knobs_need_a_gpu_or_work():
+    """set_option / counter reach the process-wide context of the CUDA device; without a GPU they fail loudly."""
+    from ormi_b200 import tensor as T
+    import torch
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            T.set_option("matmul", "bf16")
+        assert T.counter("launches") == -1
+
+
+@pytest.mark.gpu
+def test_matmul_mode_and_fusion_knobs_on_cuda():
+    from ormi_b200 import tensor as T
+    rng = np.random.default_rng(3)
+    a_h = (rng.standard_normal((256, 512)) / np.sqrt(512)).astype(np.float32)
+    b_h = (rng.standard_normal((512, 384)) / np.sqrt(512)).astype(np.float32)
+    want = a_h.astype(np.float64) @ b_h.astype(np.float64)
+    exact = (Tensor(a_h, device="cuda") @ Tensor(b_h, device="cuda")).numpy().copy()
+    assert rel(exact, want) <= REDUCE_TOL
+    T.set_option("matmul", "bf16")
+    try:
+        g0 = T.counter("gemm_launches")
+        rounded = (Tensor(a_h, device="cuda") @ Tensor(b_h, device="cuda")).numpy().copy()
+        assert T.counter("gemm_launches") == g0 + 1
+        assert 1e-5 < rel(rounded, want) <= 2e-2              # bf16 operands: inside its own tolerance, not fp32-exact
+    finally:
+        T.set_option("matmul", "fp32")
+    T.set_option("fusion", "off")
+    try:
+        l0 = T.counter("launches")
+        x = Tensor(a_h, device="cuda")
+        y = ((x * 2.0) + 1.0).exp().numpy()
+        assert T.counter("launches") - l0 >= 3                   # one kernel per node, like the reference
+        assert rel(y, np.exp(a_h.astype(np.float64) * 2 + 1)) <= PW_TOL
+    finally:
+        T.set_option("fusion", "on")
+    with pytest.raises(RuntimeError):
+        T.set_option("matmul", "fp64")
