@@ -153,6 +153,19 @@ int ormi_b200_cvt_bf16_kmajor(ormi_b200_ctx* ctx, const float* src, int64_t row_
                               int rows, int K, void* dst);
 int ormi_b200_gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, float* C, int M, int N, int Kp);
 
+/* The bf16 tensor-core matmul on operands the caller already holds in bf16, each in its own row-major layout (no
+ * counterpart in the reference; inside ormi_b200_realize the same kernel runs behind "matmul" = "bf16", with the bf16
+ * copies cached per buffer or written by the kernel that produced the fp32 values).
+ *   cvt:  dst[r][c] = bf16(src[r * ld + c]) for r < rows, c < cols; dst is contiguous [rows][cols]; cols % 8 == 0.
+ *   gemm: C[M,N] (fp32, contiguous) = A * B with fp32 accumulation (tcgen05.mma on a pair of SMs, TMEM, TMA).
+ *         a_transposed = 0: A is stored [M][K];  1: stored [K][M] (what a TRANSPOSE view of a row-major matrix is).
+ *         b_transposed = 0: B is stored [K][N];  1: stored [N][K].
+ *         The contiguous dimension of each operand must be a multiple of 8, N a multiple of 4, pointers 16-byte
+ *         aligned.  Ragged M, N and K are handled by the kernel (zero fill on load, clipped stores). */
+int ormi_b200_cvt_bf16(ormi_b200_ctx* ctx, const float* src, int64_t ld, int rows, int cols, void* dst);
+int ormi_b200_gemm_bf16(ormi_b200_ctx* ctx, const void* a16, int a_transposed, const void* b16, int b_transposed,
+                        float* C, int M, int N, int K);
+
 /* ------------------------------------------------------------------ multi-GPU combine -- */
 
 /* Batch-sharded runs: one process per GPU, each realizes its own row shard; parameter gradients (and column / global

@@ -43,6 +43,8 @@ _SIGNATURES = {
     "ormi_b200_colsum_static": (c_int, [c_void_p, ctypes.c_int64, ctypes.c_int64, c_void_p, c_void_p]),
     "ormi_b200_cvt_bf16_kmajor": (c_int, [c_void_p, c_void_p, ctypes.c_int64, ctypes.c_int64, c_int, c_int, c_void_p]),
     "ormi_b200_gemm_bf16_kmajor": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int]),
+    "ormi_b200_cvt_bf16": (c_int, [c_void_p, c_void_p, ctypes.c_int64, c_int, c_int, c_void_p]),
+    "ormi_b200_gemm_bf16": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int]),
     "ormi_b200_comm_unique_id": (c_int, [c_char_p]),
     "ormi_b200_comm_init": (c_int, [c_void_p, c_char_p, c_int, c_int]),
     "ormi_b200_allreduce_sum_f32": (c_int, [c_void_p, P(c_void_p), P(c_size_t), c_int, c_int]),

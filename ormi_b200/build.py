@@ -11,7 +11,7 @@ ROOT = os.path.dirname(HERE)
 LIB = os.path.join(HERE, "libormi_b200.so")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
-SOURCES = ["abi.cu", "runtime.cu", "fusion.cpp", "codegen.cpp", "gemm_ffma.cu", "gemm_tcgen05.cu", "colsum_static.cu", "comm.cu"]
+SOURCES = ["abi.cu", "runtime.cu", "fusion.cpp", "codegen.cpp", "gemm_ffma.cu", "gemm_tcgen05.cu", "gemm_tc.cu", "colsum_static.cu", "comm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-cudart", "static",

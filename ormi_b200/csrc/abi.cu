@@ -17,6 +17,13 @@ static int guarded(F&& f) {
 
 static void need(bool cond, const char* msg) { if (!cond) throw Error(msg); }
 
+// Every entry point that takes a context makes the context's device current first: a process may hold contexts on
+// several devices, and stream operations fail when another device is current.
+static void bind(ormi_b200_ctx* ctx, const char* who) {
+    if (!ctx) throw Error(std::string(who) + ": ctx is NULL");
+    ORMI_CUDA(cudaSetDevice(ctx->device));
+}
+
 namespace ormi_b200 {
 void set_last_error(const std::string& msg) { g_last_error = msg; }
 void gemm_dispatch(ormi_b200_ctx* ctx, const GemmArgs& g) {
@@ -59,6 +66,7 @@ int ormi_b200_shutdown(ormi_b200_ctx* ctx) {
         comm_destroy(ctx);
         cudaStreamSynchronize(ctx->stream);
         for (auto& kv : ctx->kernel_cache) if (kv.second.module) ctx->drv.ModuleUnload(kv.second.module);
+        for (auto& kv : ctx->shadows) cudaFree(kv.second.ptr);
         for (auto& kv : ctx->free_blocks) for (void* p : kv.second) cudaFree(p);
         for (int i = 0; i < 2; ++i) if (ctx->stage[i]) cudaFree(ctx->stage[i]);
         if (ctx->gemm_err) cudaFree(ctx->gemm_err);
@@ -68,17 +76,16 @@ int ormi_b200_shutdown(ormi_b200_ctx* ctx) {
 }
 
 int ormi_b200_alloc(ormi_b200_ctx* ctx, size_t bytes, void** out_ptr) {
-    return guarded([&] { need(ctx && out_ptr, "ormi_b200_alloc: NULL argument"); ORMI_CUDA(cudaSetDevice(ctx->device)); *out_ptr = pool_alloc(ctx, bytes); });
+    return guarded([&] { need(out_ptr != nullptr, "ormi_b200_alloc: NULL argument"); bind(ctx, "ormi_b200_alloc"); *out_ptr = pool_alloc(ctx, bytes); });
 }
 
 int ormi_b200_free(ormi_b200_ctx* ctx, void* ptr, size_t bytes) {
-    return guarded([&] { need(ctx != nullptr, "ormi_b200_free: ctx is NULL"); pool_free(ctx, ptr, bytes); });
+    return guarded([&] { bind(ctx, "ormi_b200_free"); pool_free(ctx, ptr, bytes); });
 }
 
 int ormi_b200_trim(ormi_b200_ctx* ctx) {
     return guarded([&] {
-        need(ctx != nullptr, "ormi_b200_trim: ctx is NULL");
-        ORMI_CUDA(cudaSetDevice(ctx->device));
+        bind(ctx, "ormi_b200_trim");
         ORMI_CUDA(cudaStreamSynchronize(ctx->stream));
         std::lock_guard<std::mutex> lock(ctx->pool_mutex);
         for (auto& kv : ctx->free_blocks) for (void* p : kv.second) cudaFree(p);
@@ -87,16 +94,17 @@ int ormi_b200_trim(ormi_b200_ctx* ctx) {
 }
 
 int ormi_b200_memset(ormi_b200_ctx* ctx, void* ptr, int value, size_t bytes) {
-    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); ORMI_CUDA(cudaMemsetAsync(ptr, value, bytes, ctx->stream)); });
+    return guarded([&] { bind(ctx, "ormi_b200_memset"); shadow_drop(ctx, ptr, bytes); ORMI_CUDA(cudaMemsetAsync(ptr, value, bytes, ctx->stream)); });
 }
 
 int ormi_b200_memcpy_d2d(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes) {
-    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream)); });
+    return guarded([&] { bind(ctx, "ormi_b200_memcpy_d2d"); shadow_drop(ctx, dst, bytes); ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream)); });
 }
 
 int ormi_b200_memcpy_h2d(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes) {
     return guarded([&] {
-        need(ctx != nullptr, "ctx is NULL");
+        bind(ctx, "ormi_b200_memcpy_h2d");
+        shadow_drop(ctx, dst, bytes);
         ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
         ORMI_CUDA(cudaStreamSynchronize(ctx->stream));   // the host buffer may be reused on return
     });
@@ -104,7 +112,7 @@ int ormi_b200_memcpy_h2d(ormi_b200_ctx* ctx, void* dst, const void* src, size_t 
 
 int ormi_b200_memcpy_d2h(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes) {
     return guarded([&] {
-        need(ctx != nullptr, "ctx is NULL");
+        bind(ctx, "ormi_b200_memcpy_d2h");
         ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
         ORMI_CUDA(cudaStreamSynchronize(ctx->stream));
         check_gemm_error(ctx);
@@ -117,8 +125,9 @@ __global__ void fill_u32_kernel(uint32_t* dst, uint32_t v, size_t n) {
 
 int ormi_b200_fill_u32(ormi_b200_ctx* ctx, void* dst, uint32_t pattern, size_t count) {
     return guarded([&] {
-        need(ctx != nullptr, "ctx is NULL");
+        bind(ctx, "ormi_b200_fill_u32");
         if (count == 0) return;
+        shadow_drop(ctx, dst, count * 4);
         int grid = (int)std::min<size_t>((count + 255) / 256, (size_t)ctx->num_sms * 8);
         fill_u32_kernel<<<grid, 256, 0, ctx->stream>>>((uint32_t*)dst, pattern, count);
         ORMI_CUDA(cudaGetLastError());
@@ -126,18 +135,19 @@ int ormi_b200_fill_u32(ormi_b200_ctx* ctx, void* dst, uint32_t pattern, size_t c
 }
 
 int ormi_b200_fill_u8(ormi_b200_ctx* ctx, void* dst, uint8_t pattern, size_t count) {
-    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); ORMI_CUDA(cudaMemsetAsync(dst, pattern, count, ctx->stream)); });
+    return guarded([&] { bind(ctx, "ormi_b200_fill_u8"); shadow_drop(ctx, dst, count); ORMI_CUDA(cudaMemsetAsync(dst, pattern, count, ctx->stream)); });
 }
 
 int ormi_b200_sync(ormi_b200_ctx* ctx) {
-    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); ORMI_CUDA(cudaStreamSynchronize(ctx->stream)); check_gemm_error(ctx); });
+    return guarded([&] { bind(ctx, "ormi_b200_sync"); ORMI_CUDA(cudaStreamSynchronize(ctx->stream)); check_gemm_error(ctx); });
 }
 
 void* ormi_b200_stream(ormi_b200_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 
 int ormi_b200_realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots) {
     return guarded([&] {
-        need(ctx && nodes && roots && n_nodes > 0 && n_roots > 0, "ormi_b200_realize: bad arguments");
+        need(nodes && roots && n_nodes > 0 && n_roots > 0, "ormi_b200_realize: bad arguments");
+        bind(ctx, "ormi_b200_realize");
         realize(ctx, nodes, n_nodes, roots, n_roots);
     });
 }
@@ -192,7 +202,8 @@ static void fill_node(ormi_b200_node& nd, int op, int ndim, const int32_t* shape
 int ormi_b200_sum(ormi_b200_ctx* ctx, const float* in, int ndim, const int32_t* shape, const int32_t* strides,
                   const int32_t* axes, int n_axes, float* out) {
     return guarded([&] {
-        need(ctx && in && out && ndim >= 0 && ndim <= ORMI_B200_MAX_DIMS, "ormi_b200_sum: bad arguments");
+        need(in && out && ndim >= 0 && ndim <= ORMI_B200_MAX_DIMS, "ormi_b200_sum: bad arguments");
+        bind(ctx, "ormi_b200_sum");
         ormi_b200_node g[2];
         fill_node(g[0], ORMI_OP_LEAF, ndim, shape, strides, (void*)in);
         int32_t oshape[ORMI_B200_MAX_DIMS]; int ond = 0;
@@ -215,7 +226,8 @@ int ormi_b200_matmul(ormi_b200_ctx* ctx,
                      const float* B, int ndim_b, const int32_t* shape_b, const int32_t* strides_b,
                      float* out, int ndim_out, const int32_t* shape_out) {
     return guarded([&] {
-        need(ctx && A && B && out, "ormi_b200_matmul: NULL argument");
+        need(A && B && out, "ormi_b200_matmul: NULL argument");
+        bind(ctx, "ormi_b200_matmul");
         need(ndim_a >= 2 && ndim_b >= 2 && ndim_a <= ORMI_B200_MAX_DIMS && ndim_b <= ORMI_B200_MAX_DIMS && ndim_out <= ORMI_B200_MAX_DIMS,
              "MATMUL requires operands to have at least 2 dimensions.");
         ormi_b200_node g[3];
@@ -233,15 +245,35 @@ int ormi_b200_matmul(ormi_b200_ctx* ctx,
 
 int ormi_b200_cvt_bf16_kmajor(ormi_b200_ctx* ctx, const float* src, int64_t row_stride, int64_t k_stride, int rows, int K, void* dst) {
     return guarded([&] {
-        need(ctx && src && dst && rows > 0 && K > 0, "ormi_b200_cvt_bf16_kmajor: bad arguments");
+        need(src && dst && rows > 0 && K > 0, "ormi_b200_cvt_bf16_kmajor: bad arguments");
+        bind(ctx, "ormi_b200_cvt_bf16_kmajor");
         cvt_bf16_kmajor(ctx, src, row_stride, k_stride, rows, K, dst);
     });
 }
 
 int ormi_b200_gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, float* C, int M, int N, int Kp) {
     return guarded([&] {
-        need(ctx && a16 && b16 && C, "ormi_b200_gemm_bf16_kmajor: NULL argument");
+        need(a16 && b16 && C, "ormi_b200_gemm_bf16_kmajor: NULL argument");
+        bind(ctx, "ormi_b200_gemm_bf16_kmajor");
         gemm_bf16_kmajor(ctx, a16, b16, C, M, N, Kp);
+    });
+}
+
+int ormi_b200_cvt_bf16(ormi_b200_ctx* ctx, const float* src, int64_t ld, int rows, int cols, void* dst) {
+    return guarded([&] {
+        need(src && dst, "ormi_b200_cvt_bf16: NULL argument");
+        bind(ctx, "ormi_b200_cvt_bf16");
+        cvt_bf16(ctx, src, ld, rows, cols, dst);
+    });
+}
+
+int ormi_b200_gemm_bf16(ormi_b200_ctx* ctx, const void* a16, int a_transposed, const void* b16, int b_transposed,
+                        float* C, int M, int N, int K) {
+    return guarded([&] {
+        need(a16 && b16 && C, "ormi_b200_gemm_bf16: NULL argument");
+        bind(ctx, "ormi_b200_gemm_bf16");
+        shadow_drop(ctx, C, (size_t)M * N * 4);
+        gemm_tc(ctx, a16, a_transposed ? 1 : 0, b16, b_transposed ? 0 : 1, C, M, N, K);
     });
 }
 
@@ -250,39 +282,41 @@ int ormi_b200_comm_unique_id(char id[128]) {
 }
 
 int ormi_b200_comm_init(ormi_b200_ctx* ctx, const char id[128], int rank, int world_size) {
-    return guarded([&] { need(ctx && id, "ormi_b200_comm_init: NULL argument"); comm_init(ctx, id, rank, world_size); });
+    return guarded([&] { need(id != nullptr, "ormi_b200_comm_init: NULL argument"); bind(ctx, "ormi_b200_comm_init"); comm_init(ctx, id, rank, world_size); });
 }
 
 int ormi_b200_allreduce_sum_f32(ormi_b200_ctx* ctx, void* const* buffers, const size_t* counts, int n, int overlap) {
     return guarded([&] {
-        need(ctx && buffers && counts && n > 0, "ormi_b200_allreduce_sum_f32: bad arguments");
+        need(buffers && counts && n > 0, "ormi_b200_allreduce_sum_f32: bad arguments");
+        bind(ctx, "ormi_b200_allreduce_sum_f32");
         comm_allreduce(ctx, buffers, counts, n, overlap);
     });
 }
 
 int ormi_b200_comm_join(ormi_b200_ctx* ctx) {
-    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); comm_join(ctx); });
+    return guarded([&] { bind(ctx, "ormi_b200_comm_join"); comm_join(ctx); });
 }
 
 int ormi_b200_comm_mark(ormi_b200_ctx* ctx, int slot) {
-    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); comm_mark(ctx, slot); });
+    return guarded([&] { bind(ctx, "ormi_b200_comm_mark"); comm_mark(ctx, slot); });
 }
 
 int ormi_b200_comm_wait(ormi_b200_ctx* ctx, int slot) {
-    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); comm_wait(ctx, slot); });
+    return guarded([&] { bind(ctx, "ormi_b200_comm_wait"); comm_wait(ctx, slot); });
 }
 
 int ormi_b200_comm_destroy(ormi_b200_ctx* ctx) {
-    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); comm_destroy(ctx); });
+    return guarded([&] { bind(ctx, "ormi_b200_comm_destroy"); comm_destroy(ctx); });
 }
 
 int ormi_b200_selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms) {
-    return guarded([&] { need(ctx != nullptr, "ctx is NULL"); ORMI_CUDA(cudaSetDevice(ctx->device)); selftest_wait_timeout(ctx, limit_ms); });
+    return guarded([&] { bind(ctx, "ormi_b200_selftest_wait_timeout"); selftest_wait_timeout(ctx, limit_ms); });
 }
 
 int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value) {
     return guarded([&] {
-        need(ctx && key && value, "ormi_b200_set_option: NULL argument");
+        need(key && value, "ormi_b200_set_option: NULL argument");
+        bind(ctx, "ormi_b200_set_option");
         std::string k = key, v = value;
         if (k == "matmul") {
             if (v == "fp32") ctx->matmul_mode = MatmulMode::FP32;
@@ -290,6 +324,9 @@ int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value)
             else if (v == "tf32") ctx->matmul_mode = MatmulMode::TF32;
             else if (v == "3xtf32") ctx->matmul_mode = MatmulMode::TF32X3;
             else throw Error("unknown matmul mode: " + v);
+        } else if (k == "tc_pair") {
+            // bf16 GEMM: "on" = one tcgen05.mma per pair of SMs (256 x 256 tiles, default), "off" = one per SM (128 x 256)
+            if (v == "on") ctx->tc_cta_group = 2; else if (v == "off") ctx->tc_cta_group = 1; else throw Error("tc_pair must be on or off");
         } else if (k == "fusion") {
             if (v == "on") ctx->fusion = true; else if (v == "off") ctx->fusion = false; else throw Error("fusion must be on or off");
         } else throw Error("unknown option: " + k);

@@ -55,6 +55,23 @@ struct CachedPlan {
 
 enum class MatmulMode { FP32, BF16, TF32, TF32X3 };
 
+// bf16 twin of an fp32 matrix that matmuls read (gemm_tc.cu): contiguous [rows][cols] copy of the fp32 data at the
+// key pointer (row pitch ld, src_bytes long).
+struct Shadow16 {
+    void* ptr = nullptr;
+    size_t bytes = 0, src_bytes = 0;
+    int rows = 0, cols = 0;
+    long long ld = 0;
+};
+
+// Generated epilogue of the run-time compiled tensor-core GEMM: text spliced into the kernel template plus the
+// device pointers of its extra parameters, in parameter order.
+struct TcEpilogue {
+    std::string prelude, params, init, cols, body;
+    int wpq = 1;                       // epilogue warps per TMEM lane quarter (1, 2 or 4)
+    std::vector<void*> args;
+};
+
 }  // namespace ormi_b200
 
 namespace ormi_b200 { constexpr int kErrorWords = 64, kTileCounterWord = 32; }
@@ -74,7 +91,10 @@ struct ormi_b200_ctx {
     ormi_b200::MatmulMode matmul_mode = ormi_b200::MatmulMode::FP32;
     bool fusion = true;
 
-    // bf16 staging for the tensor-core GEMM path (grown on demand, reused across calls)
+    // bf16 twins of fp32 matmul operands, by fp32 pointer (dropped when that buffer is freed or written through the ABI)
+    std::unordered_map<const void*, ormi_b200::Shadow16> shadows;
+    int tc_cta_group = 2;             // CTAs per tcgen05.mma of the bf16 GEMM: 2 = a pair of SMs per 256 x 256 tile
+    // operand staging of the tf32 / 3xTF32 GEMM path (grown on demand, reused across calls)
     void* stage[2] = {nullptr, nullptr};
     size_t stage_bytes[2] = {0, 0};
     // kErrorWords ints: word 0 is the error word, word kTileCounterWord (its own 128-byte line) the GEMM's tile counter
@@ -83,7 +103,7 @@ struct ormi_b200_ctx {
     bool gemm_attr_set = false;
 
     std::map<std::string, int64_t> counters;
-    void* nccl = nullptr;   // opaque: collective state (nccl.cpp)
+    void* nccl = nullptr;   // opaque: collective state (comm.cu)
 };
 
 namespace ormi_b200 {
@@ -115,6 +135,18 @@ void selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms);   // queues a wait
 void check_gemm_error(ormi_b200_ctx* ctx);   // throws when the tensor-core kernel reported a wait that ran out
 void gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, float* C, int M, int N, int Kp);
 void cvt_bf16_kmajor(ormi_b200_ctx* ctx, const float* src, long long s_row, long long s_k, int rows, int K, void* dst);
+
+// run-time compiled tensor-core GEMM on bf16 operands in their natural row-major layout (gemm_tc.cu)
+bool gemm_tc_supported(const GemmArgs& g);
+void gemm_tc(ormi_b200_ctx* ctx, const void* a16, int a_mn, const void* b16, int b_mn, float* C, int M, int N, int K,
+             const TcEpilogue* epi = nullptr);
+void gemm_tc_from_fp32(ormi_b200_ctx* ctx, const GemmArgs& g, const void* a16 = nullptr, const void* b16 = nullptr,
+                       const TcEpilogue* epi = nullptr);
+void cvt_bf16(ormi_b200_ctx* ctx, const float* src, long long ld, int rows, int cols, void* dst);
+const void* shadow_of(ormi_b200_ctx* ctx, const float* src, int rows, int cols, long long ld);
+const void* shadow_find(ormi_b200_ctx* ctx, const void* src, int rows, int cols, long long ld);
+void shadow_register(ormi_b200_ctx* ctx, const void* src, void* p16, int rows, int cols, long long ld);
+void shadow_drop(ormi_b200_ctx* ctx, const void* ptr, size_t bytes);
 
 // collectives (comm.cu)
 void comm_unique_id(char* out128);

@@ -476,6 +476,8 @@ void gemm_bf16(ormi_b200_ctx* ctx, const GemmArgs& g) {
     // Small or batched problems stay on the fp32 path (a batch is a loop of independent GEMMs; the tensor path is
     // worth its two conversion passes only for large single products).
     if (g.batch != 1 || (long long)g.M * g.N * g.K < (1ll << 21) || g.K < 64) { gemm_ffma(ctx, g); return; }
+    // operands whose rows are whole 16-byte pieces of bf16 go to the run-time compiled kernel, in their own layout
+    if (ctx->tc_cta_group != 0 && gemm_tc_supported(g)) { gemm_tc_from_fp32(ctx, g); return; }
     const int Kp = (g.K + BK - 1) / BK * BK;
     __nv_bfloat16* a16 = (__nv_bfloat16*)stage_buffer(ctx, 0, (size_t)g.M * Kp * 2);
     __nv_bfloat16* b16 = (__nv_bfloat16*)stage_buffer(ctx, 1, (size_t)g.N * Kp * 2);

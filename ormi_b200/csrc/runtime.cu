@@ -78,6 +78,7 @@ void* pool_alloc(ormi_b200_ctx* ctx, size_t bytes) {
 void pool_free(ormi_b200_ctx* ctx, void* ptr, size_t bytes) {
     if (!ptr) return;
     if (bytes == 0) bytes = 4;
+    shadow_drop(ctx, ptr, bytes);      // a bf16 twin of this buffer goes back to the pool with it
     std::lock_guard<std::mutex> lock(ctx->pool_mutex);
     ctx->free_blocks[bytes].push_back(ptr);
 }
