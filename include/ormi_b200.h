@@ -40,6 +40,8 @@ enum ormi_b200_op {
 
 /* Node flags (in). */
 #define ORMI_NODE_KEEP   1u  /* somebody outside the graph holds this node: it must own a buffer after realize */
+#define ORMI_NODE_TWIN16 8u  /* "bf16" matmul arithmetic: a later matmul will read this root (a weight an update produces): write
+                              * its bf16 copy along with it, so that no conversion pass is needed then */
 /* Node flags (out, set by ormi_b200_realize). */
 #define ORMI_NODE_OWNED  2u  /* `data` is a fresh pool buffer now owned by the caller (free with ormi_b200_free) */
 #define ORMI_NODE_ALIAS  4u  /* `data` aliases the buffer of the node's view base (ormi-core/csrc/backend/runtime.cpp:20-23) */
@@ -118,6 +120,12 @@ int ormi_b200_realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, co
  * (ormi-core/csrc/backend/cuda/compiler.cuh:8-16) for a whole graph. */
 int ormi_b200_plan_json(const ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots,
                         char* buf, size_t cap, size_t* out_len);
+
+/* The same, for a schedule that depends on options: `options` is "key=value,key=value" with the keys of
+ * ormi_b200_set_option that shape a schedule ("matmul", "fusion", "tune.*") plus "aligned=0" for inputs that do not
+ * start on 16-byte boundaries.  NULL or "" gives the defaults. */
+int ormi_b200_plan_json_opts(const ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots, const char* options,
+                             char* buf, size_t cap, size_t* out_len);
 
 /* cuda::compile (ormi-core/csrc/backend/cuda/compiler.cu:53-112): CUDA C source of the guarded scalar
  * `fused_kernel` for the un-realized pointwise sub-graph under `root`, with the leaves in argument order.

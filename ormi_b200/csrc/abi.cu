@@ -163,6 +163,39 @@ int ormi_b200_plan_json(const ormi_b200_node* nodes, int n_nodes, const int* roo
     });
 }
 
+int ormi_b200_plan_json_opts(const ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots, const char* options,
+                             char* buf, size_t cap, size_t* out_len) {
+    return guarded([&] {
+        need(nodes && roots && n_nodes > 0 && n_roots > 0, "ormi_b200_plan_json_opts: bad arguments");
+        SchedOptions opt;
+        std::string text = options ? options : "";
+        size_t pos = 0;
+        while (pos < text.size()) {
+            size_t end = text.find(',', pos);
+            if (end == std::string::npos) end = text.size();
+            const std::string item = text.substr(pos, end - pos);
+            pos = end + 1;
+            const size_t eq = item.find('=');
+            if (eq == std::string::npos) throw Error("option without a value: " + item);
+            const std::string k = item.substr(0, eq), v = item.substr(eq + 1);
+            if (k == "matmul") opt.bf16_matmul = (v == "bf16");
+            else if (k == "fusion") opt.fusion = (v != "off");
+            else if (k == "aligned") opt.aligned = (v != "0");
+            else if (k.rfind("tune.", 0) == 0) {
+                static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist"};
+                int which = -1;
+                for (int i = 0; i < kTuneKnobs; ++i) if (k.substr(5) == names[i]) which = i;
+                if (which < 0) throw Error("unknown option: " + k);
+                opt.tune[which] = std::atoi(v.c_str());
+            } else throw Error("unknown option: " + k);
+        }
+        Plan p = build_plan(nodes, n_nodes, roots, n_roots, opt);
+        std::string js = plan_to_json(p);
+        if (out_len) *out_len = js.size();
+        if (buf && cap) { size_t c = std::min(cap - 1, js.size()); std::memcpy(buf, js.data(), c); buf[c] = 0; }
+    });
+}
+
 int ormi_b200_compile_source(const ormi_b200_node* nodes, int n_nodes, int root, char* buf, size_t cap, size_t* out_len,
                              int* leaf_index, int leaf_cap, int* n_leaves) {
     return guarded([&] {
@@ -327,6 +360,13 @@ int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value)
         } else if (k == "tc_pair") {
             // bf16 GEMM: "on" = one tcgen05.mma per pair of SMs (256 x 256 tiles, default), "off" = one per SM (128 x 256)
             if (v == "on") ctx->tc_cta_group = 2; else if (v == "off") ctx->tc_cta_group = 1; else throw Error("tc_pair must be on or off");
+        } else if (k.rfind("tune.", 0) == 0) {
+            // overrides of the code generator's measured defaults (experiments); "0" restores the default
+            static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist"};
+            int which = -1;
+            for (int i = 0; i < kTuneKnobs; ++i) if (k.substr(5) == names[i]) which = i;
+            if (which < 0) throw Error("unknown option: " + k);
+            ctx->tune[which] = std::atoi(v.c_str());
         } else if (k == "fusion") {
             if (v == "on") ctx->fusion = true; else if (v == "off") ctx->fusion = false; else throw Error("fusion must be on or off");
         } else throw Error("unknown option: " + k);

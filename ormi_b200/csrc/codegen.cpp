@@ -60,6 +60,21 @@ __device__ __forceinline__ float ormi_warp_max(float v, int width) {
     return v;
 }
 #define ORMI_NEG_INF __int_as_float(0xff800000)
+// fp32 -> bf16, round to nearest even (what the tensor-core matmul reads): one value, and four packed into 8 bytes.
+#ifndef ORMI_EMULATE
+__device__ __forceinline__ unsigned short ormi_bf16(float x) { unsigned short r; asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(x)); return r; }
+__device__ __forceinline__ unsigned ormi_pack_bf16(float lo, float hi) { unsigned r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
+#else
+__device__ __forceinline__ unsigned short ormi_bf16(float x) {
+    unsigned u = __float_as_uint(x);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (unsigned short)0x7fff;
+    return (unsigned short)((u + 0x7fffu + ((u >> 16) & 1u)) >> 16);
+}
+__device__ __forceinline__ unsigned ormi_pack_bf16(float lo, float hi) { return (unsigned)ormi_bf16(lo) | ((unsigned)ormi_bf16(hi) << 16); }
+#endif
+__device__ __forceinline__ void ormi_store_bf16x4(unsigned short* p, float a, float b, float c, float d) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(ormi_pack_bf16(a, b), ormi_pack_bf16(c, d));
+}
 #ifndef ORMI_EMULATE
 // Rows staged in shared memory by bulk asynchronous copies (the TMA engine), completion counted on an mbarrier.
 #define ORMI_DYN_SMEM(name) extern __shared__ __align__(1024) unsigned char name[]
@@ -148,6 +163,20 @@ int64_t touched_bytes(const KLoad& l, const std::vector<int>& D) {
     return e * 4;
 }
 
+// kernel parameters: one pointer per load, then per output the fp32 pointer (unless only a bf16 twin is wanted) and
+// the bf16 twin pointer
+std::string param_list(const KernelSpec& spec) {
+    std::ostringstream s;
+    bool first = true;
+    auto sep = [&]() { std::string r = first ? "" : ", "; first = false; return r; };
+    for (size_t l = 0; l < spec.loads.size(); ++l) s << sep() << "const float* __restrict__ in" << l;
+    for (size_t o = 0; o < spec.outputs.size(); ++o) {
+        if (spec.outputs[o].store) s << sep() << "float* __restrict__ out" << o;
+        if (spec.outputs[o].twin) s << sep() << "unsigned short* __restrict__ out16_" << o;
+    }
+    return s.str();
+}
+
 // ---------------------------------------------------------------------------------------- flat template
 GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
     GeneratedKernel out;
@@ -164,7 +193,7 @@ GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
     const size_t cd = cs.size();
     int64_t total = 1; for (int v : spec.D) total *= v;
     int V = 4;
-    if (cd == 0 || cs.back() % 4 != 0) V = 1;
+    if (cd == 0 || cs.back() % 4 != 0 || !spec.aligned) V = 1;
     for (size_t l = 0; l < spec.loads.size() && V == 4; ++l) {
         int64_t inner = lst[l].back();
         if (inner != 0 && inner != 1) V = 1;
@@ -180,8 +209,7 @@ GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
     std::ostringstream s;
     s << device_prelude();
     s << "extern \"C\" __global__ void __launch_bounds__(" << NT << ") " << name << "(";
-    for (size_t l = 0; l < spec.loads.size(); ++l) s << (l ? ", " : "") << "const float* __restrict__ in" << l;
-    for (size_t o = 0; o < spec.outputs.size(); ++o) s << ((spec.loads.size() + o) ? ", " : "") << "float* __restrict__ out" << o;
+    s << param_list(spec);
     s << ") {\n";
     std::vector<bool> scalar(spec.loads.size());
     for (size_t l = 0; l < spec.loads.size(); ++l) {
@@ -191,8 +219,7 @@ GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
     for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) s << "    float gacc" << o << " = " << red_ident(spec.outputs[o].is_max) << ";\n";
     {   // long arithmetic chains are bound by instruction issue, not by memory: two iterations in flight hide the
         // load latency behind the other iteration's arithmetic (measured: GELU forward 165 -> 151 us at 8192 x 8192)
-        const char* u = getenv("ORMI_B200_FLAT_UNROLL");
-        const int unroll = u ? atoi(u) : (spec.nodes.size() >= 8 ? 2 : 1);
+        const int unroll = spec.tune[TUNE_FLAT_UNROLL] > 0 ? spec.tune[TUNE_FLAT_UNROLL] : (spec.nodes.size() >= 8 ? 2 : 1);
         if (unroll > 1) s << "    #pragma unroll " << unroll << "\n";
     }
     s << "    for (int i = blockIdx.x * " << NT << " + threadIdx.x; i < " << nvec << "; i += gridDim.x * " << NT << ") {\n";
@@ -241,9 +268,11 @@ GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
         if (ko.kind == KOutput::GLOBALSUM) {
             for (int j = 0; j < V; ++j) s << "        gacc" << o << " = " << red_comb(ko.is_max, "gacc" + std::to_string(o), val(j)) << ";\n";
         } else if (V == 4) {
-            s << "        *reinterpret_cast<float4*>(out" << o << " + e0) = make_float4(" << val(0) << ", " << val(1) << ", " << val(2) << ", " << val(3) << ");\n";
+            if (ko.store) s << "        *reinterpret_cast<float4*>(out" << o << " + e0) = make_float4(" << val(0) << ", " << val(1) << ", " << val(2) << ", " << val(3) << ");\n";
+            if (ko.twin) s << "        ormi_store_bf16x4(out16_" << o << " + e0, " << val(0) << ", " << val(1) << ", " << val(2) << ", " << val(3) << ");\n";
         } else {
-            s << "        out" << o << "[e0] = " << val(0) << ";\n";
+            if (ko.store) s << "        out" << o << "[e0] = " << val(0) << ";\n";
+            if (ko.twin) s << "        out16_" << o << "[e0] = ormi_bf16(" << val(0) << ");\n";
         }
     }
     s << "    }\n";
@@ -274,7 +303,7 @@ GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
     w << "flat[total=" << total << ",V=" << V << ",dims=" << cd << "] nodes=" << spec.nodes.size() << " loads=" << spec.loads.size() << " outs=" << spec.outputs.size();
     out.step.what = w.str();
     for (auto& l : spec.loads) out.step.bytes_read += touched_bytes(l, spec.D);
-    for (auto& o : spec.outputs) out.step.bytes_written += (o.kind == KOutput::GLOBALSUM) ? 4 * (int64_t)grid : total * 4;
+    for (auto& o : spec.outputs) out.step.bytes_written += (o.kind == KOutput::GLOBALSUM) ? 4 * (int64_t)grid : total * ((o.store ? 4 : 0) + (o.twin ? 2 : 0));
     return out;
 }
 
@@ -305,14 +334,15 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         I.sr = st[k - 1];
         if (I.row_var && !I.row_collapsed) need_row_coords = true;
     }
-    int V = (C % 4 == 0) ? 4 : 1;
+    int V = (C % 4 == 0 && spec.aligned) ? 4 : 1;
     for (size_t l = 0; l < spec.loads.size() && V == 4; ++l) {
         if (!li[l].elem) continue;
         if (li[l].sc != 1) V = 1;
         for (int d = 0; d < k; ++d) if (spec.loads[l].st[d] % 4 != 0) V = 1;
     }
-    // Tuning knobs (environment overrides are for experiments only).
-    auto env_int = [](const char* name, int dflt) { const char* v = std::getenv(name); return v ? std::atoi(v) : dflt; };
+    // Measured defaults below; spec.tune (ormi_b200_set_option "tune.*") overrides them for experiments.
+    auto knob = [&](int which, int dflt) { return spec.tune[which] > 0 ? spec.tune[which] : dflt; };
+    auto toggle = [&](int which, bool dflt) { return spec.tune[which] == 1 ? false : (spec.tune[which] == 2 ? true : dflt); };
     // Depth = number of dependent row-sum levels.  Defaults measured on B200 at [16384, 4096] (GB/s of algorithmic
     // bytes, measured copy bandwidth 6537):
     //   depth 4 (layernorm fwd+bwd): 16 elements/thread, registers capped for 2 blocks/SM, grid 2/SM, next rows
@@ -330,10 +360,10 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
             depth = std::max(depth, lv);
         }
     }
-    const int target = env_int("ORMI_B200_ROWS_VPT", spec.tune_vpt > 0 ? spec.tune_vpt : ((V == 4 && depth >= 2) ? 16 : 8));
-    const bool hoist = env_int("ORMI_B200_ROWS_HOIST", spec.tune_hoist) != 0;
-    int minb = env_int("ORMI_B200_ROWS_MINB", spec.tune_minblocks > 0 ? spec.tune_minblocks : (depth == 2 ? 3 : 2));
-    const int grid_mult = env_int("ORMI_B200_ROWS_GRID", spec.tune_grid > 0 ? spec.tune_grid : (depth == 2 ? 3 : 2));
+    const int target = knob(TUNE_ROWS_VPT, (V == 4 && depth >= 2) ? 16 : 8);
+    const bool hoist = toggle(TUNE_ROWS_HOIST, true);
+    int minb = knob(TUNE_ROWS_MINB, depth == 2 ? 3 : 2);
+    const int grid_mult = knob(TUNE_ROWS_GRID, depth == 2 ? 3 : 2);
     int T = std::min(1024, std::max(32, ceil_pow2((C + target - 1) / target)));
     int64_t VPT = (C + T - 1) / T;
     VPT = (VPT + V - 1) / V * V;
@@ -351,7 +381,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     std::vector<size_t> staged;
     int stages = 0;
     {
-        const int want = env_int("ORMI_B200_ROWS_STAGE", spec.tune_stage >= 0 ? spec.tune_stage : (depth == 2 ? 0 : 1));
+        const bool want = toggle(TUNE_ROWS_STAGE, depth != 2);
         bool can = want && V == 4 && G == 1 && !col_pred;
         for (size_t l = 0; can && l < spec.loads.size(); ++l) {
             bool varies = false;
@@ -363,7 +393,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         if (can && !staged.empty()) {
             const int64_t per_stage = (int64_t)staged.size() * C * 4;
             const int64_t budget = (int64_t)(minb >= 3 ? 70 : (minb == 2 ? 100 : 200)) * 1024;
-            stages = (int)std::min<int64_t>(env_int("ORMI_B200_ROWS_NSTAGE", 2), budget / per_stage);
+            stages = (int)std::min<int64_t>(knob(TUNE_ROWS_NSTAGE, 2), budget / per_stage);
             if (stages < 2) stages = 0;
         }
         if (!stages) staged.clear();
@@ -396,15 +426,13 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     std::ostringstream s;
     s << device_prelude();
     s << "extern \"C\" __global__ void __launch_bounds__(" << NT << (minb > 0 ? ", " + std::to_string(minb) : "") << ") " << name << "(";
-    for (size_t l = 0; l < spec.loads.size(); ++l) s << (l ? ", " : "") << "const float* __restrict__ in" << l;
-    for (size_t o = 0; o < spec.outputs.size(); ++o) s << ((spec.loads.size() + o) ? ", " : "") << "float* __restrict__ out" << o;
+    s << param_list(spec);
     // Rows handed out dynamically (an atomic counter in the context's word buffer, the next index fetched one row ahead):
     // a block that becomes resident late, because a collective of the second stream holds its SM for a while, takes what
     // is left instead of a fixed share the others would have to wait for.  Only for kernels whose outputs do not depend
     // on which block handled which row (no column / global partials — those stay bit-reproducible with fixed shares)
     // and only when the row loop has a block barrier of its own to publish the next index.
-    const bool dyn_rows = !stages && n_col == 0 && n_glob == 0 && max_sums_per_level > 0 && NW > 1 &&
-                          !(getenv("ORMI_B200_ROWS_DYNAMIC") && atoi(getenv("ORMI_B200_ROWS_DYNAMIC")) == 0);
+    const bool dyn_rows = !stages && n_col == 0 && n_glob == 0 && max_sums_per_level > 0 && NW > 1 && toggle(TUNE_ROWS_DYNAMIC, true);
     if (stages || dyn_rows) s << ", int* __restrict__ err";
     s << ") {\n";
     s << "    // rows=" << R << " cols=" << C << " threads/row=" << T << " rows/block=" << G << " elems/thread=" << VPT << " vec=" << V << "\n";
@@ -572,10 +600,15 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
             if (row_pred) pred = "rok";
             if (col_pred) pred += std::string(pred.empty() ? "" : " && ") + "col < " + std::to_string(C);
             auto v = [&](int e) { return elem ? ref(ko.value, std::to_string(V) + " * q + " + std::to_string(e)) : ref(ko.value, "0"); };
-            s << "            " << (pred.empty() ? "" : "if (" + pred + ") ");
-            if (V == 4) s << "*reinterpret_cast<float4*>(out" << o << " + r * " << C << " + col) = make_float4(" << v(0) << ", " << v(1) << ", " << v(2) << ", " << v(3) << ");\n";
-            else s << "out" << o << "[r * " << C << " + col] = " << v(0) << ";\n";
-            s << "        }\n";
+            s << "            " << (pred.empty() ? "" : "if (" + pred + ") ") << "{\n";
+            if (V == 4) {
+                if (ko.store) s << "                *reinterpret_cast<float4*>(out" << o << " + r * " << C << " + col) = make_float4(" << v(0) << ", " << v(1) << ", " << v(2) << ", " << v(3) << ");\n";
+                if (ko.twin) s << "                ormi_store_bf16x4(out16_" << o << " + r * " << C << " + col, " << v(0) << ", " << v(1) << ", " << v(2) << ", " << v(3) << ");\n";
+            } else {
+                if (ko.store) s << "                out" << o << "[r * " << C << " + col] = " << v(0) << ";\n";
+                if (ko.twin) s << "                out16_" << o << "[r * " << C << " + col] = ormi_bf16(" << v(0) << ");\n";
+            }
+            s << "            }\n        }\n";
         } else if (ko.kind == KOutput::ROW) {
             s << "        if (tid == 0" << (row_pred ? " && rok" : "") << ") out" << o << "[r] = " << ref(ko.value, "0") << ";\n";
         } else if (ko.kind == KOutput::COLSUM) {
@@ -638,7 +671,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     out.step.what = w.str();
     for (auto& l : spec.loads) out.step.bytes_read += touched_bytes(l, spec.D);
     for (auto& o : spec.outputs) {
-        if (o.kind == KOutput::FULL) out.step.bytes_written += R * C * 4;
+        if (o.kind == KOutput::FULL) out.step.bytes_written += R * C * ((o.store ? 4 : 0) + (o.twin ? 2 : 0));
         else if (o.kind == KOutput::ROW) out.step.bytes_written += R * 4;
         else if (o.kind == KOutput::COLSUM) out.step.bytes_written += (int64_t)grid * C * 4;
         else out.step.bytes_written += (int64_t)grid * 4;
@@ -654,6 +687,96 @@ GeneratedKernel generate_kernel(const KernelSpec& spec, const std::string& name,
     for (auto& o : spec.outputs) if (o.kind == KOutput::ROW || o.kind == KOutput::COLSUM) rows = true;
     GeneratedKernel g = rows ? generate_rows(spec, name) : generate_flat(spec, name);
     if (g.error.empty()) g.step.key = std::to_string(fnv1a(g.step.source));
+    return g;
+}
+
+// The pointwise work that follows a matmul, as the epilogue of the tensor-core GEMM template (gemm_tc_template.cuh).
+// The template hands this code `acc` (float4: four adjacent columns of one row of the product), `grow`, `gcol`, `M`, `N`;
+// every global access below is a 16-byte piece of a row, eight lanes covering a full 128-byte line.  The text is
+// spliced in through macros, so it holds no comments and no preprocessor lines.
+GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, bool twin_c) {
+    GeneratedEpilogue g;
+    if (spec.D.size() != 2) { g.error = "epilogue: domain is not [M, N]"; return g; }
+    const int64_t N = spec.D[1];
+    if (N % 4 != 0) { g.error = "epilogue: N is not a multiple of 4"; return g; }
+    std::ostringstream params, init, cols, body;
+    for (size_t l = 0; l < spec.loads.size(); ++l) {
+        const KLoad& ld = spec.loads[l];
+        if (ld.acc) continue;
+        const int64_t sm = ld.st[0], sn = ld.st[1];
+        params << ", const float* __restrict__ ein" << l;
+        const std::string P = "ein" + std::to_string(l), L = "L" + std::to_string(l);
+        if (sm == 0 && sn == 0) {
+            init << "const float S" << l << " = " << P << "[0]; ";
+        } else if (sm == 0) {
+            cols << "float " << L << "[4]; ";
+            if (sn == 1) cols << "{ const float4 t = *reinterpret_cast<const float4*>(" << P << " + gc); " << L << "[0] = t.x; " << L << "[1] = t.y; " << L << "[2] = t.z; " << L << "[3] = t.w; } ";
+            else cols << "for (int j = 0; j < 4; ++j) " << L << "[j] = " << P << "[(long long)(gc + j) * " << sn << "]; ";
+        } else {
+            body << "float " << L << "[4]; ";
+            if (sn == 1 && sm % 4 == 0) {
+                body << "{ const float4 t = *reinterpret_cast<const float4*>(" << P << " + (long long)grow * " << sm << " + gcol); " << L << "[0] = t.x; " << L << "[1] = t.y; " << L << "[2] = t.z; " << L << "[3] = t.w; } ";
+            } else if (sn == 0) {
+                body << "{ const float t = " << P << "[(long long)grow * " << sm << "]; " << L << "[0] = t; " << L << "[1] = t; " << L << "[2] = t; " << L << "[3] = t; } ";
+            } else {
+                body << "for (int j = 0; j < 4; ++j) " << L << "[j] = " << P << "[(long long)grow * " << sm << " + (long long)(gcol + j) * " << sn << "]; ";
+            }
+        }
+    }
+    // lanes whose columns lie beyond N (the last 32-column chunk may run past it) read column 0 instead and store nothing
+    std::string cols_text = cols.str();
+    if (!cols_text.empty()) cols_text = "const int gc = gcol < N ? gcol : 0; " + cols_text;
+    auto ref = [&](const KRef& r) {
+        if (r.t == KRef::LOAD) {
+            const KLoad& ld = spec.loads[r.id];
+            if (ld.acc) return std::string("A[j]");
+            if (ld.st[0] == 0 && ld.st[1] == 0) return "S" + std::to_string(r.id);
+            return "L" + std::to_string(r.id) + "[j]";
+        }
+        return "v" + std::to_string(r.id) + "[j]";
+    };
+    body << "const float A[4] = {acc.x, acc.y, acc.z, acc.w}; ";
+    for (const KNode& kn : spec.nodes) body << "float v" << kn.node << "[4]; ";
+    if (!spec.nodes.empty()) {
+        body << "_Pragma(\"unroll\") for (int j = 0; j < 4; ++j) { ";
+        for (const KNode& kn : spec.nodes) {
+            std::string a = ref(kn.operands[0]);
+            std::string b = kn.operands.size() > 1 ? ref(kn.operands[1]) : "";
+            body << "v" << kn.node << "[j] = " << op_expr(kn.op, a, b) << "; ";
+        }
+        body << "} ";
+    }
+    const std::string at = " + (long long)grow * " + std::to_string(N) + " + gcol";
+    if (store_c) body << "*reinterpret_cast<float4*>(C" << at << ") = acc; ";
+    for (size_t o = 0; o < spec.outputs.size(); ++o) {
+        const KOutput& ko = spec.outputs[o];
+        if (ko.kind != KOutput::FULL) { g.error = "epilogue: only full outputs"; return g; }
+        auto val = [&](int j) {
+            std::string r = ref(ko.value);
+            size_t p = r.find("[j]");
+            if (p != std::string::npos) r.replace(p, 3, "[" + std::to_string(j) + "]");
+            return r;
+        };
+        if (ko.store) {
+            params << ", float* __restrict__ eout" << o;
+            body << "*reinterpret_cast<float4*>(eout" << o << at << ") = make_float4(" << val(0) << ", " << val(1) << ", " << val(2) << ", " << val(3) << "); ";
+        }
+        if (ko.twin) {
+            params << ", unsigned short* __restrict__ eout16_" << o;
+            body << "ormi_store_bf16x4(eout16_" << o << at << ", " << val(0) << ", " << val(1) << ", " << val(2) << ", " << val(3) << "); ";
+        }
+    }
+    if (twin_c) {
+        params << ", unsigned short* __restrict__ ec16";
+        body << "ormi_store_bf16x4(ec16" << at << ", acc.x, acc.y, acc.z, acc.w); ";
+    }
+    g.prelude = device_prelude();
+    g.params = params.str();
+    g.init = init.str();
+    g.cols = cols_text;
+    g.body = body.str();
+    // exact exp / division chains cost tens of instructions per element: give them more epilogue warps
+    g.wpq = spec.nodes.size() <= 2 ? 1 : (spec.nodes.size() <= 6 ? 2 : 4);
     return g;
 }
 

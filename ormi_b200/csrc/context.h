@@ -51,6 +51,7 @@ struct CachedPlan {
     // liveness of the scratch (Temp) buffers: the step that first touches buffer b and the step after which nothing
     // reads it; -1 for buffers that are not scratch
     std::vector<int> first_use, last_use;
+    std::vector<int> twin_result;   // per buffer: for a bf16 twin of a node that is handed out, the node's fp32 buffer; else -1
 };
 
 enum class MatmulMode { FP32, BF16, TF32, TF32X3 };
@@ -63,6 +64,8 @@ struct Shadow16 {
     int rows = 0, cols = 0;
     long long ld = 0;
 };
+
+struct TcKernel { CompiledKernel* kernel = nullptr; int block = 0, smem = 0; };
 
 // Generated epilogue of the run-time compiled tensor-core GEMM: text spliced into the kernel template plus the
 // device pointers of its extra parameters, in parameter order.
@@ -86,13 +89,15 @@ struct ormi_b200_ctx {
     std::unordered_map<size_t, std::vector<void*>> free_blocks;
 
     std::unordered_map<std::string, ormi_b200::CompiledKernel> kernel_cache;   // source hash -> module
-    std::unordered_map<uint64_t, std::unique_ptr<ormi_b200::CachedPlan>> plan_cache;
+    std::unordered_map<std::string, std::unique_ptr<ormi_b200::CachedPlan>> plan_cache;   // by graph_key (runtime.cu)
+    int tune[ormi_b200::kTuneKnobs] = {0, 0, 0, 0, 0, 0, 0, 0};   // code-generator overrides (SchedOptions::tune), 0 = default
 
     ormi_b200::MatmulMode matmul_mode = ormi_b200::MatmulMode::FP32;
     bool fusion = true;
 
     // bf16 twins of fp32 matmul operands, by fp32 pointer (dropped when that buffer is freed or written through the ABI)
     std::unordered_map<const void*, ormi_b200::Shadow16> shadows;
+    std::unordered_map<std::string, ormi_b200::TcKernel> tc_kernels;   // compiled variants of the tensor-core GEMM
     int tc_cta_group = 2;             // CTAs per tcgen05.mma of the bf16 GEMM: 2 = a pair of SMs per 256 x 256 tile
     // operand staging of the tf32 / 3xTF32 GEMM path (grown on demand, reused across calls)
     void* stage[2] = {nullptr, nullptr};

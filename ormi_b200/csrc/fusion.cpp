@@ -73,6 +73,17 @@ std::vector<int> canonical_dm(const std::vector<int>& shape) {
     return dm;
 }
 
+// One operand of a MATMUL as the kernel sees it: source buffer, the matrix (rows x cols of the operand), strides.
+struct OperandView {
+    int src = -1;
+    std::vector<int> sh, st;
+    int rows = 0, cols = 0, s_row = 0, s_col = 0;
+    bool ok_n = false, ok_t = false;   // rows contiguous / columns contiguous
+    // the stored matrix behind the operand: [srows][scols] with pitch ld (the operand itself, or its transpose)
+    int srows = 0, scols = 0, ld = 0;
+    bool dense = false;                // the stored matrix is the whole source buffer, contiguous
+};
+
 struct Scheduler {
     const ormi_b200_node* nodes;
     int n;
@@ -390,6 +401,40 @@ struct Scheduler {
         if (discover) info[o].in_M = true;
     }
 
+    OperandView matmul_operand(int o, bool discover) {
+        OperandView v;
+        operand_view(o, v.src, v.sh, v.st, discover);
+        const int nd = (int)v.sh.size();
+        if (nd < 2) return v;
+        v.rows = v.sh[nd - 2]; v.cols = v.sh[nd - 1];
+        v.s_row = v.st[nd - 2]; v.s_col = v.st[nd - 1];
+        v.ok_n = (v.s_col == 1 || v.cols == 1) && (v.rows == 1 || v.s_row >= v.cols);
+        v.ok_t = (v.s_row == 1 || v.rows == 1) && (v.cols == 1 || v.s_col >= v.rows);
+        if (v.ok_n) { v.srows = v.rows; v.scols = v.cols; v.ld = v.s_row; }
+        else if (v.ok_t) { v.srows = v.cols; v.scols = v.rows; v.ld = v.s_col; }
+        v.dense = (v.ok_n || v.ok_t) && v.rows > 1 && v.cols > 1 && v.ld == v.scols &&
+                  (int64_t)v.srows * v.scols == info[v.src].numel;
+        return v;
+    }
+
+    // Does MATMUL node m qualify for the tensor-core kernel (gemm_tc.cu)?  One product (no batch), large enough to be
+    // worth it, both operands row- or column-contiguous with a contiguous dimension of whole 16-byte pieces of bf16.
+    bool tc_eligible(int m) {
+        if (!opt.bf16_matmul || !opt.aligned || info[m].kind != K_MATMUL) return false;
+        const auto& nd = nodes[m];
+        OperandView a = matmul_operand(nd.parents[0], false), b = matmul_operand(nd.parents[1], false);
+        if (a.sh.size() < 2 || b.sh.size() < 2) return false;
+        int64_t batch = 1;
+        for (size_t d = 0; d + 2 < info[m].shape.size(); ++d) batch *= info[m].shape[d];
+        const int64_t M = a.rows, K = a.cols, N = b.cols;
+        if (batch != 1 || b.rows != K || M * N * K < (int64_t(1) << 21) || K < 64 || N % 4 != 0) return false;
+        for (const OperandView* v : {&a, &b}) {
+            if (!(v->ok_n || v->ok_t) || v->rows <= 1 || v->cols <= 1 || v->scols % 8 != 0 || v->ld % 8 != 0) return false;
+            for (size_t d = 0; d + 2 < v->sh.size(); ++d) if (v->sh[d] != 1) return false;
+        }
+        return true;
+    }
+
     // ------------------------------------------------------------------ the plan
     Plan run(const int* roots, int n_roots);
 };
@@ -399,25 +444,29 @@ struct StepNode {
     std::vector<int> outputs;     // M nodes
     std::vector<int> D; int k = -1;
     std::set<int> succ;
+    bool dead = false;            // FUSED: absorbed into a GEMM step as its epilogue
+    std::vector<int> epi_outputs; // GEMM: outputs of the absorbed step
+    bool tc = false;              // GEMM: runs on the tensor-core kernel (decided from shapes and options)
 };
+
 
 Plan Scheduler::run(const int* roots, int n_roots) {
     Plan plan;
     if (!classify(roots, n_roots)) { plan.error = error; return plan; }
 
     // ---- 3. materialization set
-    std::vector<int> root_bases;
+    std::vector<bool> handed(n, false);     // roots, KEEP nodes and the bases of such views: the caller receives these
     for (int r = 0; r < n_roots; ++r) {
         int i = roots[r];
         if (info[i].kind == K_INPUT) continue;
         int b = info[i].kind == K_VIEW ? info[i].base : i;
-        if (info[b].kind != K_INPUT) info[b].in_M = true;
+        if (info[b].kind != K_INPUT) { info[b].in_M = true; handed[b] = true; }
     }
     for (int i = 0; i < n; ++i) {
         if (!info[i].needed || info[i].kind == K_INPUT) continue;
         if (nodes[i].flags & ORMI_NODE_KEEP) {
             int b = info[i].kind == K_VIEW ? info[i].base : i;
-            if (info[b].kind != K_INPUT) info[b].in_M = true;
+            if (info[b].kind != K_INPUT) { info[b].in_M = true; handed[b] = true; }
         }
         if (info[i].kind == K_MATMUL || info[i].kind == K_GENSUM || info[i].kind == K_COLSUM || info[i].kind == K_GLOBALSUM) info[i].in_M = true;
         if (!opt.fusion && info[i].kind != K_VIEW) info[i].in_M = true;
@@ -481,6 +530,97 @@ Plan Scheduler::run(const int* roots, int n_roots) {
         for (const Dep& d : deps[m]) { int ds = info[d.node].step; if (ds != chosen) steps[ds].succ.insert(chosen); }
     }
 
+    // ---- 4b. matmuls on the tensor-core kernel: which qualify, what follows them, who writes their bf16 operands
+    std::vector<bool> need_twin(n, false), drop_f32(n, false);
+    std::vector<std::pair<int, int>> twin_shape(n, {0, 0});
+    std::vector<std::vector<int>> consumers(n);          // materialized node -> materialized nodes whose step reads it
+    for (int x = 0; x < n; ++x) if (info[x].in_M) for (const Dep& d : deps[x]) consumers[d.node].push_back(x);
+    if (opt.bf16_matmul && opt.fusion) {
+        for (auto& S : steps) if (S.type == StepNode::GEMM) S.tc = tc_eligible(S.outputs[0]);
+        // (a) epilogues: a flat kernel over the [M, N] domain of a qualifying matmul that reads the product moves into
+        //     the GEMM kernel, unless that would make the GEMM wait for something that itself waits for the GEMM.
+        for (size_t gs = 0; gs < steps.size(); ++gs) {
+            StepNode& Gs = steps[gs];
+            if (Gs.type != StepNode::GEMM || !Gs.tc) continue;
+            const int m = Gs.outputs[0];
+            if (info[m].sq.size() != 2) continue;
+            for (size_t fs = 0; fs < steps.size(); ++fs) {
+                StepNode& Fs = steps[fs];
+                if (Fs.type != StepNode::FUSED || Fs.dead || Fs.D != info[m].sq || Fs.k >= 0) continue;
+                bool reads_m = false, ok = true;
+                for (int o : Fs.outputs) {
+                    if (!(info[o].kind == K_PW || info[o].kind == K_IDSUM) || info[o].row_cls) ok = false;
+                    for (const Dep& d : deps[o]) {
+                        if (d.node == m) { reads_m = true; continue; }
+                        const int ds = info[d.node].step;
+                        if (ds == (int)fs) continue;
+                        if (ds == (int)gs || reaches((int)gs, ds)) ok = false;
+                    }
+                }
+                if (!ok || !reads_m) continue;
+                // the product must be read element for element (not transposed or broadcast) by every member
+                Walk w; w.D = Fs.D; w.k = -1;
+                for (int o : Fs.outputs) w.outputs.insert(o);
+                for (int o : Fs.outputs) walk_output(w, o, false, nullptr);
+                int acc_loads = 0;
+                for (const KLoad& l : w.loads) if (l.src_node == m) { ++acc_loads; if (l.st != std::vector<int64_t>{(int64_t)Fs.D[1], 1}) ok = false; }
+                if (!ok || acc_loads != 1 || w.k_conflict) continue;
+                // absorb: the outputs of Fs become outputs of the GEMM step
+                Fs.dead = true;
+                Gs.epi_outputs = Fs.outputs;
+                for (int o : Fs.outputs) info[o].step = (int)gs;
+                for (auto& T : steps) if (T.succ.erase((int)fs) && &T != &Gs) T.succ.insert((int)gs);
+                for (int t : Fs.succ) if (t != (int)gs) Gs.succ.insert(t);
+                Fs.succ.clear();
+                break;                                   // one epilogue per matmul
+            }
+        }
+        // (b) bf16 twins: an operand that is produced inside this plan is written as bf16 by its producer
+        auto want_twin = [&](int src, int rows, int cols) {
+            need_twin[src] = true;
+            if (!twin_shape[src].first) twin_shape[src] = {rows, cols};
+        };
+        for (auto& S : steps) {
+            if (S.type != StepNode::GEMM || !S.tc) continue;
+            const auto& nd = nodes[S.outputs[0]];
+            for (int p = 0; p < 2; ++p) {
+                OperandView v = matmul_operand(nd.parents[p], false);
+                if (info[v.src].kind == K_INPUT || !v.dense) continue;
+                const Kind pk = info[v.src].kind;
+                const StepNode& Ps = steps[info[v.src].step];
+                bool producer_ok = (pk == K_MATMUL && Ps.tc) ||
+                                   ((pk == K_PW || pk == K_IDSUM) && !info[v.src].row_cls && (Ps.type == StepNode::FUSED || Ps.type == StepNode::GEMM));
+                if (producer_ok) want_twin(v.src, v.srows, v.scols);
+            }
+        }
+        // a root the caller flagged: its bf16 twin is written along and remembered by the context
+        for (int x = 0; x < n; ++x) {
+            if (!info[x].in_M || !(nodes[x].flags & ORMI_NODE_TWIN16) || info[x].sq.size() != 2 || info[x].sq[1] % 8 != 0) continue;
+            const Kind pk = info[x].kind;
+            if ((pk == K_MATMUL && steps[info[x].step].tc) || ((pk == K_PW || pk == K_IDSUM) && !info[x].row_cls)) want_twin(x, info[x].sq[0], info[x].sq[1]);
+        }
+        // (c) a pointwise result nobody but tensor-core matmuls reads is not written as fp32 at all
+        for (int x = 0; x < n; ++x) {
+            if (!need_twin[x] || handed[x] || info[x].kind == K_MATMUL) continue;
+            bool only_tc = true, any = false;
+            for (int y : consumers[x]) {
+                if (info[y].step == info[x].step) continue;     // an output of the same kernel reads the value from registers
+                any = true;
+                if (!(info[y].kind == K_MATMUL && steps[info[y].step].tc)) only_tc = false;
+            }
+            only_tc = only_tc && any;
+            for (int y : consumers[x]) {       // and each of those reads it as the dense matrix the twin is
+                if (!only_tc) break;
+                if (info[y].kind != K_MATMUL) continue;
+                for (int p = 0; p < 2; ++p) {
+                    OperandView v = matmul_operand(nodes[y].parents[p], false);
+                    if (v.src == x && !v.dense) only_tc = false;
+                }
+            }
+            drop_f32[x] = only_tc;
+        }
+    }
+
     // ---- 5. buffers
     std::map<int, int> buf_of_node;   // node -> plan buffer
     auto buffer_for = [&](int node) {
@@ -498,18 +638,30 @@ Plan Scheduler::run(const int* roots, int n_roots) {
         plan.buffers.push_back(PlanBuffer{BufKind::Temp, -1, std::max<int64_t>(4, bytes)});
         return (int)plan.buffers.size() - 1;
     };
+    std::map<int, int> twin_of_node;  // node -> Twin16 plan buffer
+    auto twin_for = [&](int node) {
+        auto it = twin_of_node.find(node);
+        if (it != twin_of_node.end()) return it->second;
+        PlanBuffer b{BufKind::Twin16, node, info[node].numel * 2};
+        b.rows = twin_shape[node].first; b.cols = twin_shape[node].second;
+        plan.buffers.push_back(b);
+        twin_of_node[node] = (int)plan.buffers.size() - 1;
+        return (int)plan.buffers.size() - 1;
+    };
 
     // topological order of the steps (Kahn, lowest first output first)
     std::vector<int> indeg(steps.size(), 0), order;
     for (auto& S : steps) for (int t : S.succ) indeg[t]++;
     std::set<std::pair<int, int>> ready;
-    for (size_t s = 0; s < steps.size(); ++s) if (!indeg[s]) ready.insert({steps[s].outputs[0], (int)s});
+    size_t live_steps = 0;
+    for (auto& S : steps) live_steps += !S.dead;
+    for (size_t s = 0; s < steps.size(); ++s) if (!indeg[s] && !steps[s].dead) ready.insert({steps[s].outputs[0], (int)s});
     while (!ready.empty()) {
         int s = ready.begin()->second; ready.erase(ready.begin());
         order.push_back(s);
         for (int t : steps[s].succ) if (--indeg[t] == 0) ready.insert({steps[t].outputs[0], t});
     }
-    if (order.size() != steps.size()) { plan.error = "internal: cyclic kernel graph"; return plan; }
+    if (order.size() != live_steps) { plan.error = "internal: cyclic kernel graph"; return plan; }
 
     int kernel_serial = 0;
     for (int s : order) {
@@ -538,7 +690,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
                     KernelSpec ks;
                     ks.D = squeeze(sh[p]);
                     ks.k = -1;
-                    ks.num_sms = opt.num_sms;
+                    ks.num_sms = opt.num_sms; ks.aligned = opt.aligned; std::copy(opt.tune, opt.tune + kTuneKnobs, ks.tune);
                     std::vector<int> dm = canonical_dm(sh[p]);
                     KLoad ld{srcs[p], strides_over_domain(dm, st[p], ks.D.size())};
                     ks.loads.push_back(ld);
@@ -574,6 +726,54 @@ Plan Scheduler::run(const int* roots, int n_roots) {
                     (p == 0 ? g.astride : g.bstride)[d] = v;
                 }
             }
+            g.tc = S.tc;
+            if (S.tc) {
+                for (int p = 0; p < 2; ++p) {      // operands some earlier step of this plan writes as bf16
+                    OperandView v = matmul_operand(nd.parents[p], false);
+                    if (info[v.src].kind != K_INPUT && need_twin[v.src] && v.dense) (p == 0 ? g.a16 : g.b16) = twin_for(v.src);
+                }
+                const bool twin_c = need_twin[m];
+                bool c_read = handed[m] || (S.epi_outputs.empty() && !twin_c);
+                for (int y : consumers[m]) if (info[y].step != s) c_read = true;
+                g.store_c = c_read;
+                if (!c_read) drop_f32[m] = true;
+                if (!S.epi_outputs.empty() || twin_c || !c_read) {
+                    Walk w; w.D = info[m].sq; w.k = -1;
+                    for (int o : S.epi_outputs) w.outputs.insert(o);
+                    KernelSpec ks;
+                    for (int o : S.epi_outputs) walk_output(w, o, false, &ks.outputs);
+                    std::sort(w.members.begin(), w.members.end());
+                    ks.D = w.D; ks.k = -1; ks.num_sms = opt.num_sms; ks.aligned = opt.aligned; std::copy(opt.tune, opt.tune + kTuneKnobs, ks.tune);
+                    ks.loads = w.loads;
+                    for (KLoad& l : ks.loads) if (l.src_node == m) l.acc = true;
+                    for (int q : w.members) {
+                        KNode kn;
+                        kn.node = q;
+                        kn.op = info[q].kind == K_PW ? nodes[q].op : KNode::OP_ID;
+                        kn.row = false;
+                        kn.scalar = false;
+                        kn.operands = w.operands[q];
+                        ks.nodes.push_back(kn);
+                    }
+                    for (KOutput& o : ks.outputs) { o.twin = need_twin[o.node]; o.store = !drop_f32[o.node]; }
+                    GeneratedEpilogue ge = generate_gemm_epilogue(ks, g.store_c, twin_c);
+                    if (!ge.error.empty()) { plan.error = ge.error; return plan; }
+                    g.has_epi = true;
+                    g.epi_prelude = ge.prelude; g.epi_params = ge.params; g.epi_init = ge.init; g.epi_cols = ge.cols; g.epi_body = ge.body;
+                    g.epi_wpq = ge.wpq;
+                    for (const KLoad& l : ks.loads) if (!l.acc) g.epi_args.push_back(buffer_for(l.src_node));
+                    for (const KOutput& o : ks.outputs) {
+                        if (o.store) g.epi_args.push_back(buffer_for(o.node));
+                        if (o.twin) g.epi_args.push_back(twin_for(o.node));
+                    }
+                    if (twin_c) g.epi_args.push_back(twin_for(m));
+                    std::ostringstream what;
+                    what << "epilogue[nodes=" << ks.nodes.size() << ",loads=" << ks.loads.size() - 1 << ",outs=";
+                    for (const KOutput& o : ks.outputs) what << (o.store ? "F" : "") << (o.twin ? "h" : "");
+                    what << ",product=" << (g.store_c ? "F" : "") << (twin_c ? "h" : "") << ",wpq=" << ge.wpq << "]";
+                    g.epi_what = what.str();
+                }
+            }
             Step stp; stp.type = Step::Gemm; stp.g = g;
             plan.steps.push_back(stp);
             continue;
@@ -598,7 +798,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
         for (int m : S.outputs) walk_output(w, m, false, &ks.outputs);
         if (w.k_conflict) { plan.error = "internal: kernel with two different row/column splits"; return plan; }
         std::sort(w.members.begin(), w.members.end());
-        ks.D = w.D; ks.k = w.k; ks.num_sms = opt.num_sms;
+        ks.D = w.D; ks.k = w.k; ks.num_sms = opt.num_sms; ks.aligned = opt.aligned; std::copy(opt.tune, opt.tune + kTuneKnobs, ks.tune);
         ks.loads = w.loads;
         for (int q : w.members) {
             KNode kn;
@@ -610,6 +810,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
             kn.operands = w.operands[q];
             ks.nodes.push_back(kn);
         }
+        for (KOutput& o : ks.outputs) if (o.kind == KOutput::FULL && o.node >= 0) { o.twin = need_twin[o.node]; o.store = !drop_f32[o.node]; }
         GeneratedKernel gk = generate_kernel(ks, "ormi_fused_" + std::to_string(kernel_serial++), nodes);
         if (!gk.error.empty()) {
             if (gk.unsupported_sums) {   // the row/column template cannot take this shape: retry with generic sums
@@ -625,8 +826,10 @@ Plan Scheduler::run(const int* roots, int n_roots) {
         std::vector<std::pair<int, int>> finals;   // (scratch buffer, output index)
         for (size_t oi = 0; oi < ks.outputs.size(); ++oi) {
             const KOutput& o = ks.outputs[oi];
-            if (o.kind == KOutput::FULL || o.kind == KOutput::ROW) stp.k.args.push_back(buffer_for(o.node));
-            else {
+            if (o.kind == KOutput::FULL || o.kind == KOutput::ROW) {
+                if (o.store) stp.k.args.push_back(buffer_for(o.node));
+                if (o.twin) stp.k.args.push_back(twin_for(o.node));
+            } else {
                 int64_t per = o.kind == KOutput::COLSUM ? gk.cols : 1;
                 int tmp = temp_buffer(per * 4 * gk.step.grid);
                 stp.k.args.push_back(tmp);
@@ -653,7 +856,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
     // ---- results: every materialized node, plus roots / KEEP nodes that are views (aliases)
     for (int i = 0; i < n; ++i) {
         if (!info[i].needed || info[i].kind == K_INPUT) continue;
-        if (info[i].in_M) plan.results.push_back(NodeResult{i, buffer_for(i), false});
+        if (info[i].in_M && !drop_f32[i]) plan.results.push_back(NodeResult{i, buffer_for(i), false});
     }
     auto alias_result = [&](int i) {
         if (info[i].kind != K_VIEW) return;
@@ -692,7 +895,7 @@ std::string plan_to_json(const Plan& plan) {
     o << "{\"error\": \"" << json_escape(plan.error) << "\", \"buffers\": [";
     for (size_t i = 0; i < plan.buffers.size(); ++i) {
         const auto& b = plan.buffers[i];
-        o << (i ? ", " : "") << "{\"kind\": \"" << (b.kind == BufKind::External ? "external" : b.kind == BufKind::NodeOut ? "node" : b.kind == BufKind::ErrorWord ? "error" : "temp")
+        o << (i ? ", " : "") << "{\"kind\": \"" << (b.kind == BufKind::External ? "external" : b.kind == BufKind::NodeOut ? "node" : b.kind == BufKind::ErrorWord ? "error" : b.kind == BufKind::Twin16 ? "twin16" : "temp")
           << "\", \"node\": " << b.node << ", \"bytes\": " << b.bytes << "}";
     }
     o << "], \"steps\": [";
@@ -715,7 +918,11 @@ std::string plan_to_json(const Plan& plan) {
             for (int d = 0; d < g.nbatch; ++d) o << (d ? ", " : "") << g.astride[d];
             o << "], \"bstride\": [";
             for (int d = 0; d < g.nbatch; ++d) o << (d ? ", " : "") << g.bstride[d];
-            o << "]}";
+            o << "], \"tc\": " << (g.tc ? "true" : "false") << ", \"a16\": " << g.a16 << ", \"b16\": " << g.b16
+              << ", \"store_c\": " << (g.store_c ? "true" : "false") << ", \"epilogue\": \"" << json_escape(g.epi_what) << "\", \"epi_args\": [";
+            for (size_t a = 0; a < g.epi_args.size(); ++a) o << (a ? ", " : "") << g.epi_args[a];
+            o << "], \"epi_body\": \"" << json_escape(g.epi_body) << "\", \"epi_cols\": \"" << json_escape(g.epi_cols) << "\", \"epi_init\": \""
+              << json_escape(g.epi_init) << "\", \"epi_params\": \"" << json_escape(g.epi_params) << "\", \"epi_prelude\": \"" << json_escape(g.epi_prelude) << "\"}";
         }
     }
     o << "], \"results\": [";

@@ -170,9 +170,20 @@ void gemm_tc(ormi_b200_ctx* ctx, const void* a16, int a_mn, const void* b16, int
     if ((a_mn ? M : K) % 8 || (b_mn ? N : K) % 8 || N % 4) throw Error("gemm_tc: the contiguous dimension of each bf16 operand must be a multiple of 8 and N a multiple of 4");
     if (((uintptr_t)a16 | (uintptr_t)b16 | (uintptr_t)C) & 15) throw Error("gemm_tc: operands must be 16-byte aligned");
     int cg = ctx->tc_cta_group;
-    const Variant v = make_variant(cg, a_mn, b_mn, epi ? epi->wpq : 1);
-    const KernelStep ks = make_kernel(v, epi);
-    CompiledKernel* k = get_kernel(ctx, ks);
+    // the kernel of this variant: looked up by its few parameters and the epilogue text, not by the whole source
+    std::string vkey = std::to_string(cg) + "|" + std::to_string(a_mn) + "|" + std::to_string(b_mn);
+    if (epi) vkey += "|" + std::to_string(epi->wpq) + "|" + epi->params + "|" + epi->init + "|" + epi->cols + "|" + epi->body;
+    auto found = ctx->tc_kernels.find(vkey);
+    if (found == ctx->tc_kernels.end()) {
+        const Variant v = make_variant(cg, a_mn, b_mn, epi ? epi->wpq : 1);
+        const KernelStep made = make_kernel(v, epi);
+        TcKernel tk;
+        tk.kernel = get_kernel(ctx, made);
+        tk.block = made.block; tk.smem = made.dyn_smem;
+        found = ctx->tc_kernels.emplace(vkey, tk).first;
+    }
+    CompiledKernel* k = found->second.kernel;
+    struct { int block, dyn_smem; } ks{found->second.block, found->second.smem};
     CUtensorMap map_a, map_b;
     if (a_mn) make_map(ctx, &map_a, a16, K, M, M, 64);            // stored [K][M]
     else make_map(ctx, &map_a, a16, M, K, K, 128);                // stored [M][K]

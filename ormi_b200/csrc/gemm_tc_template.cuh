@@ -53,7 +53,7 @@ constexpr int EPI_WARPS = 4 * EPI_WPQ;
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNC * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int STG_BYTES = 4096;               // per epilogue warp: 32 rows x 128 bytes
-constexpr int GROUP_M = 8;
+constexpr int GROUP_M = 16 / CG;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -76,15 +76,28 @@ __device__ __forceinline__ unsigned in_cta(unsigned addr, unsigned cta) {
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
-// Arrivals and waits use cluster scope so that a signal may come from the other CTA of the pair; `bar` is a
-// shared::cluster address (in_cta) for arrivals and a plain shared::cta address for waits.
+// Barrier operations come in two strengths.  The per-stage ring and the accumulator hand-over carry no data written
+// by ordinary stores (TMA and tcgen05 deliver it, the barriers only count), so they use the default CTA-scope
+// forms, also for an arrival on the other CTA's barrier: a cluster-scope release there is a memory fence on the
+// producer's critical path, once per 64 k.  The tile schedule slot IS written by an ordinary (remote) store, once per
+// tile, so its arrivals release and its waits acquire at cluster scope.  `bar` is a shared::cluster address (in_cta)
+// for arrivals and a plain shared::cta address for waits.
 __device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_release_cluster(unsigned bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait_acquire_cluster(unsigned bar, unsigned parity) {
     unsigned ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
@@ -106,11 +119,13 @@ __device__ __forceinline__ void raise_abort(Shared& sh, int code) {
 }
 
 // Bounded wait.  Returns false when the pair is aborting (this wait ran out, or another role's did).
+template <bool CLUSTER_ACQUIRE = false>
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, Shared& sh, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
+    auto poll = [&]() { return CLUSTER_ACQUIRE ? mbar_try_wait_acquire_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+    if (poll()) return true;
     const unsigned long long t0 = global_ns();
     for (;;) {
-        for (int i = 0; i < 64; ++i) if (mbar_try_wait(bar, parity)) return true;
+        for (int i = 0; i < 64; ++i) if (poll()) return true;
         if (sh.abort_flag) return false;
         if (global_ns() - t0 > WAIT_LIMIT_NS) { raise_abort(sh, code); return false; }
     }
@@ -276,7 +291,7 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
             while (ok) {
                 int t;
                 if (rank == 0) {
-                    if (!mbar_wait(sempty_bar(q), qphase ^ 1u, sh, 5)) break;
+                    if (!mbar_wait<true>(sempty_bar(q), qphase ^ 1u, sh, 5)) break;
                     t = atomicAdd(tile_counter, 1);
                     if (t >= num_tiles) {
                         // Every leader draws exactly one index past the end; the one that draws the last leaves the
@@ -287,13 +302,13 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
                     sched_tile[q] = t;
 #if G_CTA_GROUP == 2
                     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(in_cta(smem_u32((const void*)&sched_tile[q]), 1u)), "r"(t) : "memory");
-                    mbar_arrive(in_cta(sfull_bar(q), 1u));
+                    mbar_arrive_release_cluster(in_cta(sfull_bar(q), 1u));
 #endif
-                    mbar_arrive(in_cta(sfull_bar(q), 0u));
+                    mbar_arrive_release_cluster(in_cta(sfull_bar(q), 0u));
                 } else {
-                    if (!mbar_wait(sfull_bar(q), qphase, sh, 5)) break;
+                    if (!mbar_wait<true>(sfull_bar(q), qphase, sh, 5)) break;
                     t = sched_tile[q];
-                    mbar_arrive(in_cta(sempty_bar(q), 0u));
+                    mbar_arrive_release_cluster(in_cta(sempty_bar(q), 0u));
                 }
                 if (++q == SCHED) { q = 0; qphase ^= 1u; }
                 if (t < 0) break;
@@ -334,9 +349,9 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
             int s = 0; unsigned phase = 0;
             int q = 0; unsigned qphase = 0;
             for (int it = 0;; ++it) {
-                if (!mbar_wait(sfull_bar(q), qphase, sh, 6)) break;
+                if (!mbar_wait<true>(sfull_bar(q), qphase, sh, 6)) break;
                 const int t = sched_tile[q];
-                mbar_arrive(in_cta(sempty_bar(q), 0u));
+                mbar_arrive_release_cluster(in_cta(sempty_bar(q), 0u));
                 if (++q == SCHED) { q = 0; qphase ^= 1u; }
                 if (t < 0) break;
                 const int a = it & 1;
@@ -370,12 +385,12 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
         G_EPI_INIT
         int q = 0; unsigned qphase = 0;
         for (int it = 0;; ++it) {
-            bool got = mbar_wait(sfull_bar(q), qphase, sh, 7);
+            bool got = mbar_wait<true>(sfull_bar(q), qphase, sh, 7);
             got = __all_sync(0xffffffffu, got);
             if (!got) break;
             const int t = sched_tile[q];
             __syncwarp();                                     // every lane has read the slot
-            if (lane == 0) mbar_arrive(in_cta(sempty_bar(q), 0u));
+            if (lane == 0) mbar_arrive_release_cluster(in_cta(sempty_bar(q), 0u));
             if (++q == SCHED) { q = 0; qphase ^= 1u; }
             if (t < 0) break;
             int mb, nb; tile_coords(t, tiles_m, tiles_n, mb, nb);

@@ -17,6 +17,7 @@ struct KRef {
 struct KLoad {
     int src_node;               // node whose buffer is read
     std::vector<int64_t> st;    // element stride per domain dim (0 = broadcast)
+    bool acc = false;           // GEMM epilogue only: the value is the accumulator of the matmul, not a memory read
 };
 
 struct KNode {
@@ -34,6 +35,11 @@ struct KOutput {
     int node;                   // materialized node (-1: anonymous gather target)
     KRef value;                 // what is stored (FULL/ROW) or accumulated (COLSUM/GLOBALSUM)
     bool is_max = false;        // COLSUM/GLOBALSUM: keep the maximum instead of adding (ORMI_OP_MAX)
+    // FULL only: `store` = write the fp32 values; `twin` = also (or only) write a contiguous bf16 copy, the form in
+    // which a tensor-core matmul of the same plan reads this node.  Argument order: fp32 pointer (if store), then
+    // bf16 pointer (if twin).
+    bool store = true;
+    bool twin = false;
 };
 
 struct KernelSpec {
@@ -43,13 +49,8 @@ struct KernelSpec {
     std::vector<KNode> nodes;   // in topological (index) order
     std::vector<KOutput> outputs;
     int num_sms = 148;
-    // rows template tuning: elements per thread (0 = default), keep row-invariant vectors in registers,
-    // minimum resident blocks per SM for __launch_bounds__ (0 = none), blocks per SM in the grid (0 = default)
-    int tune_vpt = 0;
-    int tune_hoist = 1;
-    int tune_minblocks = 0;
-    int tune_grid = 0;
-    int tune_stage = -1;        // stage row operands through shared memory with bulk async copies (-1 = automatic)
+    bool aligned = true;        // every buffer starts on a 16-byte boundary (else scalar accesses only, no bulk copies)
+    int tune[kTuneKnobs] = {0, 0, 0, 0, 0, 0, 0, 0};   // SchedOptions::tune
 };
 
 struct GeneratedKernel {
@@ -62,6 +63,18 @@ struct GeneratedKernel {
 // Argument order of a generated fused kernel: one pointer per load (in order), then one per output
 // (FULL/ROW: the output buffer; COLSUM/GLOBALSUM: a scratch buffer of grid x {cols|1} partials).
 GeneratedKernel generate_kernel(const KernelSpec& spec, const std::string& name, const ormi_b200_node* nodes);
+// Epilogue of the run-time compiled tensor-core GEMM: the pointwise work of `spec` (domain [M, N], every output FULL)
+// on the accumulator, as text for the kernel template.  The load flagged `acc` is the matmul itself; `store_c` /
+// `twin_c` say whether the raw product is written as fp32 / as bf16.  Kernel-argument order: every other load in
+// order, then per output the fp32 pointer (if store) and the bf16 pointer (if twin), then the product's bf16 pointer
+// (if twin_c).
+struct GeneratedEpilogue {
+    std::string prelude, params, init, cols, body;
+    int wpq = 1;
+    std::string error;
+};
+GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, bool twin_c);
+
 // out[c] = sum over p < parts of partial[p * width + c]   (fixed order: deterministic)
 GeneratedKernel generate_finalize(int parts, int64_t width, const std::string& name, bool is_max = false);
 // One thread per output element, serial sum over the reduced coordinates, arbitrary input strides.

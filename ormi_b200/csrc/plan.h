@@ -15,12 +15,14 @@ namespace ormi_b200 {
 // keeps its tile counter in another line of the same buffer).
 constexpr int kRowCounterWord = 48;
 
-enum class BufKind { External, NodeOut, Temp, ErrorWord /* the context's device error word */ };
+enum class BufKind { External, NodeOut, Temp, ErrorWord /* the context's device error word */,
+                     Twin16 /* contiguous bf16 copy of a node's value, read by tensor-core matmuls */ };
 
 struct PlanBuffer {
     BufKind kind;
-    int     node;    // External: node whose `data` is read; NodeOut: node that owns the buffer afterwards
+    int     node;    // External: node whose `data` is read; NodeOut: node that owns the buffer afterwards; Twin16: the node copied
     int64_t bytes;
+    int     rows = 0, cols = 0;   // Twin16: the matrix shape under which matmuls read it
 };
 
 struct KernelStep {
@@ -48,6 +50,14 @@ struct GemmStep {
     int64_t astride[ORMI_B200_MAX_DIMS] = {0};   // per output batch dim; 0 = broadcast
     int64_t bstride[ORMI_B200_MAX_DIMS] = {0};
     int node = -1;
+    // "bf16" matmul arithmetic on the run-time compiled tensor-core kernel (gemm_tc.cu)
+    bool tc = false;                     // the shapes qualify (decided when the plan is built)
+    int a16 = -1, b16 = -1;              // Twin16 plan buffers written earlier in the plan (-1: the context's twin cache, or a conversion)
+    bool store_c = true;                 // write the fp32 product to `c`
+    bool has_epi = false;                // pointwise work fused behind the accumulator
+    std::string epi_prelude, epi_params, epi_init, epi_cols, epi_body, epi_what;
+    int epi_wpq = 1;
+    std::vector<int> epi_args;           // plan buffer ids, in the epilogue's parameter order
 };
 
 struct Step {
@@ -69,9 +79,18 @@ struct Plan {
     std::string error;                 // non-empty: scheduling failed
 };
 
+// Overrides of the code generator's measured defaults, for experiments (ormi_b200_set_option "tune.<name>"); 0 keeps the
+// default.  They are part of the plan key.
+enum TuneKnob { TUNE_ROWS_VPT = 0, TUNE_ROWS_MINB, TUNE_ROWS_GRID, TUNE_ROWS_STAGE /* 1 off, 2 on */, TUNE_ROWS_NSTAGE,
+                TUNE_ROWS_DYNAMIC /* 1 off, 2 on */, TUNE_FLAT_UNROLL, TUNE_ROWS_HOIST /* 1 off, 2 on */ };
+constexpr int kTuneKnobs = 8;
+
 struct SchedOptions {
     int  num_sms = 148;
     bool fusion = true;
+    bool bf16_matmul = false;   // matmuls run on the tensor-core kernel: fuse epilogues, let producers write bf16 twins
+    bool aligned = true;        // every realized input starts on a 16-byte boundary (else: no 128-bit accesses, no bulk copies)
+    int  tune[kTuneKnobs] = {0, 0, 0, 0, 0, 0, 0, 0};
 };
 
 Plan build_plan(const ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots, const SchedOptions& opt);

@@ -205,10 +205,14 @@ int* device_error_word(ormi_b200_ctx* ctx) {
 }
 
 // ------------------------------------------------------------------------------------------------ realize
-static uint64_t graph_hash(const ormi_b200_ctx* ctx, const ormi_b200_node* nodes, int n, const int* roots, int n_roots) {
-    uint64_t h = 1469598103934665603ull;
-    auto mix = [&](uint64_t v) { h ^= v; h *= 1099511628211ull; };
-    mix((uint64_t)n); mix(ctx->fusion ? 1 : 0);
+// Everything a schedule depends on, as a string of words: the options, and per node the fields the scheduler reads.
+// Two calls share a cached plan when their keys are EQUAL (the map is keyed by the text, not by a hash of it).
+static std::string graph_key(const ormi_b200_ctx* ctx, const ormi_b200_node* nodes, int n, const int* roots, int n_roots, bool aligned) {
+    std::string key;
+    key.reserve((size_t)n * 48 + 64);
+    auto mix = [&](uint64_t v) { const uint32_t w = (uint32_t)v; key.append(reinterpret_cast<const char*>(&w), 4); };
+    mix((uint64_t)n); mix(ctx->fusion ? 1 : 0); mix((uint64_t)ctx->matmul_mode); mix(aligned ? 1 : 0); mix((uint64_t)ctx->tc_cta_group);
+    for (int v : ctx->tune) mix((uint64_t)(uint32_t)v);
     for (int i = 0; i < n; ++i) {
         const auto& nd = nodes[i];
         mix((uint64_t)nd.op); mix((uint64_t)nd.n_parents);
@@ -217,17 +221,23 @@ static uint64_t graph_hash(const ormi_b200_ctx* ctx, const ormi_b200_node* nodes
         for (int d = 0; d < nd.ndim; ++d) { mix((uint64_t)(uint32_t)nd.shape[d]); mix((uint64_t)(uint32_t)nd.strides[d]); }
         mix((uint64_t)nd.n_axes);
         for (int a = 0; a < nd.n_axes; ++a) mix((uint64_t)nd.axes[a]);
-        mix((uint64_t)nd.keepdims); mix((uint64_t)(nd.flags & ORMI_NODE_KEEP));
+        mix((uint64_t)nd.keepdims); mix((uint64_t)(nd.flags & (ORMI_NODE_KEEP | ORMI_NODE_TWIN16)));
         mix(nd.data ? (nd.data_bytes == 4 ? 2 : 1) : 0);
     }
+    mix(0xffffffffu);
     for (int r = 0; r < n_roots; ++r) mix((uint64_t)roots[r]);
-    return h;
+    return key;
 }
 
 void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots,
              const std::vector<std::pair<int, void*>>* preassigned) {
     ORMI_CUDA(cudaSetDevice(ctx->device));
-    uint64_t key = graph_hash(ctx, nodes, n_nodes, roots, n_roots);
+    // 128-bit loads, bulk copies and TMA need 16-byte aligned buffers.  Pool blocks are; a caller's own pointer may
+    // not be, and then the whole plan is generated with scalar accesses (the bit is part of the plan key).
+    bool aligned = true;
+    for (int i = 0; i < n_nodes; ++i) if (nodes[i].data && ((uintptr_t)nodes[i].data & 15)) aligned = false;
+    if (preassigned) for (auto& pr : *preassigned) if ((uintptr_t)pr.second & 15) aligned = false;
+    const std::string key = graph_key(ctx, nodes, n_nodes, roots, n_roots, aligned);
     CachedPlan* cp = nullptr;
     auto it = ctx->plan_cache.find(key);
     if (it != ctx->plan_cache.end()) { cp = it->second.get(); ctx->counters["plan_cache_hits"]++; }
@@ -235,6 +245,9 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
         SchedOptions opt;
         opt.num_sms = ctx->num_sms;
         opt.fusion = ctx->fusion;
+        opt.bf16_matmul = ctx->matmul_mode == MatmulMode::BF16;
+        opt.aligned = aligned;
+        std::copy(std::begin(ctx->tune), std::end(ctx->tune), opt.tune);
         auto fresh = std::make_unique<CachedPlan>();
         fresh->plan = build_plan(nodes, n_nodes, roots, n_roots, opt);
         if (!fresh->plan.error.empty()) throw Error(fresh->plan.error);
@@ -247,14 +260,22 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
         fresh->last_use.assign(p.buffers.size(), -1);
         for (size_t si = 0; si < p.steps.size(); ++si) {
             const Step& s = p.steps[si];
-            std::vector<int> used = s.type == Step::Kernel ? s.k.args : std::vector<int>{s.g.a, s.g.b, s.g.c};
+            std::vector<int> used = s.type == Step::Kernel ? s.k.args : std::vector<int>{s.g.a, s.g.b, s.g.c, s.g.a16, s.g.b16};
+            if (s.type == Step::Gemm) used.insert(used.end(), s.g.epi_args.begin(), s.g.epi_args.end());
             for (int b : used) {
-                if (b < 0 || p.buffers[b].kind != BufKind::Temp) continue;
+                if (b < 0 || (p.buffers[b].kind != BufKind::Temp && p.buffers[b].kind != BufKind::Twin16)) continue;
                 if (fresh->first_use[b] < 0) fresh->first_use[b] = (int)si;
                 fresh->last_use[b] = (int)si;
             }
         }
         for (const NodeResult& r : p.results) { fresh->first_use[r.buffer] = -1; fresh->last_use[r.buffer] = -1; }   // handed out: never scratch
+        // the bf16 twin of a node that is handed out stays with the context (later calls find it by the fp32 pointer)
+        fresh->twin_result.assign(p.buffers.size(), -1);
+        for (size_t b = 0; b < p.buffers.size(); ++b) {
+            if (p.buffers[b].kind != BufKind::Twin16) continue;
+            for (const NodeResult& r : p.results)
+                if (!r.alias && r.node == p.buffers[b].node) { fresh->twin_result[b] = r.buffer; fresh->first_use[b] = -1; fresh->last_use[b] = -1; }
+        }
         cp = fresh.get();
         ctx->plan_cache[key] = std::move(fresh);
     }
@@ -294,7 +315,16 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
                 std::memcpy(g.bshape, st.g.bshape, sizeof g.bshape);
                 std::memcpy(g.astride, st.g.astride, sizeof g.astride);
                 std::memcpy(g.bstride, st.g.bstride, sizeof g.bstride);
-                gemm_dispatch(ctx, g);
+                if (st.g.tc) {
+                    TcEpilogue epi;
+                    if (st.g.has_epi) {
+                        epi.prelude = st.g.epi_prelude; epi.params = st.g.epi_params; epi.init = st.g.epi_init;
+                        epi.cols = st.g.epi_cols; epi.body = st.g.epi_body; epi.wpq = st.g.epi_wpq;
+                        for (int a : st.g.epi_args) epi.args.push_back(bufs[a]);
+                    }
+                    gemm_tc_from_fp32(ctx, g, st.g.a16 >= 0 ? bufs[st.g.a16] : nullptr, st.g.b16 >= 0 ? bufs[st.g.b16] : nullptr,
+                                      st.g.has_epi ? &epi : nullptr);
+                } else gemm_dispatch(ctx, g);
             }
             for (size_t b = 0; b < plan.buffers.size(); ++b)
                 if (cp->last_use[b] == (int)s && bufs[b]) { pool_free(ctx, bufs[b], (size_t)plan.buffers[b].bytes); bufs[b] = nullptr; handed[b] = true; }
@@ -311,6 +341,12 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
         if (r.alias) nd.flags |= ORMI_NODE_ALIAS;
         else if (handed[r.buffer]) nd.flags |= ORMI_NODE_ALIAS;   // caller-owned target
         else { nd.flags |= ORMI_NODE_OWNED; handed[r.buffer] = true; }
+    }
+    for (size_t b = 0; b < plan.buffers.size(); ++b) {
+        if (plan.buffers[b].kind == BufKind::Twin16 && cp->twin_result[b] >= 0 && bufs[b]) {
+            shadow_register(ctx, bufs[cp->twin_result[b]], bufs[b], plan.buffers[b].rows, plan.buffers[b].cols, plan.buffers[b].cols);
+            handed[b] = true;
+        }
     }
     for (size_t b = 0; b < plan.buffers.size(); ++b)
         if (plan.buffers[b].kind != BufKind::External && !handed[b]) pool_free(ctx, bufs[b], (size_t)plan.buffers[b].bytes);

@@ -62,6 +62,7 @@ REDUCE_OPS = (OpEnum.SUM, OpEnum.MAX)
 NODE_KEEP = 1
 NODE_OWNED = 2
 NODE_ALIAS = 4
+NODE_TWIN16 = 8           # in: also write this root's bf16 copy ("bf16" matmul arithmetic; a later matmul reads it)
 NODE_REQUIRES_GRAD = 0x100  # only read by the oracle driver
 
 
@@ -138,7 +139,7 @@ class Buffer:
 class Node:
     """Mirror of ormi::Node (ormi-core/csrc/core/node.h:12-37)."""
     __slots__ = ("op", "parents", "data", "grad", "requires_grad", "shape", "strides",
-                 "axes", "keepdims", "keep", "name", "__weakref__")
+                 "axes", "keepdims", "keep", "twin16", "name", "__weakref__")
 
     def __init__(self, op, parents=(), *, data: Buffer | None = None, requires_grad=False,
                  axes: Sequence[int] = (), keepdims=False, shape: Sequence[int] | None = None):
@@ -149,6 +150,7 @@ class Node:
         self.axes = [int(a) for a in axes]
         self.keepdims = bool(keepdims)
         self.keep = False
+        self.twin16 = False
         self.name = None
         if self.op == OpEnum.LEAF:
             # leaf constructor, node.cpp:8-13
@@ -631,7 +633,7 @@ def flatten(roots: Sequence[Node], *, host_pointers=False, stop_at_realized=True
         for d, a in enumerate(n.axes):
             c.axes[d] = a
         c.keepdims = int(n.keepdims)
-        c.flags = (NODE_KEEP if n.keep else 0) | (NODE_REQUIRES_GRAD if n.requires_grad else 0)
+        c.flags = (NODE_KEEP if n.keep else 0) | (NODE_TWIN16 if n.twin16 else 0) | (NODE_REQUIRES_GRAD if n.requires_grad else 0)
         if n.is_realized and stop_at_realized or n.op == OpEnum.LEAF:
             c.n_parents = 0
             buf = n.data

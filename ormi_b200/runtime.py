@@ -142,14 +142,15 @@ def _find_buffer(order, ptr):
     raise RuntimeError("alias of an unknown buffer")
 
 
-def plan(roots: Sequence[G.Node], host_pointers=True) -> dict:
-    """The schedule the backend would run for ``roots`` (needs no GPU)."""
+def plan(roots: Sequence[G.Node], host_pointers=True, options: str = "") -> dict:
+    """The schedule the backend would run for ``roots`` (needs no GPU).  ``options``: "matmul=bf16,fusion=on,..."."""
     arr, order, root_idx = G.flatten(list(roots), host_pointers=host_pointers, stop_at_realized=True)
     ridx = (ctypes.c_int * len(root_idx))(*root_idx)
     n = ctypes.c_size_t()
-    check(lib.ormi_b200_plan_json(arr, len(order), ridx, len(root_idx), None, 0, ctypes.byref(n)))
+    opts = options.encode()
+    check(lib.ormi_b200_plan_json_opts(arr, len(order), ridx, len(root_idx), opts, None, 0, ctypes.byref(n)))
     buf = ctypes.create_string_buffer(n.value + 1)
-    check(lib.ormi_b200_plan_json(arr, len(order), ridx, len(root_idx), buf, n.value + 1, ctypes.byref(n)))
+    check(lib.ormi_b200_plan_json_opts(arr, len(order), ridx, len(root_idx), opts, buf, n.value + 1, ctypes.byref(n)))
     out = json.loads(buf.value.decode())
     out["order"] = order
     out["roots"] = root_idx

@@ -130,8 +130,14 @@ class MLPTrainer:
         G.compute_gradients(loss)
         self.names = ["w1", "b1", "w2", "b2"]
         grads = {k: params[k].grad for k in self.names}
+
+        def weight_update(node, k):
+            # the new weight matrices are matmul operands of the next step: in "bf16" arithmetic the update kernel
+            # writes their bf16 copies along (the flag is ignored by the other arithmetics)
+            node.twin16 = k in ("w1", "w2")
+            return node
         if world == 1:
-            ups = [W.sgd_update(params[k], lr) for k in self.names]
+            ups = [weight_update(W.sgd_update(params[k], lr), k) for k in self.names]
             p.add_phase([loss] + ups)
         else:
             # the updates read the summed gradients as plain inputs; until a step has produced some they are zero
@@ -142,7 +148,12 @@ class MLPTrainer:
                 p.external("g" + k, g_leaf[k])
                 self._zero[k] = p.ext_ptr["g" + k]
             lr_c = dev.const(lr)
-            up = {k: G.sub(params[k], G.mul(lr_c, g_leaf[k])) for k in self.names}
+            up = {k: weight_update(G.sub(params[k], G.mul(lr_c, g_leaf[k])), k) for k in self.names}
+            # what a later phase reads is held on to explicitly: the first product (the backward pass re-derives the
+            # GELU from it) and the gradient of the output (its matmuls are split over phases B1 and B2)
+            taps["xw1"].keep = True
+            if taps["out"].grad is not None:
+                taps["out"].grad.keep = True
             p.add_phase([taps["h"]])                             # F
             p.add_phase([up["w2"], up["b2"]])                    # U2
             p.add_phase([loss, grads["w1"], grads["b1"]])        # B1

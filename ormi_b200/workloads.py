@@ -64,12 +64,14 @@ def gelu_tanh(u):
 
 def mlp_loss(x, w1, b1, w2, b2, t, scale=None, taps=None):
     """loss = mean((gelu(x@W1 + b1) @ W2 + b2 - t)^2); ``scale`` overrides 1/(B*D) (batch-sharded runs
-    divide by the global batch).  ``taps``, a dict, receives the hidden activation node under "h"."""
-    u = G.add(G.matmul(x, w1), b1)
+    divide by the global batch).  ``taps``, a dict, receives the hidden activation node under "h", the first matmul
+    under "xw1" and the output under "out" (a host loop that realizes the step in several calls holds on to these)."""
+    xw1 = G.matmul(x, w1)
+    u = G.add(xw1, b1)
     h = gelu_tanh(u)
-    if taps is not None:
-        taps["h"] = h
     out = G.add(G.matmul(h, w2), b2)
+    if taps is not None:
+        taps["h"], taps["xw1"], taps["out"] = h, xw1, out
     d = G.sub(out, t)
     if scale is None:
         scale = 1.0 / (out.shape[0] * out.shape[1])

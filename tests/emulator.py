@@ -1,8 +1,10 @@
 """TEST INFRASTRUCTURE: executes a schedule (ormi_b200.runtime.plan) on the CPU.
 
 Every generated kernel is compiled unchanged with g++ against tests/cuda_emul.h and launched with its
-real grid/block geometry; GEMM steps are computed with numpy.  This checks the scheduler and the code
-generator against the oracle without a GPU.  It is not a fallback: nothing in the package imports it.
+real grid/block geometry; GEMM steps are computed with numpy — for a step of the tensor-core kernel, on operands
+rounded to bf16 (taken from the bf16 twin an earlier step wrote, when the plan says so), followed by the step's
+generated epilogue, compiled from the same text the kernel template receives.  This checks the scheduler and the
+code generator against the oracle without a GPU.  It is not a fallback: nothing in the package imports it.
 """
 from __future__ import annotations
 
@@ -46,9 +48,12 @@ def run_plan(plan: dict) -> dict:
         elif b["kind"] == "external":
             host = order[b["node"]].data.host
             bufs.append(np.ascontiguousarray(host, dtype=np.float32).reshape(-1))
+        elif b["kind"] == "twin16":
+            bufs.append(np.full(max(1, b["bytes"] // 2), 0x7fc0, dtype=np.uint16))      # bf16 NaN until written
         else:
             bufs.append(np.full(max(1, b["bytes"] // 4), np.nan, dtype=np.float32))
     kernels = [(s["name"], s["source"]) for s in plan["steps"] if s["type"] == "kernel"]
+    kernels += [(f"epi_{i}", _epilogue_source(f"epi_{i}", s)) for i, s in enumerate(plan["steps"]) if s["type"] == "gemm" and s.get("epilogue")]
     lib = _compile(kernels) if kernels else None
     for s in plan["steps"]:
         if s["type"] == "kernel":
@@ -56,9 +61,50 @@ def run_plan(plan: dict) -> dict:
             args = (ctypes.c_void_p * len(s["args"]))(*[bufs[a].ctypes.data for a in s["args"]])
             rc = lib.emul_launch(fn, s["grid"], s["block"], args, len(s["args"]))
             assert rc == 0
+        elif s.get("tc"):
+            _gemm_tc(s, bufs, lib, f"epi_{plan['steps'].index(s)}")
         else:
             _gemm(s, bufs)
     return {r["node"]: bufs[r["buffer"]] for r in plan["results"]}
+
+
+def _epilogue_source(name, s):
+    """The generated epilogue text of a tensor-core GEMM step as a plain loop over (row, 4 columns)."""
+    return (s["epi_prelude"] + f'\nextern "C" void {name}(float* C, const float* P, int M, int N{s["epi_params"]}) {{\n'
+            f'    {s["epi_init"]}\n    for (int grow = 0; grow < M; ++grow) for (int gcol = 0; gcol < N; gcol += 4) {{\n'
+            f'        {s["epi_cols"]}\n        const float4 acc = make_float4(P[(long long)grow * N + gcol], P[(long long)grow * N + gcol + 1], '
+            f'P[(long long)grow * N + gcol + 2], P[(long long)grow * N + gcol + 3]);\n        {s["epi_body"]}\n    }}\n}}\n')
+
+
+def _to_bf16(x):
+    """fp32 -> bf16 (round to nearest even) -> fp32."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    r = ((u + 0x7fff + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return (r.astype(np.uint32) << 16).view(np.float32)
+
+
+def _gemm_tc(s, bufs, lib, epi_name):
+    M, N, K = s["M"], s["N"], s["K"]
+
+    def operand(buf, twin, rows, cols, trans, ld):
+        srows, scols = (cols, rows) if trans else (rows, cols)          # the stored matrix
+        if twin >= 0:
+            mat = (bufs[twin][: srows * scols].astype(np.uint32) << 16).view(np.float32).reshape(srows, scols)
+        else:
+            mat = _to_bf16(np.lib.stride_tricks.as_strided(bufs[buf], shape=(srows, scols), strides=(4 * ld, 4)))
+        return mat.T if trans else mat
+
+    A = operand(s["a"], s["a16"], M, K, s["trans_a"], s["lda"])
+    B = operand(s["b"], s["b16"], K, N, s["trans_b"], s["ldb"])
+    prod = np.ascontiguousarray((A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32))
+    if not s["epilogue"]:
+        bufs[s["c"]][: M * N] = prod.reshape(-1)
+        return
+    fn = getattr(lib, epi_name)
+    args = [ctypes.c_void_p(bufs[s["c"]].ctypes.data if s["store_c"] else None), ctypes.c_void_p(prod.ctypes.data), ctypes.c_int(M), ctypes.c_int(N)]
+    args += [ctypes.c_void_p(bufs[a].ctypes.data) for a in s["epi_args"]]
+    fn.restype = None
+    fn(*args)
 
 
 def _gemm(s, bufs):
@@ -79,10 +125,10 @@ def _gemm(s, bufs):
         c[bi * M * N:(bi + 1) * M * N] = (A.astype(np.float32) @ B.astype(np.float32)).reshape(-1)
 
 
-def realize(roots):
+def realize(roots, options=""):
     """Plan + run; returns the logical value (view strides applied) of each root."""
     from ormi_b200 import runtime as RT
-    plan = RT.plan(list(roots), host_pointers=True)
+    plan = RT.plan(list(roots), host_pointers=True, options=options)
     res = run_plan(plan)
     order = plan["order"]
     outs = []

@@ -245,3 +245,91 @@ def test_ragged_shapes_softmax_layernorm_and_sums(shape):
     y.grad = G.leaf(W.normal(3, (R, C)))
     G.compute_gradients(y)
     compare([y, x.grad, g.grad, b.grad, W.softmax(x), G.sum_(x, [0], False), G.sum_(x, [1], True), G.sum_(x, [], False)], 5 * REDUCE_TOL)
+
+
+# ---------------------------------------------------------------------------- "bf16" matmul arithmetic: fused epilogues, bf16 twins
+
+BF16_TOL = 2e-2
+
+
+def _mlp(B, D, H, bias_std=0.1):
+    x, t = G.leaf(W.normal(0, (B, D))), G.leaf(W.normal(1, (B, D)))
+    w1, b1 = G.leaf(W.kaiming_uniform(2, D, (D, H)), True), G.leaf(W.normal(4, (H,), bias_std), True)
+    w2, b2 = G.leaf(W.kaiming_uniform(3, H, (H, D)), True), G.leaf(W.normal(5, (D,), bias_std), True)
+    loss = W.mlp_loss(x, w1, b1, w2, b2, t)
+    G.compute_gradients(loss)
+    return loss, (w1, b1, w2, b2)
+
+
+def test_bf16_mlp_step_fuses_epilogues_and_writes_twins():
+    """The training step in "bf16" arithmetic: GELU runs in the first GEMM's epilogue and leaves only a bf16 hidden
+    activation, every in-plan matmul operand is written as bf16 by its producer (no conversion pass over it), the hidden
+    gradient is never written as fp32, and the weight update of the first layer sits in the epilogue of its gradient GEMM."""
+    loss, params = _mlp(256, 128, 512)
+    ups = [W.sgd_update(p, 0.1) for p in params]
+    plan = RT.plan([loss] + ups, options="matmul=bf16")
+    assert not plan["error"]
+    gemms = [s for s in plan["steps"] if s["type"] == "gemm"]
+    assert len(gemms) == 5 and all(g["tc"] for g in gemms)
+    first = gemms[0]
+    assert "nodes=13" in first["epilogue"] and "outs=h" in first["epilogue"] and first["store_c"]      # h as bf16 only, x W1 kept for backward
+    assert "expf" in first["epi_body"] and "ormi_store_bf16x4" in first["epi_body"]
+    assert gemms[1]["a16"] >= 0                                     # h W2 reads the twin the epilogue wrote
+    assert gemms[2]["a16"] >= 0                                     # g_out W2^T reads g_out's twin
+    dw1 = [g for g in gemms if g["trans_a"] and not g["store_c"]]
+    assert len(dw1) >= 1 and all("outs=F" in g["epilogue"] for g in dw1)   # W1 - lr * (x^T du): the product itself is never stored
+    twins = [b for b in plan["buffers"] if b["kind"] == "twin16"]
+    assert len(twins) == 3                                          # h, g_out, du
+    assert not any("gelu" in s.get("what", "") for s in plan["steps"])
+    kernels = [s for s in plan["steps"] if s["type"] == "kernel"]
+    assert len(kernels) + len(gemms) <= 14
+    # without the option the same graph keeps the fp32 schedule
+    assert not any(s.get("tc") for s in RT.plan([loss] + ups)["steps"] if s["type"] == "gemm")
+
+
+@pytest.mark.parametrize("bdh", [(256, 128, 512), (128, 136, 264)])
+def test_bf16_mlp_step_on_the_emulator(bdh):
+    loss, params = _mlp(*bdh)
+    roots = [loss] + [p.grad for p in params] + [W.sgd_update(p, 0.1) for p in params]
+    ref, _ = O.port_run(roots)
+    outs, plan = E.realize(roots, options="matmul=bf16")
+    assert sum(1 for s in plan["steps"] if s["type"] == "gemm" and s["tc"]) == 5
+    for a, b in zip(outs, ref):
+        assert a.shape == b.shape
+        assert np.abs(a - b).max() <= BF16_TOL * max(1e-30, np.abs(b).max())
+
+
+def test_bf16_matmul_chain_and_epilogue_operand_kinds():
+    """A product that feeds the next matmul directly (bf16 twin written by the GEMM itself), and an epilogue with every
+    operand kind: a bias row, a per-row column, a full matrix, a scalar."""
+    M, K, N, P = 128, 128, 136, 128
+    a, b, c = G.leaf(W.normal(0, (M, K), 0.1)), G.leaf(W.normal(1, (K, N), 0.1)), G.leaf(W.normal(2, (N, P), 0.1))
+    bias, col, full = G.leaf(W.normal(3, (P,))), G.leaf(W.normal(4, (M, 1))), G.leaf(W.normal(5, (M, P)))
+    y = G.matmul(G.matmul(a, b), c)
+    root = G.mul(G.add(G.add(y, bias), G.mul(col, full)), G.const(0.5))
+    ref, _ = O.port_run([root])
+    outs, plan = E.realize([root], options="matmul=bf16")
+    gemms = [s for s in plan["steps"] if s["type"] == "gemm"]
+    assert [g["tc"] for g in gemms] == [True, True]
+    assert "product=Fh" in gemms[0]["epilogue"] or "product=h" in gemms[0]["epilogue"]
+    assert gemms[1]["a16"] >= 0 and not gemms[1]["store_c"] and len(plan["steps"]) == 2
+    assert np.abs(outs[0] - ref[0]).max() <= BF16_TOL * np.abs(ref[0]).max()
+
+
+def test_unaligned_inputs_get_scalar_kernels():
+    """A caller's pointer that is not on a 16-byte boundary: the whole plan is generated without 128-bit accesses, bulk
+    copies or the tensor-core kernel (the bit is part of the plan key)."""
+    loss, params = _mlp(256, 128, 512)
+    plan = RT.plan([loss, params[0].grad], options="matmul=bf16,aligned=0")
+    assert not plan["error"]
+    for s in plan["steps"]:
+        if s["type"] == "kernel":
+            assert "float4" not in s["source"].split("#endif")[-1] and s["dyn_smem"] == 0
+        else:
+            assert not s["tc"]
+    x = G.leaf(W.normal(0, (64, 256)), True)
+    y = W.softmax(x)
+    outs, plan = E.realize([y], options="aligned=0")
+    assert "V=1" in plan["steps"][0]["what"]
+    ref, _ = O.port_run([y])
+    assert np.abs(outs[0] - ref[0]).max() <= REDUCE_TOL * np.abs(ref[0]).max()
