@@ -84,7 +84,13 @@ const char* ormi_b200_last_error(void);
 
 /* Exact-size caching pool: a freed block is handed back for the next request of the same byte size
  * (contract pinned by ormi-core/csrc/tests/core/test_allocator.cpp:12-47).
- * Replaces CUDAAllocator::allocate / free (allocator.cu:36-55). */
+ * Replaces CUDAAllocator::allocate / free (allocator.cu:36-55).
+ * The pool is ordered by the context's COMPUTE stream: a freed block may be handed out again at once, which is safe for
+ * work queued on that stream only.  A buffer whose last use is on another stream — an all-reduce queued with
+ * overlap = 1, an asynchronous copy — must not be freed before the compute stream has waited for that use
+ * (ormi_b200_comm_join / ormi_b200_comm_wait / ormi_b200_copy_wait).
+ * Every pointer handed out is 256-byte aligned.  Buffers the caller brings from elsewhere may be passed to every entry
+ * point; when one does not start on a 16-byte boundary the kernels of that call are generated with scalar accesses. */
 int ormi_b200_alloc(ormi_b200_ctx* ctx, size_t bytes, void** out_ptr);
 int ormi_b200_free(ormi_b200_ctx* ctx, void* ptr, size_t bytes);
 /* Returns every cached block to the driver (the reference never does; additive). */
@@ -98,6 +104,20 @@ int ormi_b200_memcpy_h2d(ormi_b200_ctx* ctx, void* dst, const void* src, size_t 
 int ormi_b200_memcpy_d2h(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes);
 int ormi_b200_fill_u32(ormi_b200_ctx* ctx, void* dst, uint32_t pattern, size_t count);
 int ormi_b200_fill_u8(ormi_b200_ctx* ctx, void* dst, uint8_t pattern, size_t count);
+/* Copies that do not stop the caller (no counterpart in the reference, whose copies are synchronous cuMemcpy calls,
+ * allocator.cu:89-95): for loops that move the next batch in and the last results out while kernels run.  Each
+ * direction has a stream of its own beside the compute stream; host memory should be pinned (pageable memory makes the
+ * copy synchronous).  One cudaMemcpyAsync per call.
+ *   h2d_async  after_compute != 0: the upload first waits for everything queued on the compute stream so far (the
+ *              kernels that still read the old contents of `dst`); 0: it starts as soon as the upload stream is free.
+ *   d2h_async  always starts after everything queued on the compute stream so far (the kernels that write `src`).
+ *   copy_wait  direction 0: the COMPUTE STREAM waits for every upload queued so far (call it before launching what reads
+ *              them; the host does not block); direction 1: the HOST waits for every download queued so far, and a
+ *              device-side error is reported as by ormi_b200_sync.
+ * A buffer with an upload or download in flight must not be freed before the matching copy_wait. */
+int ormi_b200_memcpy_h2d_async(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes, int after_compute);
+int ormi_b200_memcpy_d2h_async(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes);
+int ormi_b200_copy_wait(ormi_b200_ctx* ctx, int direction);
 /* Waits for everything queued on the context's stream. */
 int ormi_b200_sync(ormi_b200_ctx* ctx);
 /* The context's compute stream as a cudaStream_t, for callers that time with CUDA events. */
@@ -208,9 +228,6 @@ int ormi_b200_colsum_static(const float* in, int64_t rows, int64_t cols, float* 
 
 /* ------------------------------------------------------------------ options, counters -- */
 
-/* Matmul arithmetic used by ormi_b200_realize / ormi_b200_matmul (additive knob; the reference has none):
- * "fp32" (SIMT FFMA, default), "bf16" (tcgen05, fp32 accumulate), "tf32", "3xtf32". Key "matmul".
- * Key "fusion": "on" (default) / "off" (one kernel per node, like the reference scheduler). */
 /* Self-test of the device-side bounded waits (no counterpart in the reference): queues a one-warp kernel that waits on a
  * barrier nobody arrives on, with a limit of `limit_ms` (1..1000).  The wait gives up, the kernel returns, and the next
  * ormi_b200_sync / ormi_b200_memcpy_d2h fails once with "a bounded device-side wait ran out (code 9 ...)"; the
@@ -218,6 +235,16 @@ int ormi_b200_colsum_static(const float* in, int64_t rows, int64_t cols, float* 
  * without faulting or hanging a GPU. */
 int ormi_b200_selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms);
 
+/* Options (additive; the reference has none).
+ *   "matmul":  arithmetic of ormi_b200_realize / ormi_b200_matmul: "fp32" (SIMT FFMA, default), "bf16" (tcgen05, fp32
+ *              accumulate; pointwise work behind a matmul runs in the GEMM's epilogue and matmul operands are kept as
+ *              bf16 copies beside their fp32 buffers — those buffers must then only be written through this ABI),
+ *              "tf32", "3xtf32".
+ *   "fusion":  "on" (default) / "off" (one kernel per node, like the reference scheduler).
+ *   "tc_pair": "on" (default: one tcgen05.mma per pair of SMs, 256 x 256 tiles) / "off" (one per SM, 128 x 256).
+ *   "tune.rows_vpt", "tune.rows_minb", "tune.rows_grid", "tune.rows_stage", "tune.rows_nstage", "tune.rows_dynamic",
+ *   "tune.flat_unroll", "tune.rows_hoist": integer overrides of the code generator's measured defaults, for
+ *              experiments ("0" = default; for the on/off ones 1 = off, 2 = on). */
 int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value);
 
 /* Counters since init: "kernels_compiled", "kernel_cache_hits", "plan_cache_hits", "launches",

@@ -70,6 +70,7 @@ int ormi_b200_shutdown(ormi_b200_ctx* ctx) {
         for (auto& kv : ctx->free_blocks) for (void* p : kv.second) cudaFree(p);
         for (int i = 0; i < 2; ++i) if (ctx->stage[i]) cudaFree(ctx->stage[i]);
         if (ctx->gemm_err) cudaFree(ctx->gemm_err);
+        if (ctx->up_stream) { cudaStreamSynchronize(ctx->up_stream); cudaStreamSynchronize(ctx->down_stream); cudaStreamDestroy(ctx->up_stream); cudaStreamDestroy(ctx->down_stream); cudaEventDestroy(ctx->copy_event); }
         cudaStreamDestroy(ctx->stream);
         delete ctx;
     });
@@ -116,6 +117,53 @@ int ormi_b200_memcpy_d2h(ormi_b200_ctx* ctx, void* dst, const void* src, size_t 
         ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
         ORMI_CUDA(cudaStreamSynchronize(ctx->stream));
         check_gemm_error(ctx);
+    });
+}
+
+static void copy_streams(ormi_b200_ctx* ctx) {
+    if (ctx->up_stream) return;
+    ORMI_CUDA(cudaStreamCreateWithFlags(&ctx->up_stream, cudaStreamNonBlocking));
+    ORMI_CUDA(cudaStreamCreateWithFlags(&ctx->down_stream, cudaStreamNonBlocking));
+    ORMI_CUDA(cudaEventCreateWithFlags(&ctx->copy_event, cudaEventDisableTiming));
+}
+
+int ormi_b200_memcpy_h2d_async(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes, int after_compute) {
+    return guarded([&] {
+        bind(ctx, "ormi_b200_memcpy_h2d_async");
+        need(dst && src, "ormi_b200_memcpy_h2d_async: NULL argument");
+        copy_streams(ctx);
+        shadow_drop(ctx, dst, bytes);
+        if (after_compute) {
+            ORMI_CUDA(cudaEventRecord(ctx->copy_event, ctx->stream));
+            ORMI_CUDA(cudaStreamWaitEvent(ctx->up_stream, ctx->copy_event, 0));
+        }
+        ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->up_stream));
+    });
+}
+
+int ormi_b200_memcpy_d2h_async(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    return guarded([&] {
+        bind(ctx, "ormi_b200_memcpy_d2h_async");
+        need(dst && src, "ormi_b200_memcpy_d2h_async: NULL argument");
+        copy_streams(ctx);
+        ORMI_CUDA(cudaEventRecord(ctx->copy_event, ctx->stream));
+        ORMI_CUDA(cudaStreamWaitEvent(ctx->down_stream, ctx->copy_event, 0));
+        ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->down_stream));
+    });
+}
+
+int ormi_b200_copy_wait(ormi_b200_ctx* ctx, int direction) {
+    return guarded([&] {
+        bind(ctx, "ormi_b200_copy_wait");
+        need(direction == 0 || direction == 1, "ormi_b200_copy_wait: direction must be 0 (uploads) or 1 (downloads)");
+        copy_streams(ctx);
+        if (direction == 0) {
+            ORMI_CUDA(cudaEventRecord(ctx->copy_event, ctx->up_stream));
+            ORMI_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->copy_event, 0));
+        } else {
+            ORMI_CUDA(cudaStreamSynchronize(ctx->down_stream));
+            check_gemm_error(ctx);
+        }
     });
 }
 

@@ -18,7 +18,9 @@
 //   * keeps the contents of the last call.  Nothing in it has to start at zero: stage 2 only reads the partial
 //     rows that stage 1 of the same call has just written.
 // The first call on a device looks the array's device address up (cudaGetSymbolAddress) with that device
-// current; make that first call before any stream capture starts.
+// current; make that first call before any stream capture starts.  The address is remembered per device ordinal for the
+// life of the process: after a cudaDeviceReset in the same process it would be stale, so do not reset a device that
+// this entry point has been used on.
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -95,9 +97,12 @@ extern "C" int ormi_b200_colsum_static(const float* in, int64_t rows, int64_t co
     if (parts > rows) parts = rows;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     dim3 grid1((unsigned)((cols + 255) / 256), (unsigned)parts);
+    cudaGetLastError();          // an error some earlier call left behind is not this call's
     colsum_partials<<<grid1, 256, 0, s>>>(in, rows, cols, (int)parts, scratch);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(std::string("CUDA Error: colsum_partials: ") + cudaGetErrorString(e));   // the second launch is not queued
     colsum_finalize<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(scratch, cols, (int)parts, out);
     e = cudaGetLastError();
-    if (e != cudaSuccess) return fail(std::string("CUDA Error: ") + cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail(std::string("CUDA Error: colsum_finalize: ") + cudaGetErrorString(e));
     return 0;
 }

@@ -83,6 +83,9 @@ struct ormi_b200_ctx {
     int device = 0;
     int num_sms = 148;
     cudaStream_t stream = nullptr;
+    // asynchronous host copies (abi.cu): one stream per direction, created on first use
+    cudaStream_t up_stream = nullptr, down_stream = nullptr;
+    cudaEvent_t copy_event = nullptr;
     ormi_b200::DriverApi drv;
 
     std::mutex pool_mutex;

@@ -42,6 +42,18 @@ class Device:
     def d2h(self, array: np.ndarray, ptr: int):
         check(lib.ormi_b200_memcpy_d2h(self.handle, array.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(ptr), array.nbytes))
 
+    def h2d_async(self, ptr: int, array: np.ndarray, after_compute: bool = True):
+        """Upload from pinned host memory on the upload stream; pair with ``copy_wait(0)`` before the kernels that read it."""
+        check(lib.ormi_b200_memcpy_h2d_async(self.handle, ctypes.c_void_p(ptr), array.ctypes.data_as(ctypes.c_void_p), array.nbytes,
+                                             1 if after_compute else 0))
+
+    def d2h_async(self, array: np.ndarray, ptr: int):
+        """Download into pinned host memory on the download stream, behind the kernels queued so far; ``copy_wait(1)`` waits."""
+        check(lib.ormi_b200_memcpy_d2h_async(self.handle, array.ctypes.data_as(ctypes.c_void_p), ctypes.c_void_p(ptr), array.nbytes))
+
+    def copy_wait(self, direction: int):
+        check(lib.ormi_b200_copy_wait(self.handle, direction))
+
     def sync(self):
         check(lib.ormi_b200_sync(self.handle))
 
