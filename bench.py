@@ -38,6 +38,8 @@ BYTES_STEP = BYTES_SOFTMAX + BYTES_LAYERNORM
 # DRAM traffic of the dominant kernel from its ncu capture (profiles/rows_layernorm_fwd_bwd_8192x4096.md): 269.5 MB read +
 # 225.4 MB written per launch over 8192 rows; the traffic is proportional to the rows, the bench launch covers 16384.
 LN_TRAFFIC_BYTES = 2 * (269_485_568 + 225_356_800)
+LN_TRAFFIC_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 8192 rows (494.8 MB), times 2 for 16384 rows"
+LN_KERNEL = "fused layernorm forward+backward (rows template) + 2 finalize launches"
 
 
 _REAL_STDOUT = None
@@ -176,102 +178,193 @@ def timed(dev, torch, fn, steps, dist=None, after=None):
     return ms
 
 
-def cpu_reference(rows, repeats=1):
-    """The reference CPU backend (unmodified, oracle/_ref) — or its C restatement when that library is absent — on
-    `rows` rows of the same workload.  Returns (GB/s of algorithmic bytes, seconds per run, kind, cores)."""
+CPU_ROWS_PER_WORKER = 256      # rows of the configs[1] workload one CPU worker realizes per step
+
+
+def _cpu_worker(arg):
+    """One worker: `rows` rows of the step (softmax + layernorm, forward + backward) on the reference CPU backend —
+    the unmodified reference from oracle/_ref, or its C restatement when that library is absent.  Returns the seconds
+    spent in autograd + realize."""
+    seed, rows = arg
     from ormi_b200 import graph as G, workloads as W
     from oracle import oracle as O
-    x = G.leaf(W.normal(0, (rows, C), math.sqrt(2.0)), True)
-    gy = G.leaf(W.normal(1, (rows, C)))
+    x = G.leaf(W.normal(100 * seed, (rows, C), math.sqrt(2.0)), True)
+    gy = G.leaf(W.normal(100 * seed + 1, (rows, C)))
     g = G.leaf(W.uniform(2, (C,), 0.5, 1.5), True)
     b = G.leaf(W.normal(3, (C,), 0.1), True)
-    best = None
-    kind = "reference" if O.ref_available() else "port"
-    for _ in range(repeats):
-        if kind == "reference":
-            y = W.softmax(x)
-            _, s1 = O.ref_run([(y, "value"), (x, "grad")], seeds=[(y, gy)], backward_root=y, caps=[rows * C] * 2)
-            y2 = W.layernorm(x, g, b)
-            _, s2 = O.ref_run([(y2, "value"), (x, "grad"), (g, "grad"), (b, "grad")], seeds=[(y2, gy)], backward_root=y2,
-                              caps=[rows * C] * 4)
-        else:
-            sm, ln, _ = build_graphs(G, W, G.leaf, rows)
-            _, s1 = O.port_run(sm)
-            _, s2 = O.port_run(ln)
-        secs = s1 + s2
-        best = secs if best is None else min(best, secs)
-    nbytes = BYTES_STEP * rows / R
-    return nbytes / best / 1e9, best, kind, 1
+    if O.ref_available():
+        y = W.softmax(x)
+        _, s1 = O.ref_run([(y, "value"), (x, "grad")], seeds=[(y, gy)], backward_root=y, caps=[rows * C] * 2)
+        y2 = W.layernorm(x, g, b)
+        _, s2 = O.ref_run([(y2, "value"), (x, "grad"), (g, "grad"), (b, "grad")], seeds=[(y2, gy)], backward_root=y2,
+                          caps=[rows * C] * 4)
+    else:
+        sm, ln, _ = build_graphs(G, W, G.leaf, rows, shard=seed)
+        _, s1 = O.port_run(sm)
+        _, s2 = O.port_run(ln)
+    return s1 + s2
+
+
+class CpuReference:
+    """The reference's CPU implementation of the path on the host cores of this machine.  Its realize path is single
+    threaded (one interpreter loop per node), and rows are independent, so every core gets a worker process with its
+    own rows: the aggregate is what the host can do with the reference code.  One step = workers x 256 rows."""
+
+    def __init__(self, max_workers=None):
+        from oracle import oracle as O
+        import multiprocessing as mp
+        self.kind = "reference" if O.ref_available() else "port"
+        cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        self.workers = max(1, min(cores, max_workers or 32))
+        self.pool = None
+        if self.workers > 1:
+            try:
+                self.pool = mp.get_context("fork").Pool(self.workers)
+                self.pool.map(_cpu_worker, [(i, 8) for i in range(self.workers)])      # load libraries, touch memory
+            except Exception:
+                self.pool, self.workers = None, 1
+        self.rows = self.workers * CPU_ROWS_PER_WORKER
+        self.sample = (f"{self.workers} worker process(es) x {CPU_ROWS_PER_WORKER} rows = {self.rows} of {R} rows per step "
+                       "(same graphs, seeded rows), autograd + realize on the reference CPU backend, wall clock over all workers")
+
+    def step(self):
+        """Runs one sample; returns (wall seconds, seconds of the slowest single worker)."""
+        args = [(i, CPU_ROWS_PER_WORKER) for i in range(self.workers)]
+        t0 = time.perf_counter()
+        secs = self.pool.map(_cpu_worker, args) if self.pool else [_cpu_worker(a) for a in args]
+        return time.perf_counter() - t0, max(secs)
+
+    def gbps(self, wall):
+        return BYTES_STEP * self.rows / R / wall / 1e9
+
+    def close(self):
+        if self.pool:
+            self.pool.close()
+            self.pool.join()
 
 
 def run_reference_arm(args, rank):
     if rank != 0:
         return
-    rows = 256
+    cpu = CpuReference()
     for _ in range(args.warmup):
-        cpu_reference(rows)
+        cpu.step()
     t0 = time.perf_counter()
+    one_core = []
     for _ in range(args.steps):
-        gbps, secs, kind, cores = cpu_reference(rows)
+        _, slowest = cpu.step()
+        one_core.append(slowest)
     ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    value = (BYTES_STEP * rows / R) / (ms * 1e-3) / 1e9
+    value = cpu.gbps(ms * 1e-3)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "rows_per_gpu": R, "cols": C},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
-                         "sample": f"{rows} of {R} rows per step (same graphs, same seeds), autograd + realize on the reference CPU backend"},
+        "config": {"workload": WORKLOAD, "rows_per_gpu": R, "cols": C, "cpu_sample": cpu.sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cpu.workers, "kind": cpu.kind, "sample": cpu.sample,
+                         "one_core_gbps": BYTES_STEP * CPU_ROWS_PER_WORKER / R / float(np.median(one_core)) / 1e9},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    cpu.close()
     emit(line)
 
 
 def matmul_sweep(dev, torch, G, W, steps=5):
-    """configs[2]: C = A @ B, fp32 (SIMT FFMA path, through the graph) and bf16 (tcgen05 path on operands already
-    converted to bf16 in HBM; the conversion pass is timed on its own)."""
+    """configs[2]: C = A @ B.  fp32 on the SIMT FFMA path through the graph; bf16 on the tcgen05 kernel with operands
+    already in bf16 in HBM (the conversion pass is timed on its own) and through the graph (operands found in the
+    context's bf16 cache, as in a loop that reuses them); the opt-in tf32 / 3xTF32 fp32 modes through the graph.
+    cuBLAS (torch.matmul, TF32 off for fp32) on the same box is the comparator, never part of the product path."""
     from ormi_b200._lib import lib, check
     out = {}
+    torch.backends.cuda.matmul.allow_tf32 = False
+    P = ctypes.c_void_p
     for (M, N, K) in [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (8192, 1024, 8192)]:
         a = dev.leaf(W.normal(0, (M, K), 1 / math.sqrt(K)))
         b = dev.leaf(W.normal(1, (K, N), 1 / math.sqrt(K)))
         flop = 2.0 * M * N * K
         rec = {}
-        dev.set_option("matmul", "fp32")
-        runner = StepRunner(dev, G, [[G.matmul(a, b)]])
-        n32 = steps if flop < 3e11 else 2
-        for _ in range(2):
-            runner.run()
-        rec["fp32_ffma_tflops"] = flop / (timed(dev, torch, lambda: runner.run(), n32) / n32 * 1e-3) / 1e12
-        Kp = (K + 63) // 64 * 64
-        a16, b16, c = dev.alloc(M * Kp * 2), dev.alloc(N * Kp * 2), dev.alloc(M * N * 4)
+        n_slow = steps if flop < 3e11 else 2
+
+        def through_graph(mode, n):
+            dev.set_option("matmul", mode)
+            runner = StepRunner(dev, G, [[G.matmul(a, b)]])
+            for _ in range(3):
+                runner.run()
+            return flop / (timed(dev, torch, lambda: runner.run(), n) / n * 1e-3) / 1e12
+
+        rec["fp32_ffma_tflops"] = through_graph("fp32", n_slow)
+        rec["tf32_tflops"] = through_graph("tf32", 2 * steps)
+        rec["3xtf32_tflops"] = through_graph("3xtf32", steps)
+        rec["bf16_graph_tflops"] = through_graph("bf16", 2 * steps)
+        a16, b16, c = dev.alloc(M * K * 2), dev.alloc(K * N * 2), dev.alloc(M * N * 4)
         h = dev.handle
 
         def cvt():
-            check(lib.ormi_b200_cvt_bf16_kmajor(h, ctypes.c_void_p(a.data.dev_ptr), K, 1, M, K, ctypes.c_void_p(a16)))
-            check(lib.ormi_b200_cvt_bf16_kmajor(h, ctypes.c_void_p(b.data.dev_ptr), 1, N, N, K, ctypes.c_void_p(b16)))
+            check(lib.ormi_b200_cvt_bf16(h, P(a.data.dev_ptr), K, M, K, P(a16)))
+            check(lib.ormi_b200_cvt_bf16(h, P(b.data.dev_ptr), N, K, N, P(b16)))
 
         def gemm():
-            check(lib.ormi_b200_gemm_bf16_kmajor(h, ctypes.c_void_p(a16), ctypes.c_void_p(b16), ctypes.c_void_p(c), M, N, Kp))
+            check(lib.ormi_b200_gemm_bf16(h, P(a16), 0, P(b16), 0, P(c), M, N, K))
 
         for _ in range(3):
             cvt(); gemm()
         rec["bf16_convert_ms"] = timed(dev, torch, cvt, steps) / steps
-        rec["bf16_tcgen05_tflops"] = flop / (timed(dev, torch, gemm, 2 * steps) / (2 * steps) * 1e-3) / 1e12
-        for ptr, nbytes in ((a16, M * Kp * 2), (b16, N * Kp * 2), (c, M * N * 4)):
+        rec["bf16_tcgen05_tflops"] = flop / (timed(dev, torch, gemm, 4 * steps) / (4 * steps) * 1e-3) / 1e12
+        for ptr, nbytes in ((a16, M * K * 2), (b16, K * N * 2), (c, M * N * 4)):
             dev.free(ptr, nbytes)
+        dev.sync()
+        # comparators: cuBLAS through torch, same shapes, same box, same run
+        for name, dt, n in (("cublas_bf16_tflops", torch.bfloat16, 4 * steps), ("cublas_sgemm_tflops", torch.float32, n_slow)):
+            ta = torch.randn(M, K, device="cuda", dtype=dt) / math.sqrt(K)
+            tb = torch.randn(K, N, device="cuda", dtype=dt) / math.sqrt(K)
+            for _ in range(3):
+                torch.matmul(ta, tb)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                torch.matmul(ta, tb)
+            e1.record()
+            e1.synchronize()
+            rec[name] = flop / (e0.elapsed_time(e1) / n * 1e-3) / 1e12
+            del ta, tb
         out[f"{M}x{N}x{K}"] = rec
-        del runner, a, b
+        del a, b
     dev.set_option("matmul", "fp32")
     return out
+
+
+def rowsum_config0(dev, torch, G, W, peak, steps=20):
+    """configs[0]: y = sum(relu(a*b + c) * exp(-|a|), axis=1) on [4096, 4096] fp32, one generated kernel.  Three input
+    sets are rotated, so that no launch finds its 201 MB of operands left in L2 by the one before."""
+    n = 4096
+    sets = []
+    for k in range(3):
+        a, b, c = (dev.leaf(W.normal(10 * k + i, (n, n))) for i in range(3))
+        sets.append(StepRunner(dev, G, [[W.fused_rowsum(a, b, c)]]))
+    nbytes = 3 * n * n * 4 + n * 4
+    state = {"i": 0}
+
+    def run():
+        sets[state["i"] % 3].run()
+        state["i"] += 1
+
+    for _ in range(6):
+        run()
+    ms = timed(dev, torch, run, 3 * steps) / (3 * steps)
+    gbps = nbytes / (ms * 1e-3) / 1e9
+    return {"gbps": gbps, "us_per_launch": ms * 1e3, "frac": gbps / peak, "algorithmic_bytes": nbytes,
+            "l2": "3 input sets of 201 MB rotated", "shape": "a, b, c [4096,4096] fp32 -> y [4096]"}
 
 
 def mlp_steps_per_s(dev, torch, W, batch, d_in, hidden, matmul, steps, rank=0, world=1, dist=None, global_batch=None):
     """configs[3] / configs[4]: full training step (forward, autograd backward, SGD update) of the 2-layer MLP."""
     from ormi_b200.train_step import MLPTrainer
     dev.set_option("matmul", matmul)
-    x = W.normal(1000 + rank, (batch, d_in))
-    t = W.normal(2000 + rank, (batch, d_in))
+    # ONE seeded global batch whatever the number of ranks; this rank takes its rows of it
+    rows = slice(rank * batch, (rank + 1) * batch)
+    x = np.ascontiguousarray(W.normal(1000, (batch * world, d_in))[rows])
+    t = np.ascontiguousarray(W.normal(2000, (batch * world, d_in))[rows])
     w1, w2 = W.kaiming_uniform(2, d_in, (d_in, hidden)), W.kaiming_uniform(3, hidden, (hidden, d_in))
     b1, b2 = np.zeros(hidden, np.float32), np.zeros(d_in, np.float32)
     tr = MLPTrainer(dev, x, t, w1, b1, w2, b2, lr=0.05, global_batch=global_batch or batch * world, world=world)
@@ -285,6 +378,39 @@ def mlp_steps_per_s(dev, torch, W, batch, d_in, hidden, matmul, steps, rank=0, w
     flop = 5 * 2.0 * batch * world * d_in * hidden
     return {"steps_per_s": 1e3 / ms, "ms_per_step": ms, "gemm_tflops_per_gpu": flop / world / (ms * 1e-3) / 1e12,
             "loss_first": first, "loss_last": last}
+
+
+def mlp_sharded_vs_single(dev, W, rank, world, dist, d_in=2048, hidden=8192, rows_per_rank=512, steps=3):
+    """Numerical parity of the sharded step: the N-rank trainer against a single-rank trainer fed the whole of the same
+    reduced batch (configs[4] widths, rows_per_rank x N rows), after `steps` SGD steps.  Returns, on rank 0, the largest
+    of |loss_N - loss_1| / |loss_1| and max|p_N - p_1| / max|p_1| over the four parameters."""
+    from ormi_b200.train_step import MLPTrainer
+    dev.set_option("matmul", "bf16")
+    B = rows_per_rank * world
+    x, t = W.normal(3000, (B, d_in)), W.normal(3001, (B, d_in))
+    w1, w2 = W.kaiming_uniform(2, d_in, (d_in, hidden)), W.kaiming_uniform(3, hidden, (hidden, d_in))
+    b1, b2 = W.normal(4, (hidden,), 0.1), W.normal(5, (d_in,), 0.1)
+    rows = slice(rank * rows_per_rank, (rank + 1) * rows_per_rank)
+    tr = MLPTrainer(dev, np.ascontiguousarray(x[rows]), np.ascontiguousarray(t[rows]), w1, b1, w2, b2, lr=0.05, global_batch=B, world=world)
+    for _ in range(steps):
+        tr.step()
+    loss = tr.loss()
+    params = [tr.parameter(n) for n in tr.names]
+    err = None
+    if rank == 0:
+        solo = MLPTrainer(dev, x, t, w1, b1, w2, b2, lr=0.05)
+        for _ in range(steps):
+            solo.step()
+        errs = [abs(loss - solo.loss()) / abs(solo.loss())]
+        for n, got in zip(solo.names, params):
+            want = solo.parameter(n)
+            errs.append(float(np.abs(got - want).max() / np.abs(want).max()))
+        err = max(errs)
+        del solo
+    del tr
+    dist.barrier()
+    dev.set_option("matmul", "fp32")
+    return err
 
 
 def run_only(args):
@@ -348,6 +474,7 @@ def main():
                     help="profiling aid: run just this graph --steps times on --rows rows and exit")
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--no-extras", action="store_true", help="skip the matmul sweep and the MLP training steps")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     args = ap.parse_args()
     # Libraries (NCCL's version banner, for one) print to stdout; the contract is ONE JSON line there.  Everything but
     # that line goes to stderr.
@@ -365,9 +492,20 @@ def main():
     if args.only:
         return run_only(args)
 
+    # The CPU baseline leg runs first, before this process touches CUDA (its worker processes are forked): the
+    # reference CPU backend on the same sample the reference arm steps over, best of a few repeats.
+    cpu_rec = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = CpuReference()
+        walls = [cpu.step()[0] for _ in range(6)]
+        cpu_rec = {"value": cpu.gbps(min(walls)), "unit": UNIT, "cores": cpu.workers, "kind": cpu.kind,
+                   "sample": cpu.sample + f"; best of {len(walls)} repeats ({sum(walls):.1f} s of wall clock in all)"}
+        cpu.close()
+
     import torch
     from ormi_b200 import graph as G, workloads as W
     from ormi_b200.runtime import Device
+    from ormi_b200._lib import lib, check
 
     torch.cuda.set_device(local_rank)
     dist = None
@@ -383,7 +521,6 @@ def main():
     runner = StepRunner(dev, G, [sm_roots, ln_roots])
 
     if dist is not None:
-        from ormi_b200._lib import lib, check
         from ormi_b200.train_step import init_comm
 
         def bcast(payload):
@@ -434,7 +571,7 @@ def main():
     launches0 = dev.counter("launches")
     ms_total = timed(dev, torch, step, args.steps, dist, after=settle)
     launches = dev.counter("launches") - launches0
-    # dominant kernel alone (the fused layernorm forward+backward kernel and its two finalize launches)
+    # dominant kernel alone (the fused layernorm forward+backward kernel)
     ms_ln = timed(dev, torch, lambda: runner.run(which=1), args.steps, dist)
     ms_sm = timed(dev, torch, lambda: runner.run(which=0), args.steps, dist)
     for _ in range(300):
@@ -443,27 +580,76 @@ def main():
     dev.sync()
     clocks = sampler.stop() if rank == 0 else None
 
-    # end to end: host buffers in, host buffers out, through the public Device API
-    pinned = {k: torch.from_numpy(np.ascontiguousarray(v.data.host if v.data.host is not None else dev.download(v.data))).pin_memory()
-              for k, v in inputs.items()}
-    out_host = [torch.empty(R * C, dtype=torch.float32).pin_memory() for _ in range(4)] + [torch.empty(C, dtype=torch.float32).pin_memory() for _ in range(2)]
-    h2d = sum(t.numel() * 4 for t in pinned.values())
-    d2h = sum(t.numel() * 4 for t in out_host)
+    # ------------------------------------------------------------------------------------------------ end to end
+    # Host buffers in, host buffers out, through the public Device API, pipelined: the step is row independent, so it
+    # runs in chunks of E2E_CHUNK rows — while the kernels of chunk k run, chunk k+1 is uploaded on the upload stream
+    # and the results of chunk k-1 go back on the download stream.  dg, db come back as one partial per chunk and are
+    # added on the host (and, with N > 1, summed over the ranks on the device first).
+    E2E_CHUNK = 1024
+    n_chunks = R // E2E_CHUNK
+    host_in = {k: torch.from_numpy(np.ascontiguousarray(v.data.host if v.data.host is not None else dev.download(v.data))).pin_memory()
+               for k, v in inputs.items()}
+    host_out = [torch.empty(R * C, dtype=torch.float32).pin_memory() for _ in range(4)]
+    host_part = torch.empty(n_chunks * 2 * C, dtype=torch.float32).pin_memory()
+    h2d = sum(t.numel() * 4 for t in host_in.values())
+    d2h = sum(t.numel() * 4 for t in host_out) + host_part.numel() * 4
+    # two sets of chunk-sized device inputs (one being computed on, one being uploaded into) and their graphs
+    chunk_sets = []
+    for _ in range(2):
+        csm, cln, cin = build_graphs(G, W, lambda a, rg=False: dev.leaf(a, rg), rows=E2E_CHUNK, shard=rank)
+        chunk_sets.append((StepRunner(dev, G, [csm, cln]), cin))
+    np_in = {k: t.numpy() for k, t in host_in.items()}
+    np_out = [t.numpy() for t in host_out]
+    np_part = host_part.numpy()
+
+    def upload(k):
+        _, cin = chunk_sets[k % 2]
+        rows = slice(k * E2E_CHUNK * C, (k + 1) * E2E_CHUNK * C)
+        dev.h2d_async(cin["x"].data.dev_ptr, np_in["x"].reshape(-1)[rows])
+        dev.h2d_async(cin["gy"].data.dev_ptr, np_in["gy"].reshape(-1)[rows])
+        if k < 2:      # the two parameter vectors, once per buffer set
+            dev.h2d_async(cin["g"].data.dev_ptr, np_in["g"].reshape(-1))
+            dev.h2d_async(cin["b"].data.dev_ptr, np_in["b"].reshape(-1))
 
     def e2e_step():
-        for k, node in inputs.items():
-            dev.h2d(node.data.dev_ptr, pinned[k].numpy())
-        outs = runner.run(keep=True)
-        if dist is not None:      # the cross-shard sums of dg, db, before they are read back
-            bufs = (ctypes.c_void_p * 2)(outs[-2][0], outs[-1][0])
-            counts = (ctypes.c_size_t * 2)(C, C)
-            check(lib.ormi_b200_allreduce_sum_f32(dev.handle, bufs, counts, 2, 0))
-        for (ptr, nbytes), host in zip(outs, out_host):
-            dev.d2h(host.numpy(), ptr)
-            dev.free(ptr, nbytes)
+        held = []
+        upload(0)
+        for k in range(n_chunks):
+            if k + 1 < n_chunks:
+                upload(k + 1)                    # waits (on the device) for the kernels that still read that buffer set
+            dev.copy_wait(0)                     # the compute stream waits for the uploads queued so far
+            outs = chunk_sets[k % 2][0].run(keep=True)
+            if dist is not None:
+                bufs = (ctypes.c_void_p * 2)(outs[-2][0], outs[-1][0])
+                counts = (ctypes.c_size_t * 2)(C, C)
+                check(lib.ormi_b200_allreduce_sum_f32(dev.handle, bufs, counts, 2, 0))
+            rows = slice(k * E2E_CHUNK * C, (k + 1) * E2E_CHUNK * C)
+            for (ptr, nbytes), host in zip(outs[:4], np_out):
+                dev.d2h_async(host[rows], ptr)
+            dev.d2h_async(np_part[(2 * k) * C:(2 * k + 1) * C], outs[4][0])
+            dev.d2h_async(np_part[(2 * k + 1) * C:(2 * k + 2) * C], outs[5][0])
+            held.append(outs)
+        dev.copy_wait(1)                         # the host waits for the downloads
+        for outs in held:
+            for ptr, nbytes in outs:
+                dev.free(ptr, nbytes)
+        part = np_part.reshape(n_chunks, 2, C)
+        return part[:, 0].sum(axis=0), part[:, 1].sum(axis=0)
+
+    def copy_rate(fn, nbytes):
+        dev.sync()
+        t0 = time.perf_counter()
+        fn()
+        return nbytes / (time.perf_counter() - t0) / 1e9
+
+    big = dev.alloc(R * C * 4)
+    h2d_gbps = copy_rate(lambda: (dev.h2d_async(big, np_in["x"].reshape(-1), False), dev.copy_wait(0), dev.sync()), R * C * 4)
+    d2h_gbps = copy_rate(lambda: (dev.d2h_async(np_out[0], big), dev.copy_wait(1)), R * C * 4)
+    dev.free(big, R * C * 4)
 
     e2e_steps = max(2, min(args.steps, 5))
     e2e_step()
+    dev.sync()
     if dist is not None:
         dist.barrier()
     t0 = time.perf_counter()
@@ -476,54 +662,68 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
 
-    # the other two legs of the metric: matmul TFLOP/s (configs[2]) and MLP training steps/s (configs[3], configs[4])
+    # the other legs of the metric: configs[0], matmul TFLOP/s (configs[2]) and MLP training steps/s (configs[3], [4])
     extras = {}
+    peak, peak_src = peaks()
     if not args.no_extras:
-        del runner, pinned, out_host
+        del runner, host_in, host_out, host_part, np_in, np_out, np_part, chunk_sets
         for node in inputs.values():
             node.data = None
         inputs.clear()
         sm_roots.clear(); ln_roots.clear()
         import gc
         gc.collect()
-        from ormi_b200._lib import lib as _lib, check as _check
-        _check(_lib.ormi_b200_trim(dev.handle))
+        check(lib.ormi_b200_trim(dev.handle))
         if world == 1:
+            extras["rowsum_config0"] = rowsum_config0(dev, torch, G, W, peak)
+            check(lib.ormi_b200_trim(dev.handle))
             extras["matmul"] = matmul_sweep(dev, torch, G, W)
+            gc.collect()
+            check(lib.ormi_b200_trim(dev.handle))
             extras["mlp_fp32_config3"] = dict(mlp_steps_per_s(dev, torch, W, 8192, 1024, 4096, "fp32", 5),
                                               shape="B=8192, 1024->4096->1024, fp32 FFMA matmuls")
+            gc.collect()
+            check(lib.ormi_b200_trim(dev.handle))
         gb = 65536
         extras["mlp_bf16_config4"] = dict(mlp_steps_per_s(dev, torch, W, gb // world, 2048, 8192, "bf16", 10, rank, world, dist, gb),
-                                          shape=f"global batch {gb} split over {world} GPU(s), 2048->8192->2048, bf16 tcgen05 matmuls, "
-                                                "fp32 master weights, gradient all-reduce overlapped with backward",
+                                          shape=f"global batch {gb} (one seeded batch, rows split over {world} GPU(s)), 2048->8192->2048, "
+                                                "bf16 tcgen05 matmuls with fused epilogues, fp32 master weights, gradient all-reduce "
+                                                "overlapped with backward",
                                           scaling="strong")
+        if dist is not None:
+            gc.collect()
+            check(lib.ormi_b200_trim(dev.handle))
+            err = mlp_sharded_vs_single(dev, W, rank, world, dist)
+            extras["mlp_bf16_config4"]["sharded_vs_single_rel_err"] = err
+            extras["mlp_bf16_config4"]["sharded_vs_single"] = (f"{world}-rank trainer against a single-rank trainer on the same {512 * world} rows, "
+                                                                "3 SGD steps: largest relative error of loss and parameters")
 
     if rank == 0:
-        peak, peak_src = peaks()
         ms_step = ms_total / args.steps
         value = world * BYTES_STEP / (ms_step * 1e-3) / 1e9
         ln_gbps = BYTES_LAYERNORM / (ms_ln / args.steps * 1e-3) / 1e9
         sm_gbps = BYTES_SOFTMAX / (ms_sm / args.steps * 1e-3) / 1e9
-        cpu_gbps, cpu_secs, kind, cores = cpu_reference(2048)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows_per_gpu": R, "cols": C,
                        "l2": "inputs larger than L2: every kernel reads 537 MB and writes 537 MB",
-                       "exchange": "all-reduce of dg, db (2 x 4096 fp32) per step" if world > 1 else "none"},
+                       "exchange": "all-reduce of dg, db (2 x 4096 fp32) per step" if world > 1 else "none",
+                       "cpu_sample": f"the reference arm and cpu_baseline step over workers x {CPU_ROWS_PER_WORKER} rows of the same workload"},
             "clocks": clocks,
             "e2e": {"value": world * BYTES_STEP / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms},
+                    "ms_per_step": e2e_ms, "pipeline": f"{n_chunks} chunks of {E2E_CHUNK} rows: upload k+1 | kernels k | download k-1",
+                    "pinned_h2d_gbps": h2d_gbps, "pinned_d2h_gbps": d2h_gbps},
             "gpu_launches": launches,
-            "roofline": {"bound": "hbm", "kernel": "fused layernorm forward+backward (rows template) + 2 finalize launches",
+            "roofline": {"bound": "hbm", "kernel": LN_KERNEL,
                          "achieved": ln_gbps, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": ln_gbps / peak,
                          "traffic": LN_TRAFFIC_BYTES, "traffic_unit": "bytes per launch",
-                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 8192 rows (494.8 MB), times 2 for 16384 rows",
+                         "traffic_source": LN_TRAFFIC_SOURCE,
                          "algorithmic_bytes": BYTES_LAYERNORM, "softmax_kernel_gbps": sm_gbps},
-            "cpu_baseline": {"value": cpu_gbps, "unit": UNIT, "cores": cores, "kind": kind,
-                             "sample": f"2048 of {R} rows, one run ({cpu_secs:.1f} s), autograd + realize on the reference CPU backend"},
         }
+        if cpu_rec is not None:
+            line["cpu_baseline"] = cpu_rec
         line["extra"] = extras
         emit(line)
     if dist is not None:
