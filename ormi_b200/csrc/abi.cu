@@ -89,7 +89,7 @@ int ormi_b200_trim(ormi_b200_ctx* ctx) {
         bind(ctx, "ormi_b200_trim");
         ORMI_CUDA(cudaStreamSynchronize(ctx->stream));
         std::lock_guard<std::mutex> lock(ctx->pool_mutex);
-        for (auto& kv : ctx->free_blocks) for (void* p : kv.second) cudaFree(p);
+        for (auto& kv : ctx->free_blocks) for (void* p : kv.second) { cudaFree(p); ctx->pool_held_bytes -= (long long)kv.first; }
         ctx->free_blocks.clear();
     });
 }
@@ -115,7 +115,7 @@ int ormi_b200_memcpy_d2h(ormi_b200_ctx* ctx, void* dst, const void* src, size_t 
     return guarded([&] {
         bind(ctx, "ormi_b200_memcpy_d2h");
         ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
-        ORMI_CUDA(cudaStreamSynchronize(ctx->stream));
+        comm_guarded_sync(ctx, ctx->stream);
         check_gemm_error(ctx);
     });
 }
@@ -161,7 +161,7 @@ int ormi_b200_copy_wait(ormi_b200_ctx* ctx, int direction) {
             ORMI_CUDA(cudaEventRecord(ctx->copy_event, ctx->up_stream));
             ORMI_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->copy_event, 0));
         } else {
-            ORMI_CUDA(cudaStreamSynchronize(ctx->down_stream));
+            comm_guarded_sync(ctx, ctx->down_stream);
             check_gemm_error(ctx);
         }
     });
@@ -187,7 +187,7 @@ int ormi_b200_fill_u8(ormi_b200_ctx* ctx, void* dst, uint8_t pattern, size_t cou
 }
 
 int ormi_b200_sync(ormi_b200_ctx* ctx) {
-    return guarded([&] { bind(ctx, "ormi_b200_sync"); ORMI_CUDA(cudaStreamSynchronize(ctx->stream)); check_gemm_error(ctx); });
+    return guarded([&] { bind(ctx, "ormi_b200_sync"); comm_guarded_sync(ctx, ctx->stream); check_gemm_error(ctx); });
 }
 
 void* ormi_b200_stream(ormi_b200_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
@@ -405,6 +405,15 @@ int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value)
             else if (v == "tf32") ctx->matmul_mode = MatmulMode::TF32;
             else if (v == "3xtf32") ctx->matmul_mode = MatmulMode::TF32X3;
             else throw Error("unknown matmul mode: " + v);
+        } else if (k == "comm_timeout_ms") {
+            // wall-clock deadline of collectives and of host-side waits behind them; past it the communicator is aborted
+            const int ms = std::atoi(v.c_str());
+            if (ms < 0) throw Error("comm_timeout_ms must be >= 0 (0 = the default of ten minutes)");
+            ctx->comm_timeout_ms = ms;
+        } else if (k == "pool_limit_bytes") {
+            // refuse allocations that would take the pool past this many bytes, as the driver does when memory is
+            // exhausted (0 = no limit): lets a host test walk the out-of-memory path without exhausting a GPU
+            ctx->pool_limit_bytes = std::atoll(v.c_str());
         } else if (k == "tc_pair") {
             // bf16 GEMM: "on" = one tcgen05.mma per pair of SMs (256 x 256 tiles, default), "off" = one per SM (128 x 256)
             if (v == "on") ctx->tc_cta_group = 2; else if (v == "off") ctx->tc_cta_group = 1; else throw Error("tc_pair must be on or off");

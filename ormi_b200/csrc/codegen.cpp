@@ -33,7 +33,15 @@ std::string device_prelude() {
 #ifndef ORMI_PRELUDE
 #define ORMI_PRELUDE
 // x ** y with the exponents the graphs actually use (0.5, 2, 3, 1, -1) evaluated the way a correctly
-// rounded powf would come out; anything else is powf.
+// rounded powf would come out; anything else is powf.  The rare paths are kept out of line: inlined at every use
+// they multiply the code size of an unrolled kernel body and push it out of the instruction cache.
+#ifndef ORMI_EMULATE
+#define ORMI_NOINLINE __noinline__
+#else
+#define ORMI_NOINLINE
+#endif
+__device__ ORMI_NOINLINE float ormi_pow_general(float x, float y) { return powf(x, y); }
+__device__ ORMI_NOINLINE float ormi_cube_wide(float x) { return (float)((double)x * (double)x * (double)x); }
 __device__ __forceinline__ float ormi_pow(float x, float y) {
     if (y == 0.5f) return sqrtf(x);
     if (y == 2.0f) return __fmul_rn(x, x);
@@ -44,12 +52,22 @@ __device__ __forceinline__ float ormi_pow(float x, float y) {
         const float hi = __fmul_rn(x2, x), e3 = __fmaf_rn(x2, x, -hi);
         const float ah = fabsf(hi);
         if (ah > 1e-25f && ah < 1e38f) return __fadd_rn(hi, __fmaf_rn(e2, x, e3));
-        return (float)((double)x * (double)x * (double)x);      // residuals under- or overflow out here
+        return ormi_cube_wide(x);                                // residuals under- or overflow out here
     }
     if (y == 1.0f) return x;
     if (y == -1.0f) return __fdiv_rn(1.0f, x);
-    return powf(x, y);
+    return ormi_pow_general(x, y);
 }
+// GEMM epilogue: sum over the four lanes that hold the same columns of a 32-row block (lanes l, l^8, l^16, l^24)
+#ifndef ORMI_EMULATE
+__device__ __forceinline__ float ormi_epi_rows(float v, bool is_max) {
+    float o = __shfl_xor_sync(0xffffffffu, v, 8);  v = is_max ? (o > v ? o : v) : __fadd_rn(v, o);
+    o = __shfl_xor_sync(0xffffffffu, v, 16);       v = is_max ? (o > v ? o : v) : __fadd_rn(v, o);
+    return v;
+}
+#else
+__device__ __forceinline__ float ormi_epi_rows(float v, bool) { return v; }   /* the emulator walks the 32 rows in one go */
+#endif
 __device__ __forceinline__ float ormi_warp_sum(float v, int width) {
     for (int o = width >> 1; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
@@ -699,7 +717,7 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
     if (spec.D.size() != 2) { g.error = "epilogue: domain is not [M, N]"; return g; }
     const int64_t N = spec.D[1];
     if (N % 4 != 0) { g.error = "epilogue: N is not a multiple of 4"; return g; }
-    std::ostringstream params, init, cols, body;
+    std::ostringstream params, init, cols, body, end;
     for (size_t l = 0; l < spec.loads.size(); ++l) {
         const KLoad& ld = spec.loads[l];
         if (ld.acc) continue;
@@ -724,8 +742,12 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
         }
     }
     // lanes whose columns lie beyond N (the last 32-column chunk may run past it) read column 0 instead and store nothing
+    const bool col_loads = !cols.str().empty();
+    for (size_t o = 0; o < spec.outputs.size(); ++o)
+        if (spec.outputs[o].kind == KOutput::COLSUM) cols << "float cs" << o << "[4] = {" << red_ident(spec.outputs[o].is_max) << ", " << red_ident(spec.outputs[o].is_max) << ", "
+                                                          << red_ident(spec.outputs[o].is_max) << ", " << red_ident(spec.outputs[o].is_max) << "}; ";
     std::string cols_text = cols.str();
-    if (!cols_text.empty()) cols_text = "const int gc = gcol < N ? gcol : 0; " + cols_text;
+    if (col_loads) cols_text = "const int gc = gcol < N ? gcol : 0; " + cols_text;
     auto ref = [&](const KRef& r) {
         if (r.t == KRef::LOAD) {
             const KLoad& ld = spec.loads[r.id];
@@ -750,13 +772,24 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
     if (store_c) body << "*reinterpret_cast<float4*>(C" << at << ") = acc; ";
     for (size_t o = 0; o < spec.outputs.size(); ++o) {
         const KOutput& ko = spec.outputs[o];
-        if (ko.kind != KOutput::FULL) { g.error = "epilogue: only full outputs"; return g; }
+        if (ko.kind != KOutput::FULL && ko.kind != KOutput::COLSUM) { g.error = "epilogue: only full and column-sum outputs"; return g; }
         auto val = [&](int j) {
             std::string r = ref(ko.value);
             size_t p = r.find("[j]");
             if (p != std::string::npos) r.replace(p, 3, "[" + std::to_string(j) + "]");
             return r;
         };
+        if (ko.kind == KOutput::COLSUM) {
+            // per chunk: this lane adds its rows of its four columns, the four lanes that share those columns are
+            // combined, and one of them writes the 32-row block's partial; a finalize kernel adds the blocks in order
+            params << ", float* __restrict__ eout" << o;
+            for (int j = 0; j < 4; ++j) body << "cs" << o << "[" << j << "] = " << red_comb(ko.is_max, "cs" + std::to_string(o) + "[" + std::to_string(j) + "]", val(j)) << "; ";
+            end << "{ ";
+            for (int j = 0; j < 4; ++j) end << "cs" << o << "[" << j << "] = ormi_epi_rows(cs" << o << "[" << j << "], " << (ko.is_max ? "true" : "false") << "); ";
+            end << "if (rsub == 0 && gcol < N) *reinterpret_cast<float4*>(eout" << o << " + (long long)(row0 >> 5) * " << N << " + gcol) = make_float4(cs" << o << "[0], cs" << o
+                << "[1], cs" << o << "[2], cs" << o << "[3]); } ";
+            continue;
+        }
         if (ko.store) {
             params << ", float* __restrict__ eout" << o;
             body << "*reinterpret_cast<float4*>(eout" << o << at << ") = make_float4(" << val(0) << ", " << val(1) << ", " << val(2) << ", " << val(3) << "); ";
@@ -775,6 +808,8 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
     g.init = init.str();
     g.cols = cols_text;
     g.body = body.str();
+    g.end = end.str();
+    g.unroll = spec.nodes.size() <= 4 ? 8 : (spec.nodes.size() <= 10 ? 2 : 1);
     // exact exp / division chains cost tens of instructions per element: give them more epilogue warps
     g.wpq = spec.nodes.size() <= 2 ? 1 : (spec.nodes.size() <= 6 ? 2 : 4);
     return g;

@@ -70,8 +70,9 @@ struct TcKernel { CompiledKernel* kernel = nullptr; int block = 0, smem = 0; };
 // Generated epilogue of the run-time compiled tensor-core GEMM: text spliced into the kernel template plus the
 // device pointers of its extra parameters, in parameter order.
 struct TcEpilogue {
-    std::string prelude, params, init, cols, body;
+    std::string prelude, params, init, cols, body, end;
     int wpq = 1;                       // epilogue warps per TMEM lane quarter (1, 2 or 4)
+    int unroll = 8;                    // unrolled row steps per chunk
     std::vector<void*> args;
 };
 
@@ -89,6 +90,7 @@ struct ormi_b200_ctx {
     ormi_b200::DriverApi drv;
 
     std::mutex pool_mutex;
+    long long pool_limit_bytes = 0, pool_held_bytes = 0;   // option "pool_limit_bytes": simulated memory exhaustion
     std::unordered_map<size_t, std::vector<void*>> free_blocks;
 
     std::unordered_map<std::string, ormi_b200::CompiledKernel> kernel_cache;   // source hash -> module
@@ -112,6 +114,7 @@ struct ormi_b200_ctx {
 
     std::map<std::string, int64_t> counters;
     void* nccl = nullptr;   // opaque: collective state (comm.cu)
+    int comm_timeout_ms = 0;   // wall-clock deadline of collectives and of host waits behind them; 0 = ten minutes
 };
 
 namespace ormi_b200 {
@@ -164,6 +167,7 @@ void comm_join(ormi_b200_ctx* ctx);
 void comm_mark(ormi_b200_ctx* ctx, int slot);
 void comm_wait(ormi_b200_ctx* ctx, int slot);
 void comm_destroy(ormi_b200_ctx* ctx);
+void comm_guarded_sync(ormi_b200_ctx* ctx, cudaStream_t stream);   // cudaStreamSynchronize under the collective deadline
 
 // `preassigned`: optional (node, pointer) pairs — write that node's value into a caller-owned buffer
 // instead of a fresh pool block (used by the raw-buffer sum / matmul entry points).

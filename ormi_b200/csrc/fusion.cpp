@@ -546,10 +546,13 @@ Plan Scheduler::run(const int* roots, int n_roots) {
             if (info[m].sq.size() != 2) continue;
             for (size_t fs = 0; fs < steps.size(); ++fs) {
                 StepNode& Fs = steps[fs];
-                if (Fs.type != StepNode::FUSED || Fs.dead || Fs.D != info[m].sq || Fs.k >= 0) continue;
+                if (Fs.type != StepNode::FUSED || Fs.dead || Fs.D != info[m].sq || !(Fs.k < 0 || Fs.k == 1)) continue;
                 bool reads_m = false, ok = true;
                 for (int o : Fs.outputs) {
-                    if (!(info[o].kind == K_PW || info[o].kind == K_IDSUM) || info[o].row_cls) ok = false;
+                    // full pointwise results, and column sums over the rows of the product (a bias gradient)
+                    const bool full = (info[o].kind == K_PW || info[o].kind == K_IDSUM) && !info[o].row_cls;
+                    const bool colsum = info[o].kind == K_COLSUM && info[o].k == 1 && info[o].D == Fs.D;
+                    if (!full && !colsum) ok = false;
                     for (const Dep& d : deps[o]) {
                         if (d.node == m) { reads_m = true; continue; }
                         const int ds = info[d.node].step;
@@ -559,11 +562,12 @@ Plan Scheduler::run(const int* roots, int n_roots) {
                 }
                 if (!ok || !reads_m) continue;
                 // the product must be read element for element (not transposed or broadcast) by every member
-                Walk w; w.D = Fs.D; w.k = -1;
+                Walk w; w.D = Fs.D; w.k = Fs.k;
                 for (int o : Fs.outputs) w.outputs.insert(o);
                 for (int o : Fs.outputs) walk_output(w, o, false, nullptr);
                 int acc_loads = 0;
                 for (const KLoad& l : w.loads) if (l.src_node == m) { ++acc_loads; if (l.st != std::vector<int64_t>{(int64_t)Fs.D[1], 1}) ok = false; }
+                for (int q : w.members) if (info[q].kind == K_ROWSUM || info[q].row_cls) ok = false;     // no per-row values in an epilogue
                 if (!ok || acc_loads != 1 || w.k_conflict) continue;
                 // absorb: the outputs of Fs become outputs of the GEMM step
                 Fs.dead = true;
@@ -737,8 +741,10 @@ Plan Scheduler::run(const int* roots, int n_roots) {
                 for (int y : consumers[m]) if (info[y].step != s) c_read = true;
                 g.store_c = c_read;
                 if (!c_read) drop_f32[m] = true;
+                std::vector<Step> finalizes;
                 if (!S.epi_outputs.empty() || twin_c || !c_read) {
                     Walk w; w.D = info[m].sq; w.k = -1;
+                    for (int o : S.epi_outputs) if (info[o].kind == K_COLSUM) w.k = 1;
                     for (int o : S.epi_outputs) w.outputs.insert(o);
                     KernelSpec ks;
                     for (int o : S.epi_outputs) walk_output(w, o, false, &ks.outputs);
@@ -755,24 +761,41 @@ Plan Scheduler::run(const int* roots, int n_roots) {
                         kn.operands = w.operands[q];
                         ks.nodes.push_back(kn);
                     }
-                    for (KOutput& o : ks.outputs) { o.twin = need_twin[o.node]; o.store = !drop_f32[o.node]; }
+                    for (KOutput& o : ks.outputs) if (o.kind == KOutput::FULL) { o.twin = need_twin[o.node]; o.store = !drop_f32[o.node]; }
                     GeneratedEpilogue ge = generate_gemm_epilogue(ks, g.store_c, twin_c);
                     if (!ge.error.empty()) { plan.error = ge.error; return plan; }
                     g.has_epi = true;
                     g.epi_prelude = ge.prelude; g.epi_params = ge.params; g.epi_init = ge.init; g.epi_cols = ge.cols; g.epi_body = ge.body;
-                    g.epi_wpq = ge.wpq;
+                    g.epi_end = ge.end;
+                    g.epi_wpq = ge.wpq; g.epi_unroll = ge.unroll;
                     for (const KLoad& l : ks.loads) if (!l.acc) g.epi_args.push_back(buffer_for(l.src_node));
                     for (const KOutput& o : ks.outputs) {
+                        if (o.kind == KOutput::COLSUM) {
+                            // one partial row per 32-row block of the product; blocks past the last row (the tile grid
+                            // is rounded up to 256 rows) are written too, as zeros, and not read
+                            const int64_t blocks = (g.M + 31) / 32, padded = ((g.M + 255) / 256) * 8;
+                            int tmp = temp_buffer(padded * g.N * 4);
+                            g.epi_args.push_back(tmp);
+                            GeneratedKernel fk = generate_finalize((int)blocks, g.N, "ormi_finalize_" + std::to_string(kernel_serial++), o.is_max);
+                            Step fs; fs.type = Step::Kernel; fs.k = fk.step;
+                            fs.k.args = {tmp, buffer_for(o.node)};
+                            finalizes.push_back(fs);
+                            continue;
+                        }
                         if (o.store) g.epi_args.push_back(buffer_for(o.node));
                         if (o.twin) g.epi_args.push_back(twin_for(o.node));
                     }
                     if (twin_c) g.epi_args.push_back(twin_for(m));
                     std::ostringstream what;
                     what << "epilogue[nodes=" << ks.nodes.size() << ",loads=" << ks.loads.size() - 1 << ",outs=";
-                    for (const KOutput& o : ks.outputs) what << (o.store ? "F" : "") << (o.twin ? "h" : "");
+                    for (const KOutput& o : ks.outputs) what << (o.kind == KOutput::COLSUM ? "C" : "") << (o.kind == KOutput::FULL && o.store ? "F" : "") << (o.twin ? "h" : "");
                     what << ",product=" << (g.store_c ? "F" : "") << (twin_c ? "h" : "") << ",wpq=" << ge.wpq << "]";
                     g.epi_what = what.str();
                 }
+                Step stp; stp.type = Step::Gemm; stp.g = g;
+                plan.steps.push_back(stp);
+                for (const Step& f : finalizes) plan.steps.push_back(f);
+                continue;
             }
             Step stp; stp.type = Step::Gemm; stp.g = g;
             plan.steps.push_back(stp);
@@ -922,7 +945,7 @@ std::string plan_to_json(const Plan& plan) {
               << ", \"store_c\": " << (g.store_c ? "true" : "false") << ", \"epilogue\": \"" << json_escape(g.epi_what) << "\", \"epi_args\": [";
             for (size_t a = 0; a < g.epi_args.size(); ++a) o << (a ? ", " : "") << g.epi_args[a];
             o << "], \"epi_body\": \"" << json_escape(g.epi_body) << "\", \"epi_cols\": \"" << json_escape(g.epi_cols) << "\", \"epi_init\": \""
-              << json_escape(g.epi_init) << "\", \"epi_params\": \"" << json_escape(g.epi_params) << "\", \"epi_prelude\": \"" << json_escape(g.epi_prelude) << "\"}";
+              << json_escape(g.epi_init) << "\", \"epi_end\": \"" << json_escape(g.epi_end) << "\", \"epi_params\": \"" << json_escape(g.epi_params) << "\", \"epi_prelude\": \"" << json_escape(g.epi_prelude) << "\"}";
         }
     }
     o << "], \"results\": [";

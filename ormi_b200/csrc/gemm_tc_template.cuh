@@ -22,6 +22,9 @@ R"GEMMTPL(
 //   G_EPI_INIT    statements run once by every epilogue thread (scalar operands)
 //   G_EPI_COLS    statements run once per 32-column chunk: `gcol` is the first of the 4 columns this lane owns
 //   G_EPI_BODY    statements run per (row, 4 columns): `acc` (float4), `grow`, `gcol`, `M`, `N` are in scope
+//   G_EPI_END     statements run once per chunk after its rows (column sums: combine lanes, write the block's partial;
+//                 `row0` is the first row of the warp's 32-row block, `rsub` = lane / 8)
+//   G_EPI_UNROLL  how many of a chunk's 8 row steps are unrolled (a heavy body must not outgrow the instruction cache)
 //
 // Roles (warps): 0 producer (one lane issues TMA), 1 MMA issuer (one lane, leader CTA only) and TMEM owner,
 // 2.. epilogue.  Two 256-column accumulators in tensor memory let the epilogue of tile i overlap the MMAs of tile i+1.
@@ -49,6 +52,7 @@ constexpr int UMMA_K = 16;
 constexpr int STAGES = G_STAGES;
 constexpr int SCHED = 4;
 constexpr int EPI_WPQ = G_EPI_WPQ;
+constexpr int EPI_UNROLL = G_EPI_UNROLL;
 constexpr int EPI_WARPS = 4 * EPI_WPQ;
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNC * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -414,7 +418,7 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
                 __syncwarp();
                 const int gcol = col0 + 4 * cq;
                 G_EPI_COLS
-                #pragma unroll
+                #pragma unroll EPI_UNROLL
                 for (int p = 0; p < 8; ++p) {
                     const int rl = 4 * p + rsub;
                     const int grow = row0 + rl;
@@ -425,6 +429,7 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
                         G_EPI_BODY
                     }
                 }
+                G_EPI_END
                 __syncwarp();                                 // the staging buffer is rewritten by the next chunk
             }
             tc_fence_before();

@@ -65,12 +65,14 @@ struct GeneratedKernel {
 GeneratedKernel generate_kernel(const KernelSpec& spec, const std::string& name, const ormi_b200_node* nodes);
 // Epilogue of the run-time compiled tensor-core GEMM: the pointwise work of `spec` (domain [M, N], every output FULL)
 // on the accumulator, as text for the kernel template.  The load flagged `acc` is the matmul itself; `store_c` /
-// `twin_c` say whether the raw product is written as fp32 / as bf16.  Kernel-argument order: every other load in
-// order, then per output the fp32 pointer (if store) and the bf16 pointer (if twin), then the product's bf16 pointer
-// (if twin_c).
+// `twin_c` say whether the raw product is written as fp32 / as bf16.  A COLSUM output leaves one partial row per
+// 32-row block of the product ([ceil(M / 32) rounded up to whole tiles][N] floats, added up by a finalize kernel).
+// Kernel-argument order: every other load in order, then per output the fp32 pointer (if store; for a COLSUM the
+// partial buffer) and the bf16 pointer (if twin), then the product's bf16 pointer (if twin_c).
 struct GeneratedEpilogue {
-    std::string prelude, params, init, cols, body;
+    std::string prelude, params, init, cols, body, end;
     int wpq = 1;
+    int unroll = 8;             // how many of the 8 row steps of a chunk are unrolled (heavy bodies: 1, for the instruction cache)
     std::string error;
 };
 GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, bool twin_c);

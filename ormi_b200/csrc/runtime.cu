@@ -59,19 +59,22 @@ void* pool_alloc(ormi_b200_ctx* ctx, size_t bytes) {
         }
     }
     void* p = nullptr;
-    cudaError_t e = cudaMalloc(&p, bytes);
+    auto over_limit = [&]() { return ctx->pool_limit_bytes > 0 && ctx->pool_held_bytes + (long long)bytes > ctx->pool_limit_bytes; };
+    cudaError_t e = over_limit() ? cudaErrorMemoryAllocation : cudaMalloc(&p, bytes);
     if (e == cudaErrorMemoryAllocation) {   // give cached blocks back and try once more
         cudaGetLastError();
         {
             std::lock_guard<std::mutex> lock(ctx->pool_mutex);
             cudaStreamSynchronize(ctx->stream);
-            for (auto& kv : ctx->free_blocks) for (void* q : kv.second) cudaFree(q);
+            for (auto& kv : ctx->free_blocks) for (void* q : kv.second) { cudaFree(q); ctx->pool_held_bytes -= (long long)kv.first; }
             ctx->free_blocks.clear();
+            ctx->counters["pool_trims"]++;
         }
-        e = cudaMalloc(&p, bytes);
+        e = over_limit() ? cudaErrorMemoryAllocation : cudaMalloc(&p, bytes);
     }
     if (e != cudaSuccess) throw Error(std::string("CUDA Error: ") + cudaGetErrorString(e) + " (allocating " + std::to_string(bytes) + " bytes)");
     ctx->counters["bytes_allocated"] += (int64_t)bytes;
+    ctx->pool_held_bytes += (long long)bytes;
     return p;
 }
 
@@ -319,7 +322,7 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
                     TcEpilogue epi;
                     if (st.g.has_epi) {
                         epi.prelude = st.g.epi_prelude; epi.params = st.g.epi_params; epi.init = st.g.epi_init;
-                        epi.cols = st.g.epi_cols; epi.body = st.g.epi_body; epi.wpq = st.g.epi_wpq;
+                        epi.cols = st.g.epi_cols; epi.body = st.g.epi_body; epi.end = st.g.epi_end; epi.wpq = st.g.epi_wpq; epi.unroll = st.g.epi_unroll;
                         for (int a : st.g.epi_args) epi.args.push_back(bufs[a]);
                     }
                     gemm_tc_from_fp32(ctx, g, st.g.a16 >= 0 ? bufs[st.g.a16] : nullptr, st.g.b16 >= 0 ? bufs[st.g.b16] : nullptr,

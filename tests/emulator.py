@@ -71,9 +71,12 @@ def run_plan(plan: dict) -> dict:
 def _epilogue_source(name, s):
     """The generated epilogue text of a tensor-core GEMM step as a plain loop over (row, 4 columns)."""
     return (s["epi_prelude"] + f'\nextern "C" void {name}(float* C, const float* P, int M, int N{s["epi_params"]}) {{\n'
-            f'    {s["epi_init"]}\n    for (int grow = 0; grow < M; ++grow) for (int gcol = 0; gcol < N; gcol += 4) {{\n'
-            f'        {s["epi_cols"]}\n        const float4 acc = make_float4(P[(long long)grow * N + gcol], P[(long long)grow * N + gcol + 1], '
-            f'P[(long long)grow * N + gcol + 2], P[(long long)grow * N + gcol + 3]);\n        {s["epi_body"]}\n    }}\n}}\n')
+            f'    {s["epi_init"]}\n    const int rsub = 0;\n'
+            f'    for (int row0 = 0; row0 < M; row0 += 32) for (int gcol = 0; gcol < N; gcol += 4) {{\n'
+            f'        {s["epi_cols"]}\n        for (int grow = row0; grow < row0 + 32 && grow < M; ++grow) {{\n'
+            f'            const float4 acc = make_float4(P[(long long)grow * N + gcol], P[(long long)grow * N + gcol + 1], '
+            f'P[(long long)grow * N + gcol + 2], P[(long long)grow * N + gcol + 3]);\n            {s["epi_body"]}\n        }}\n'
+            f'        {s["epi_end"]}\n    }}\n}}\n')
 
 
 def _to_bf16(x):

@@ -151,10 +151,19 @@ def test_config3_mlp_step_fp32_full_batch(device):
     roots = _mlp_step(8192, 1024, 4096)
     device.realize(roots)
     got = [device.numpy(r) for r in roots]
-    # the loss is a serial fp32 sum of 8.4 million positive terms on the oracle's side: its own error is about 1e-3
-    assert abs(float(got[0]) - float(want[0])) <= 2e-3 * abs(float(want[0]))
     for g, w in zip(got[1:], want[1:]):
         assert g.shape == w.shape and rel(g, w) <= 3 * REDUCE_TOL
+    # The loss is a sum of 8.4 million positive terms.  The oracle adds them one after the other in fp32: once the
+    # running sum has passed 2^24 every term of about 3 is rounded to a multiple of 2, and the total ends up about one
+    # per cent low.  The GPU adds them as a tree.  So the scalar is judged against an fp64 evaluation of the same
+    # forward pass, with the oracle's value required to lie within its own error of it.
+    xh, th, w1, b1, w2, b2 = (a.astype(np.float64) for a in _mlp_problem(8192, 1024, 4096))
+    u = xh @ w1 + b1
+    z = 0.79788456 * (u + 0.044715 * u ** 3)
+    h = 0.5 * u * (1.0 + (1.0 - 2.0 / (np.exp(2.0 * z) + 1.0)))
+    loss64 = float(np.mean((h @ w2 + b2 - th) ** 2))
+    assert abs(float(got[0]) - loss64) <= 3 * REDUCE_TOL * loss64
+    assert abs(float(want[0]) - loss64) <= 3e-2 * loss64
 
 
 def test_config4_mlp_step_bf16_widths_at_1024_rows():
