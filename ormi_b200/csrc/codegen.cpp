@@ -378,10 +378,15 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
             depth = std::max(depth, lv);
         }
     }
+    //   depth <= 1 with no column / global partials, re-measured with three rotated input sets (no operand left in
+    //            L2): 8 elements/thread, 4 blocks/SM, grid 4/SM, direct loads -> 5275; 2 blocks/SM staged -> 4880.
+    bool pure_rows = true;
+    for (auto& o : spec.outputs) if (o.kind == KOutput::COLSUM || o.kind == KOutput::GLOBALSUM) pure_rows = false;
+    const bool shallow = depth <= 1 && pure_rows;
     const int target = knob(TUNE_ROWS_VPT, (V == 4 && depth >= 2) ? 16 : 8);
     const bool hoist = toggle(TUNE_ROWS_HOIST, true);
-    int minb = knob(TUNE_ROWS_MINB, depth == 2 ? 3 : 2);
-    const int grid_mult = knob(TUNE_ROWS_GRID, depth == 2 ? 3 : 2);
+    int minb = knob(TUNE_ROWS_MINB, shallow ? 4 : (depth == 2 ? 3 : 2));
+    const int grid_mult = knob(TUNE_ROWS_GRID, shallow ? 4 : (depth == 2 ? 3 : 2));
     int T = std::min(1024, std::max(32, ceil_pow2((C + target - 1) / target)));
     int64_t VPT = (C + T - 1) / T;
     VPT = (VPT + V - 1) / V * V;
@@ -399,7 +404,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     std::vector<size_t> staged;
     int stages = 0;
     {
-        const bool want = toggle(TUNE_ROWS_STAGE, depth != 2);
+        const bool want = toggle(TUNE_ROWS_STAGE, depth != 2 && !shallow);
         bool can = want && V == 4 && G == 1 && !col_pred;
         for (size_t l = 0; can && l < spec.loads.size(); ++l) {
             bool varies = false;
@@ -717,7 +722,7 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
     if (spec.D.size() != 2) { g.error = "epilogue: domain is not [M, N]"; return g; }
     const int64_t N = spec.D[1];
     if (N % 4 != 0) { g.error = "epilogue: N is not a multiple of 4"; return g; }
-    std::ostringstream params, init, cols, body, end;
+    std::ostringstream params, init, cols, pre, body, end;
     for (size_t l = 0; l < spec.loads.size(); ++l) {
         const KLoad& ld = spec.loads[l];
         if (ld.acc) continue;
@@ -733,7 +738,15 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
         } else {
             body << "float " << L << "[4]; ";
             if (sn == 1 && sm % 4 == 0) {
-                body << "{ const float4 t = *reinterpret_cast<const float4*>(" << P << " + (long long)grow * " << sm << " + gcol); " << L << "[0] = t.x; " << L << "[1] = t.y; " << L << "[2] = t.z; " << L << "[3] = t.w; } ";
+                // A full matrix read beside the accumulator: the piece for the NEXT row step (4 rows further down) is
+                // requested before this step's arithmetic, so the load's latency hides behind it even when the row
+                // loop is not unrolled.  N<l> carries the piece from one step to the next.
+                const std::string Nx = "N" + std::to_string(l);
+                cols << "float4 " << Nx << " = make_float4(0.0f, 0.0f, 0.0f, 0.0f); if (row0 + rsub < M && gcol < N) " << Nx
+                     << " = *reinterpret_cast<const float4*>(" << P << " + (long long)(row0 + rsub) * " << sm << " + gcol); ";
+                pre << "const float4 T" << l << " = " << Nx << "; if (p < 7 && grow + 4 < M && gcol < N) " << Nx
+                    << " = *reinterpret_cast<const float4*>(" << P << " + (long long)(grow + 4) * " << sm << " + gcol); ";
+                body << L << "[0] = T" << l << ".x; " << L << "[1] = T" << l << ".y; " << L << "[2] = T" << l << ".z; " << L << "[3] = T" << l << ".w; ";
             } else if (sn == 0) {
                 body << "{ const float t = " << P << "[(long long)grow * " << sm << "]; " << L << "[0] = t; " << L << "[1] = t; " << L << "[2] = t; " << L << "[3] = t; } ";
             } else {
@@ -807,6 +820,7 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
     g.params = params.str();
     g.init = init.str();
     g.cols = cols_text;
+    g.pre = pre.str();
     g.body = body.str();
     g.end = end.str();
     g.unroll = spec.nodes.size() <= 4 ? 8 : (spec.nodes.size() <= 10 ? 2 : 1);
@@ -815,37 +829,50 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
     return g;
 }
 
-GeneratedKernel generate_finalize(int parts, int64_t width, const std::string& name, bool is_max) {
+GeneratedKernel generate_finalize(int parts, int64_t width, const std::string& name, bool is_max, int count, unsigned max_bits) {
     GeneratedKernel g;
     std::ostringstream s;
-    const std::string ident = red_ident(is_max);
+    if (count == 1) max_bits = is_max ? 1u : 0u;
     s << device_prelude();
+    s << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(";
+    for (int i = 0; i < count; ++i) s << (i ? ", " : "") << "const float* __restrict__ part" << i << ", float* __restrict__ out" << i;
+    s << ") {\n";
     if (width == 1) {
-        s << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const float* __restrict__ part, float* __restrict__ out) {\n"
-          << "    __shared__ float sm[8];\n    float a = " << ident << ";\n"
-          << "    for (int p = threadIdx.x; p < " << parts << "; p += 256) a = " << red_comb(is_max, "a", "part[p]") << ";\n"
-          << "    a = " << red_warp(is_max) << "(a, 32);\n    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = a;\n    __syncthreads();\n"
-          << "    if (threadIdx.x == 0) { float t = " << ident << "; for (int w = 0; w < 8; ++w) t = " << red_comb(is_max, "t", "sm[w]") << "; out[0] = t; }\n}\n";
-        g.step.grid = 1;
+        // one block per pair
+        s << "    __shared__ float sm[8];\n";
+        for (int i = 0; i < count; ++i) {
+            const bool mx = (max_bits >> i) & 1u;
+            s << "    if (blockIdx.x == " << i << ") {\n        float a = " << red_ident(mx) << ";\n"
+              << "        for (int p = threadIdx.x; p < " << parts << "; p += 256) a = " << red_comb(mx, "a", "part" + std::to_string(i) + "[p]") << ";\n"
+              << "        a = " << red_warp(mx) << "(a, 32);\n        if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = a;\n        __syncthreads();\n"
+              << "        if (threadIdx.x == 0) { float t = " << red_ident(mx) << "; for (int w = 0; w < 8; ++w) t = " << red_comb(mx, "t", "sm[w]") << "; out" << i << "[0] = t; }\n    }\n";
+        }
+        s << "}\n";
+        g.step.grid = count;
     } else {
         // 32 columns per block; the 8 warps split the partials (warp w takes p = w, w + 8, ...), so a column's chain of
         // dependent additions is parts / 8 long and every load is a full 128-byte line; the 8 sub-sums are added in order.
-        s << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const float* __restrict__ part, float* __restrict__ out) {\n"
-          << "    __shared__ float sm[8][32];\n"
-          << "    const int c = blockIdx.x * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;\n"
-          << "    float a = " << ident << ";\n"
-          << "    if (c < " << width << ") for (int p = w; p < " << parts << "; p += 8) a = " << red_comb(is_max, "a", "part[(long long)p * " + std::to_string(width) + " + c]") << ";\n"
-          << "    sm[w][threadIdx.x & 31] = a;\n    __syncthreads();\n"
-          << "    if (w == 0 && c < " << width << ") { float t = sm[0][threadIdx.x]; for (int k = 1; k < 8; ++k) t = " << red_comb(is_max, "t", "sm[k][threadIdx.x]") << "; out[c] = t; }\n}\n";
-        g.step.grid = (int)((width + 31) / 32);
+        const int bx = (int)((width + 31) / 32);
+        s << "    __shared__ float sm[8][32];\n"
+          << "    const int pair = blockIdx.x / " << bx << ";\n"
+          << "    const int c = (blockIdx.x % " << bx << ") * 32 + (threadIdx.x & 31), w = threadIdx.x >> 5;\n";
+        for (int i = 0; i < count; ++i) {
+            const bool mx = (max_bits >> i) & 1u;
+            s << "    if (pair == " << i << ") {\n        float a = " << red_ident(mx) << ";\n"
+              << "        if (c < " << width << ") for (int p = w; p < " << parts << "; p += 8) a = " << red_comb(mx, "a", "part" + std::to_string(i) + "[(long long)p * " + std::to_string(width) + " + c]") << ";\n"
+              << "        sm[w][threadIdx.x & 31] = a;\n        __syncthreads();\n"
+              << "        if (w == 0 && c < " << width << ") { float t = sm[0][threadIdx.x]; for (int k = 1; k < 8; ++k) t = " << red_comb(mx, "t", "sm[k][threadIdx.x]") << "; out" << i << "[c] = t; }\n    }\n";
+        }
+        s << "}\n";
+        g.step.grid = bx * count;
     }
     g.step.block = 256;
     g.step.name = name;
     g.step.source = s.str();
     g.step.key = std::to_string(fnv1a(g.step.source));
-    g.step.what = std::string(is_max ? "finalize_max" : "finalize") + "[parts=" + std::to_string(parts) + ",width=" + std::to_string(width) + "]";
-    g.step.bytes_read = (int64_t)parts * width * 4;
-    g.step.bytes_written = width * 4;
+    g.step.what = std::string(max_bits ? "finalize_max" : "finalize") + "[parts=" + std::to_string(parts) + ",width=" + std::to_string(width) + (count > 1 ? ",outputs=" + std::to_string(count) : "") + "]";
+    g.step.bytes_read = (int64_t)parts * width * 4 * count;
+    g.step.bytes_written = width * 4 * count;
     return g;
 }
 

@@ -70,7 +70,7 @@ struct TcKernel { CompiledKernel* kernel = nullptr; int block = 0, smem = 0; };
 // Generated epilogue of the run-time compiled tensor-core GEMM: text spliced into the kernel template plus the
 // device pointers of its extra parameters, in parameter order.
 struct TcEpilogue {
-    std::string prelude, params, init, cols, body, end;
+    std::string prelude, params, init, cols, pre, body, end;
     int wpq = 1;                       // epilogue warps per TMEM lane quarter (1, 2 or 4)
     int unroll = 8;                    // unrolled row steps per chunk
     std::vector<void*> args;

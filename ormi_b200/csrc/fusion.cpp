@@ -766,7 +766,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
                     if (!ge.error.empty()) { plan.error = ge.error; return plan; }
                     g.has_epi = true;
                     g.epi_prelude = ge.prelude; g.epi_params = ge.params; g.epi_init = ge.init; g.epi_cols = ge.cols; g.epi_body = ge.body;
-                    g.epi_end = ge.end;
+                    g.epi_end = ge.end; g.epi_pre = ge.pre;
                     g.epi_wpq = ge.wpq; g.epi_unroll = ge.unroll;
                     for (const KLoad& l : ks.loads) if (!l.acc) g.epi_args.push_back(buffer_for(l.src_node));
                     for (const KOutput& o : ks.outputs) {
@@ -866,12 +866,17 @@ Plan Scheduler::run(const int* roots, int n_roots) {
             stp.k.args.push_back(eb);
         }
         plan.steps.push_back(stp);
-        for (auto& f : finals) {
-            const KOutput& o = ks.outputs[f.second];
-            int64_t per = o.kind == KOutput::COLSUM ? gk.cols : 1;
-            GeneratedKernel fk = generate_finalize(gk.step.grid, per, "ormi_finalize_" + std::to_string(kernel_serial++), o.is_max);
+        // one finalize launch per geometry: the column partials of all outputs together, the global partials together
+        for (int colwise = 1; colwise >= 0; --colwise) {
+            std::vector<std::pair<int, int>> group;
+            for (auto& f : finals) if ((ks.outputs[f.second].kind == KOutput::COLSUM) == (colwise == 1)) group.push_back(f);
+            if (group.empty()) continue;
+            unsigned max_bits = 0;
+            for (size_t i = 0; i < group.size(); ++i) if (ks.outputs[group[i].second].is_max) max_bits |= 1u << i;
+            const int64_t per = colwise ? gk.cols : 1;
+            GeneratedKernel fk = generate_finalize(gk.step.grid, per, "ormi_finalize_" + std::to_string(kernel_serial++), max_bits != 0, (int)group.size(), max_bits);
             Step fs; fs.type = Step::Kernel; fs.k = fk.step;
-            fs.k.args = {f.first, buffer_for(o.node)};
+            for (auto& f : group) { fs.k.args.push_back(f.first); fs.k.args.push_back(buffer_for(ks.outputs[f.second].node)); }
             plan.steps.push_back(fs);
         }
     }
@@ -945,7 +950,7 @@ std::string plan_to_json(const Plan& plan) {
               << ", \"store_c\": " << (g.store_c ? "true" : "false") << ", \"epilogue\": \"" << json_escape(g.epi_what) << "\", \"epi_args\": [";
             for (size_t a = 0; a < g.epi_args.size(); ++a) o << (a ? ", " : "") << g.epi_args[a];
             o << "], \"epi_body\": \"" << json_escape(g.epi_body) << "\", \"epi_cols\": \"" << json_escape(g.epi_cols) << "\", \"epi_init\": \""
-              << json_escape(g.epi_init) << "\", \"epi_end\": \"" << json_escape(g.epi_end) << "\", \"epi_params\": \"" << json_escape(g.epi_params) << "\", \"epi_prelude\": \"" << json_escape(g.epi_prelude) << "\"}";
+              << json_escape(g.epi_init) << "\", \"epi_pre\": \"" << json_escape(g.epi_pre) << "\", \"epi_end\": \"" << json_escape(g.epi_end) << "\", \"epi_params\": \"" << json_escape(g.epi_params) << "\", \"epi_prelude\": \"" << json_escape(g.epi_prelude) << "\"}";
         }
     }
     o << "], \"results\": [";

@@ -51,6 +51,7 @@ KernelStep make_kernel(const Variant& v, const TcEpilogue* epi) {
     def("G_EPI_INIT", epi ? one_line(epi->init) : "");
     def("G_EPI_COLS", epi ? one_line(epi->cols) : "");
     def("G_EPI_BODY", epi ? one_line(epi->body) : "*reinterpret_cast<float4*>(C + (size_t)grow * N + gcol) = acc;");
+    def("G_EPI_PRE", epi ? one_line(epi->pre) : "");
     def("G_EPI_END", epi ? one_line(epi->end) : "");
     def("G_EPI_UNROLL", std::to_string(epi ? epi->unroll : 8));
     if (epi) src += epi->prelude;
@@ -174,7 +175,7 @@ void gemm_tc(ormi_b200_ctx* ctx, const void* a16, int a_mn, const void* b16, int
     int cg = ctx->tc_cta_group;
     // the kernel of this variant: looked up by its few parameters and the epilogue text, not by the whole source
     std::string vkey = std::to_string(cg) + "|" + std::to_string(a_mn) + "|" + std::to_string(b_mn);
-    if (epi) vkey += "|" + std::to_string(epi->wpq) + "|" + std::to_string(epi->unroll) + "|" + epi->params + "|" + epi->init + "|" + epi->cols + "|" + epi->body + "|" + epi->end;
+    if (epi) vkey += "|" + std::to_string(epi->wpq) + "|" + std::to_string(epi->unroll) + "|" + epi->params + "|" + epi->init + "|" + epi->cols + "|" + epi->pre + "|" + epi->body + "|" + epi->end;
     auto found = ctx->tc_kernels.find(vkey);
     if (found == ctx->tc_kernels.end()) {
         const Variant v = make_variant(cg, a_mn, b_mn, epi ? epi->wpq : 1);

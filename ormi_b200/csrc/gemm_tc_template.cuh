@@ -21,6 +21,8 @@ R"GEMMTPL(
 //   G_EPI_PARAMS  extra kernel parameters of the generated epilogue (text starting with a comma, or empty)
 //   G_EPI_INIT    statements run once by every epilogue thread (scalar operands)
 //   G_EPI_COLS    statements run once per 32-column chunk: `gcol` is the first of the 4 columns this lane owns
+//   G_EPI_PRE     statements run per row step `p` (rows grow = row0 + 4 p + rsub) before the bounds guard: they take the
+//                 prefetched pieces of full-matrix operands and request the next step's
 //   G_EPI_BODY    statements run per (row, 4 columns): `acc` (float4), `grow`, `gcol`, `M`, `N` are in scope
 //   G_EPI_END     statements run once per chunk after its rows (column sums: combine lanes, write the block's partial;
 //                 `row0` is the first row of the warp's 32-row block, `rsub` = lane / 8)
@@ -425,6 +427,7 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
                     float4 acc;
                     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(acc.x), "=f"(acc.y), "=f"(acc.z), "=f"(acc.w)
                                  : "r"(stg + (unsigned)rl * 128u + (unsigned)((cq ^ (rl & 7)) << 4)) : "memory");
+                    G_EPI_PRE
                     if (grow < M && gcol < N) {
                         G_EPI_BODY
                     }

@@ -70,7 +70,7 @@ GeneratedKernel generate_kernel(const KernelSpec& spec, const std::string& name,
 // Kernel-argument order: every other load in order, then per output the fp32 pointer (if store; for a COLSUM the
 // partial buffer) and the bf16 pointer (if twin), then the product's bf16 pointer (if twin_c).
 struct GeneratedEpilogue {
-    std::string prelude, params, init, cols, body, end;
+    std::string prelude, params, init, cols, pre, body, end;   // pre: per row step, before the bounds guard of body
     int wpq = 1;
     int unroll = 8;             // how many of the 8 row steps of a chunk are unrolled (heavy bodies: 1, for the instruction cache)
     std::string error;
@@ -78,7 +78,9 @@ struct GeneratedEpilogue {
 GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, bool twin_c);
 
 // out[c] = sum over p < parts of partial[p * width + c]   (fixed order: deterministic)
-GeneratedKernel generate_finalize(int parts, int64_t width, const std::string& name, bool is_max = false);
+// `count` > 1: one launch adds up `count` partial buffers of the same geometry (arguments: part0, out0, part1, out1, ...;
+// is_max then holds one flag per pair, packed as bits).
+GeneratedKernel generate_finalize(int parts, int64_t width, const std::string& name, bool is_max = false, int count = 1, unsigned max_bits = 0);
 // One thread per output element, serial sum over the reduced coordinates, arbitrary input strides.
 GeneratedKernel generate_generic_sum(const std::vector<int>& shape, const std::vector<int>& strides,
                                      const std::vector<bool>& reduced, const std::string& name, bool is_max = false);

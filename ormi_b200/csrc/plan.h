@@ -55,7 +55,7 @@ struct GemmStep {
     int a16 = -1, b16 = -1;              // Twin16 plan buffers written earlier in the plan (-1: the context's twin cache, or a conversion)
     bool store_c = true;                 // write the fp32 product to `c`
     bool has_epi = false;                // pointwise work fused behind the accumulator
-    std::string epi_prelude, epi_params, epi_init, epi_cols, epi_body, epi_end, epi_what;
+    std::string epi_prelude, epi_params, epi_init, epi_cols, epi_pre, epi_body, epi_end, epi_what;
     int epi_wpq = 1, epi_unroll = 8;
     std::vector<int> epi_args;           // plan buffer ids, in the epilogue's parameter order
 };

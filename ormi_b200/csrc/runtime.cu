@@ -322,7 +322,7 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
                     TcEpilogue epi;
                     if (st.g.has_epi) {
                         epi.prelude = st.g.epi_prelude; epi.params = st.g.epi_params; epi.init = st.g.epi_init;
-                        epi.cols = st.g.epi_cols; epi.body = st.g.epi_body; epi.end = st.g.epi_end; epi.wpq = st.g.epi_wpq; epi.unroll = st.g.epi_unroll;
+                        epi.cols = st.g.epi_cols; epi.pre = st.g.epi_pre; epi.body = st.g.epi_body; epi.end = st.g.epi_end; epi.wpq = st.g.epi_wpq; epi.unroll = st.g.epi_unroll;
                         for (int a : st.g.epi_args) epi.args.push_back(bufs[a]);
                     }
                     gemm_tc_from_fp32(ctx, g, st.g.a16 >= 0 ? bufs[st.g.a16] : nullptr, st.g.b16 >= 0 ? bufs[st.g.b16] : nullptr,

@@ -69,14 +69,30 @@ def run_plan(plan: dict) -> dict:
 
 
 def _epilogue_source(name, s):
-    """The generated epilogue text of a tensor-core GEMM step as a plain loop over (row, 4 columns)."""
+    """The generated epilogue text of a tensor-core GEMM step as a plain loop over (32-row block, 4 columns)."""
+    import re
+    sums = sorted(set(re.findall(r"float cs(\d+)\[4\]", s["epi_cols"])))
+    carry_in = " ".join(f"if (have) for (int j = 0; j < 4; ++j) cs{o}[j] = carry[{k}][j];" for k, o in enumerate(sums))
+    carry_out = " ".join(f"for (int j = 0; j < 4; ++j) carry[{k}][j] = cs{o}[j];" for k, o in enumerate(sums)) + " have = true;"
+    text = _epilogue_template(name, s)
+    return text.replace("EMUL_CARRY_IN", carry_in).replace("EMUL_CARRY_OUT", carry_out)
+
+
+def _epilogue_template(name, s):
     return (s["epi_prelude"] + f'\nextern "C" void {name}(float* C, const float* P, int M, int N{s["epi_params"]}) {{\n'
-            f'    {s["epi_init"]}\n    const int rsub = 0;\n'
+            f'    {s["epi_init"]}\n'
+            # the four lane groups of a warp (rsub = 0..3) walk rows row0 + rsub + 4 p one after the other; their column
+            # partials are combined by carrying cs<o> over (the emulator's ormi_epi_rows is the identity)
             f'    for (int row0 = 0; row0 < M; row0 += 32) for (int gcol = 0; gcol < N; gcol += 4) {{\n'
-            f'        {s["epi_cols"]}\n        for (int grow = row0; grow < row0 + 32 && grow < M; ++grow) {{\n'
-            f'            const float4 acc = make_float4(P[(long long)grow * N + gcol], P[(long long)grow * N + gcol + 1], '
-            f'P[(long long)grow * N + gcol + 2], P[(long long)grow * N + gcol + 3]);\n            {s["epi_body"]}\n        }}\n'
-            f'        {s["epi_end"]}\n    }}\n}}\n')
+            f'        float carry[8][4]; bool have = false;\n'
+            f'        for (int rsub_i = 0; rsub_i < 4; ++rsub_i) {{\n            const int rsub = rsub_i == 3 ? 0 : rsub_i + 1;\n'   # rsub 0 last: it writes the partial
+            f'            {s["epi_cols"]}\n            EMUL_CARRY_IN\n'
+            f'            for (int p = 0; p < 8; ++p) {{\n                const int grow = row0 + 4 * p + rsub;\n'
+            f'                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);\n'
+            f'                if (grow < M) acc = make_float4(P[(long long)grow * N + gcol], P[(long long)grow * N + gcol + 1], '
+            f'P[(long long)grow * N + gcol + 2], P[(long long)grow * N + gcol + 3]);\n'
+            f'                {s["epi_pre"]}\n                if (grow < M && gcol < N) {{ {s["epi_body"]} }}\n            }}\n'
+            f'            EMUL_CARRY_OUT\n            if (rsub == 0) {{ {s["epi_end"]} }}\n        }}\n    }}\n}}\n')
 
 
 def _to_bf16(x):
