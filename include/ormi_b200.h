@@ -154,6 +154,14 @@ int ormi_b200_compile_source(const ormi_b200_node* nodes, int n_nodes, int root,
                              char* buf, size_t cap, size_t* out_len,
                              int* leaf_index, int leaf_cap, int* n_leaves);
 
+/* The per-op plug-in point of the reference's CUDA compiler, CUDALoweringRegistry
+ * (ormi-core/csrc/backend/cuda/lowering_registry.h:11-38; consulted for every tape entry, compiler.cu:104-108): replaces
+ * the C expression the code generator emits for pointwise op `op` — in the fused kernels, the GEMM epilogues and the
+ * source ormi_b200_compile_source returns alike.  `expr` is CUDA C over the operand placeholders $0 and $1, e.g.
+ * "fmaxf($0, $1)"; NULL or "" restores the built-in expression.  Process-wide, like the reference's registry; schedules
+ * cached before the change are not reused.  Not to be called while another thread realizes a graph. */
+int ormi_b200_set_lowering(int op, const char* expr);
+
 /* compile_ptx (ormi-core/csrc/backend/cuda/utils.cu:6-27): NVRTC, but straight to an sm_100a cubin.
  * Needs no device.  The image is written to `buf` when it fits; *out_len is its size. */
 int ormi_b200_compile_cubin(const char* source, char* buf, size_t cap, size_t* out_len);

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "ormi_b200_plan_json": (c_int, [P(CNode), c_int, P(ctypes.c_int), c_int, c_char_p, c_size_t, P(c_size_t)]),
     "ormi_b200_plan_json_opts": (c_int, [P(CNode), c_int, P(ctypes.c_int), c_int, c_char_p, c_char_p, c_size_t, P(c_size_t)]),
     "ormi_b200_compile_source": (c_int, [P(CNode), c_int, c_int, c_char_p, c_size_t, P(c_size_t), P(ctypes.c_int), c_int, P(ctypes.c_int)]),
+    "ormi_b200_set_lowering": (c_int, [c_int, c_char_p]),
     "ormi_b200_compile_cubin": (c_int, [c_char_p, c_char_p, c_size_t, P(c_size_t)]),
     "ormi_b200_sum": (c_int, [c_void_p, c_void_p, c_int, P(ctypes.c_int32), P(ctypes.c_int32), P(ctypes.c_int32), c_int, c_void_p]),
     "ormi_b200_matmul": (c_int, [c_void_p, c_void_p, c_int, P(ctypes.c_int32), P(ctypes.c_int32),

@@ -257,6 +257,14 @@ int ormi_b200_compile_source(const ormi_b200_node* nodes, int n_nodes, int root,
     });
 }
 
+int ormi_b200_set_lowering(int op, const char* expr) {
+    return guarded([&] {
+        const bool pointwise = (op >= ORMI_OP_NEG && op <= ORMI_OP_POW) || op == ORMI_OP_MAXIMUM || op == ORMI_OP_GE;
+        need(pointwise, "ormi_b200_set_lowering: only pointwise ops have a lowering");
+        set_lowering(op, expr ? expr : "");
+    });
+}
+
 int ormi_b200_compile_cubin(const char* source, char* buf, size_t cap, size_t* out_len) {
     return guarded([&] {
         need(source != nullptr, "ormi_b200_compile_cubin: source is NULL");

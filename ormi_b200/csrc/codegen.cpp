@@ -19,9 +19,11 @@
 // ormi-core/csrc/backend/cpu/lowerings/pointwise.cpp:5-15), and exp/log/sin/cos are the accurate CUDA
 // functions, never the fast intrinsics.
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <functional>
 #include <map>
+#include <mutex>
 #include <sstream>
 
 #include "kernel_ir.h"
@@ -136,10 +138,41 @@ __device__ __forceinline__ void ormi_drain() { const unsigned long long t0 = orm
 }
 
 namespace {
+std::mutex g_lowering_mutex;
+std::map<int, std::string> g_lowerings;
+std::atomic<uint64_t> g_lowering_generation{0};
+}  // namespace
+
+void set_lowering(int op, const std::string& expr) {
+    std::lock_guard<std::mutex> lock(g_lowering_mutex);
+    if (expr.empty()) g_lowerings.erase(op); else g_lowerings[op] = expr;
+    ++g_lowering_generation;
+}
+
+bool lowering_for(int op, std::string* expr) {
+    std::lock_guard<std::mutex> lock(g_lowering_mutex);
+    auto it = g_lowerings.find(op);
+    if (it == g_lowerings.end()) return false;
+    if (expr) *expr = it->second;
+    return true;
+}
+
+uint64_t lowering_generation() { return g_lowering_generation.load(); }
+
+namespace {
 
 int64_t prod(const std::vector<int>& v, size_t a, size_t b) { int64_t p = 1; for (size_t i = a; i < b; ++i) p *= v[i]; return p; }
 
 std::string op_expr(int op, const std::string& a, const std::string& b) {
+    std::string custom;
+    if (op < 1000 && lowering_for(op, &custom)) {      // a registered lowering replaces the built-in expression
+        std::string out;
+        for (size_t i = 0; i < custom.size(); ++i) {
+            if (custom[i] == '$' && i + 1 < custom.size() && (custom[i + 1] == '0' || custom[i + 1] == '1')) { out += "(" + (custom[i + 1] == '0' ? a : b) + ")"; ++i; }
+            else out += custom[i];
+        }
+        return "(" + out + ")";
+    }
     switch (op) {
         case ORMI_OP_ADD: return "__fadd_rn(" + a + ", " + b + ")";
         case ORMI_OP_SUB: return "__fsub_rn(" + a + ", " + b + ")";
@@ -560,6 +593,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         if (col_pred) p += std::string(p.empty() ? "" : " && ") + "(" + col_of(j + " / " + std::to_string(V), j + " % " + std::to_string(V)) + ") < " + std::to_string(C);
         return p;
     };
+    const bool custom_div = lowering_for(ORMI_OP_DIV, nullptr);     // a registered lowering for DIV is emitted as written
     for (int lv = 0; lv <= max_level; ++lv) {
         // (a) per-row scalars of this level
         for (const KNode& kn : spec.nodes) {
@@ -576,14 +610,14 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
             // quotient, inside the 1e-6 pointwise tolerance, and about ten instructions per element cheaper —
             // the deep row kernels are instruction-issue bound, not only bandwidth bound.
             for (const KNode& kn : spec.nodes) {
-                if (rowv(&kn) || level[kn.node] != lv || kn.op != ORMI_OP_DIV || is_elem(kn.operands[1])) continue;
+                if (rowv(&kn) || level[kn.node] != lv || kn.op != ORMI_OP_DIV || is_elem(kn.operands[1]) || custom_div) continue;
                 s << "        const float rcp" << kn.node << " = __frcp_rn(" << ref(kn.operands[1], "0") << ");\n";
             }
             s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) {\n";
             for (const KNode& kn : spec.nodes) {
                 if (rowv(&kn) || level[kn.node] != lv) continue;
                 std::string a = ref(kn.operands[0], "j"), b = kn.operands.size() > 1 ? ref(kn.operands[1], "j") : "";
-                if (kn.op == ORMI_OP_DIV && !is_elem(kn.operands[1]))
+                if (kn.op == ORMI_OP_DIV && !is_elem(kn.operands[1]) && !custom_div)
                     s << "            v" << kn.node << "[j] = __fmul_rn(" << a << ", rcp" << kn.node << ");\n";
                 else
                     s << "            v" << kn.node << "[j] = " << op_expr(kn.op, a, b) << ";\n";
@@ -959,6 +993,13 @@ SimpleKernel compile_simple(const ormi_b200_node* nodes, int n_nodes, int root) 
         std::string e;
         const std::string& a = st.operands[0];
         const std::string b = st.operands.size() > 1 ? st.operands[1] : "";
+        std::string custom;
+        if (lowering_for(st.op, &custom)) {
+            for (size_t i = 0; i < custom.size(); ++i) {
+                if (custom[i] == '$' && i + 1 < custom.size() && (custom[i + 1] == '0' || custom[i + 1] == '1')) { e += (custom[i + 1] == '0' ? a : b); ++i; }
+                else e += custom[i];
+            }
+        } else
         switch (st.op) {   // plain C operators, as in ormi-core/csrc/backend/cuda/lowerings/pointwise.cpp:4-13; -fmad=false keeps them un-fused
             case ORMI_OP_ADD: e = a + " + " + b; break;
             case ORMI_OP_SUB: e = a + " - " + b; break;

@@ -105,6 +105,12 @@ struct SimpleKernel {
 };
 SimpleKernel compile_simple(const ormi_b200_node* nodes, int n_nodes, int root);
 
+// Process-wide overrides of the expression emitted for a pointwise op (ormi_b200_set_lowering); `$0`, `$1` stand for
+// the operands.  lowering_generation() changes with every edit and is part of the plan key.
+void set_lowering(int op, const std::string& expr);
+bool lowering_for(int op, std::string* expr);
+uint64_t lowering_generation();
+
 uint64_t fnv1a(const std::string& s);
 std::string device_prelude();
 

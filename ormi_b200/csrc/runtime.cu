@@ -216,6 +216,7 @@ static std::string graph_key(const ormi_b200_ctx* ctx, const ormi_b200_node* nod
     auto mix = [&](uint64_t v) { const uint32_t w = (uint32_t)v; key.append(reinterpret_cast<const char*>(&w), 4); };
     mix((uint64_t)n); mix(ctx->fusion ? 1 : 0); mix((uint64_t)ctx->matmul_mode); mix(aligned ? 1 : 0); mix((uint64_t)ctx->tc_cta_group);
     for (int v : ctx->tune) mix((uint64_t)(uint32_t)v);
+    mix(lowering_generation());
     for (int i = 0; i < n; ++i) {
         const auto& nd = nodes[i];
         mix((uint64_t)nd.op); mix((uint64_t)nd.n_parents);

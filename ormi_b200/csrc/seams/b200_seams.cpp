@@ -11,11 +11,13 @@
 // Errors keep the reference's convention: std::runtime_error carrying the backend's message.
 #include <algorithm>
 #include <cstring>
+#include <mutex>
 #include <stdexcept>
 #include <unordered_map>
 #include <unordered_set>
 
 #include "ormi_b200.h"
+#include "b200_backend.h"
 
 #include "core/allocator.h"
 #include "core/memory.h"
@@ -37,15 +39,55 @@ namespace {
 [[noreturn]] void raise() { throw std::runtime_error(ormi_b200_last_error()); }
 #define B200(call) do { if ((call) != 0) raise(); } while (0)
 
-// One context per process on device 0: ormi::Device carries an id, but every Buffer is built with id 0
-// (core/memory.cpp:94).  Creating it fails without a GPU, which the callers rely on.
-ormi_b200_ctx* ctx() {
-    static ormi_b200_ctx* c = [] {
-        ormi_b200_ctx* p = nullptr;
-        if (ormi_b200_init(0, &p) != 0) raise();
-        return p;
-    }();
-    return c;
+// One backend context per CUDA device, created on first use.  ormi::Device carries an id (core/device.h:10), but the
+// allocator interface has none and every Buffer is built with id 0 (core/memory.cpp:94): so allocations go to the
+// ACTIVE device (cuda::set_active_device, default 0 — one process per GPU sets it once to its local rank), every
+// pointer remembers the device that owns it, and a graph runs on the context that owns its inputs.  A node whose
+// Device.id names another device than its inputs live on is an error, not a silent copy.  Creating a context fails
+// without a GPU, which the callers rely on (csrc/tests/test_utils.h:17-21).
+std::mutex g_ctx_mutex;
+std::unordered_map<int, ormi_b200_ctx*> g_contexts;
+int g_active_device = 0;
+std::unordered_map<const void*, int> g_owner;      // device pointer -> device id (pool blocks handed out through the allocator)
+
+ormi_b200_ctx* ctx(int device = -1) {
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    if (device < 0) device = g_active_device;
+    auto it = g_contexts.find(device);
+    if (it != g_contexts.end()) return it->second;
+    ormi_b200_ctx* p = nullptr;
+    if (ormi_b200_init(device, &p) != 0) raise();
+    g_contexts[device] = p;
+    return p;
+}
+
+int owner_of(const void* ptr) {
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    auto it = g_owner.find(ptr);
+    return it == g_owner.end() ? g_active_device : it->second;
+}
+
+// The pointwise expressions this backend emits for the ops of the reference's registry, in the registry's own notation
+// ("<expr>;" over the operand names).  An entry that differs — somebody registered a lowering of their own — is handed
+// to the code generator; one that matches (or was restored) clears the override.
+const std::pair<ops::OpEnum, const char*> kDefaultLowerings[] = {
+    {ops::OpEnum::ADD, "$0 + $1;"}, {ops::OpEnum::SUB, "$0 - $1;"}, {ops::OpEnum::MUL, "$0 * $1;"}, {ops::OpEnum::DIV, "$0 / $1;"},
+    {ops::OpEnum::POW, "ormi_pow($0, $1);"}, {ops::OpEnum::NEG, "-$0;"}, {ops::OpEnum::EXP, "expf($0);"}, {ops::OpEnum::LOG, "logf($0);"},
+    {ops::OpEnum::SIN, "sinf($0);"}, {ops::OpEnum::COS, "cosf($0);"}};
+
+void sync_lowerings() {
+    static std::unordered_map<int, std::string> sent;
+    for (const auto& d : kDefaultLowerings) {
+        std::string text;
+        try { text = cuda::CUDALoweringRegistry::get(d.first)({"$0", "$1"}); } catch (const std::exception&) { continue; }
+        const int op = static_cast<int>(d.first);
+        std::string expr = text == d.second ? std::string() : text;
+        while (!expr.empty() && (expr.back() == ';' || expr.back() == ' ' || expr.back() == '\n')) expr.pop_back();
+        auto it = sent.find(op);
+        if ((it == sent.end() && expr.empty()) || (it != sent.end() && it->second == expr)) continue;
+        B200(ormi_b200_set_lowering(op, expr.c_str()));
+        sent[op] = expr;
+    }
 }
 
 bool is_view(ops::OpEnum op) { return ViewOpRegistry::get().contains(op); }
@@ -140,20 +182,34 @@ void adopt_results(Flat& f) {
 class B200Allocator : public IAllocator {
 public:
     B200Allocator() { ctx(); }
-    void* allocate(size_t bytes) override { void* p = nullptr; B200(ormi_b200_alloc(ctx(), bytes, &p)); return p; }
-    void free(void* ptr, size_t bytes) override { if (ptr) ormi_b200_free(ctx(), ptr, bytes); }
-    void memset(void* ptr, int value, size_t bytes) override { B200(ormi_b200_memset(ctx(), ptr, value, bytes)); }
-    void memcpy(void* dst, const void* src, size_t size) override { B200(ormi_b200_memcpy_d2d(ctx(), dst, src, size)); }
+    void* allocate(size_t bytes) override {
+        int dev;
+        { std::lock_guard<std::mutex> lock(g_ctx_mutex); dev = g_active_device; }
+        void* p = nullptr;
+        B200(ormi_b200_alloc(ctx(dev), bytes, &p));
+        std::lock_guard<std::mutex> lock(g_ctx_mutex);
+        g_owner[p] = dev;
+        return p;
+    }
+    void free(void* ptr, size_t bytes) override {
+        if (!ptr) return;
+        const int dev = owner_of(ptr);
+        { std::lock_guard<std::mutex> lock(g_ctx_mutex); g_owner.erase(ptr); }
+        ormi_b200_free(ctx(dev), ptr, bytes);
+    }
+    void memset(void* ptr, int value, size_t bytes) override { B200(ormi_b200_memset(ctx(owner_of(ptr)), ptr, value, bytes)); }
+    void memcpy(void* dst, const void* src, size_t size) override { B200(ormi_b200_memcpy_d2d(ctx(owner_of(dst)), dst, src, size)); }
     void fill_n(void* dst, const void* val_ptr, size_t elements, DType dtype) override {
+        ormi_b200_ctx* c = ctx(owner_of(dst));
         switch (dtype) {
             case DType::Float32:
-            case DType::Int32: B200(ormi_b200_fill_u32(ctx(), dst, *static_cast<const uint32_t*>(val_ptr), elements)); break;
-            case DType::Bool: B200(ormi_b200_fill_u8(ctx(), dst, *static_cast<const uint8_t*>(val_ptr), elements)); break;
+            case DType::Int32: B200(ormi_b200_fill_u32(c, dst, *static_cast<const uint32_t*>(val_ptr), elements)); break;
+            case DType::Bool: B200(ormi_b200_fill_u8(c, dst, *static_cast<const uint8_t*>(val_ptr), elements)); break;
             default: throw std::runtime_error("DType is not supported.");
         }
     }
-    void copy_device_to_host(void* dst, const void* src, size_t bytes) override { B200(ormi_b200_memcpy_d2h(ctx(), dst, src, bytes)); }
-    void copy_host_to_device(void* dst, const void* src, size_t bytes) override { B200(ormi_b200_memcpy_h2d(ctx(), dst, src, bytes)); }
+    void copy_device_to_host(void* dst, const void* src, size_t bytes) override { B200(ormi_b200_memcpy_d2h(ctx(owner_of(src)), dst, src, bytes)); }
+    void copy_host_to_device(void* dst, const void* src, size_t bytes) override { B200(ormi_b200_memcpy_h2d(ctx(owner_of(dst)), dst, src, bytes)); }
     bool is_host_visible() const override { return false; }
 };
 
@@ -168,6 +224,11 @@ IAllocator* get_cuda_allocator() {
 extern "C" int ormi_engine_b200_set_option(const char* key, const char* value) {
     try { return ormi_b200_set_option(ctx(), key, value); } catch (...) { return 1; }
 }
+// The device later allocations (and so the graphs built on them) go to; one process per GPU calls it once with its
+// local rank.  Non-zero when the device does not exist.
+extern "C" int ormi_engine_b200_set_device(int device) {
+    try { cuda::set_active_device(device); return 0; } catch (...) { return 1; }
+}
 extern "C" long long ormi_engine_b200_counter(const char* name) {
     try {
         int64_t v = 0;
@@ -180,17 +241,53 @@ namespace cuda {
 // ---------------------------------------------------------------------------------------------- seam 2
 // Realizes the whole un-realized graph under `root` in one call: the fusion scheduler decides what becomes a
 // kernel.  Post-conditions of the reference (jit.cu:26-28): root->data set, root->view contiguous.
+void set_active_device(int device) {
+    ctx(device);                                   // throws when there is no such device
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    g_active_device = device;
+}
+
+int active_device() {
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    return g_active_device;
+}
+
+ormi_b200_ctx* b200_context(int device) { return ctx(device); }
+
+// The context a graph runs on: the one that owns its realized inputs.  Inputs on two devices, or a node that names
+// another device (Device.id) than its inputs live on, are refused.
+static int device_of_graph(const Flat& f, const Node& root) {
+    int dev = -1;
+    for (size_t i = 0; i < f.order.size(); ++i) {
+        if (!f.order[i]->is_realized() || !f.nodes[i].data) continue;
+        const int d = owner_of(f.nodes[i].data);
+        if (dev >= 0 && d != dev) throw std::runtime_error("the graph reads tensors that live on cuda:" + std::to_string(dev) + " and cuda:" + std::to_string(d));
+        dev = d;
+    }
+    if (dev < 0) dev = active_device();
+    if (root.device.id != 0 && root.device.id != dev)
+        throw std::runtime_error("node placed on cuda:" + std::to_string(root.device.id) + " but its inputs live on cuda:" + std::to_string(dev));
+    return dev;
+}
+
 void execute_jit(std::shared_ptr<Node> root) {
     if (root->is_realized()) return;
+    sync_lowerings();
     Flat f = flatten(root, true);
     int r = (int)f.nodes.size() - 1;
-    B200(ormi_b200_realize(ctx(), f.nodes.data(), (int)f.nodes.size(), &r, 1));
+    const int dev = device_of_graph(f, *root);
+    B200(ormi_b200_realize(ctx(dev), f.nodes.data(), (int)f.nodes.size(), &r, 1));
+    {   // what the backend handed out belongs to that device
+        std::lock_guard<std::mutex> lock(g_ctx_mutex);
+        for (const auto& d : f.nodes) if (d.flags & ORMI_NODE_OWNED) g_owner[d.data] = dev;
+    }
     adopt_results(f);
     if (!is_view(root->op)) root->view.strides = calc_contiguous_strides(root->view.shape);
 }
 
 // ---------------------------------------------------------------------------------------------- seam 3
 CompilationResult compile(std::shared_ptr<Node> root) {
+    sync_lowerings();
     Flat f = flatten(root, false);
     std::vector<char> src(1 << 20);
     std::vector<int> leaves(f.nodes.size() + 1);
@@ -223,7 +320,7 @@ std::vector<char> compile_ptx(const std::string& kernel_code, CUdevice) {
 std::shared_ptr<Buffer> matmul(std::shared_ptr<Buffer> A, const TensorView& view_A, std::shared_ptr<Buffer> B,
                                const TensorView& view_B, const TensorView& out_view) {
     auto out = empty(out_view.shape, DeviceEnum::CUDA);
-    B200(ormi_b200_matmul(ctx(), static_cast<const float*>(A->ptr), (int)view_A.shape.size(), view_A.shape.data(), view_A.strides.data(),
+    B200(ormi_b200_matmul(ctx(owner_of(A->ptr)), static_cast<const float*>(A->ptr), (int)view_A.shape.size(), view_A.shape.data(), view_A.strides.data(),
                           static_cast<const float*>(B->ptr), (int)view_B.shape.size(), view_B.shape.data(), view_B.strides.data(),
                           static_cast<float*>(out->ptr), (int)out_view.shape.size(), out_view.shape.data()));
     return out;
@@ -236,7 +333,7 @@ void matmul_handler(std::shared_ptr<Node> root) {
 std::shared_ptr<Buffer> sum(std::shared_ptr<Buffer> in_buf, const TensorView& in_view, const std::vector<int>& axes,
                             const TensorView& out_view, const bool) {
     auto out = empty(out_view.shape, DeviceEnum::CUDA);
-    B200(ormi_b200_sum(ctx(), static_cast<const float*>(in_buf->ptr), (int)in_view.shape.size(), in_view.shape.data(), in_view.strides.data(),
+    B200(ormi_b200_sum(ctx(owner_of(in_buf->ptr)), static_cast<const float*>(in_buf->ptr), (int)in_view.shape.size(), in_view.shape.data(), in_view.strides.data(),
                        axes.data(), (int)axes.size(), static_cast<float*>(out->ptr)));
     return out;
 }

@@ -13,8 +13,11 @@ BINARY = os.path.join(ROOT, "ormi_b200", "csrc", "seams", "_build", "ormi_backen
 needs_binary = pytest.mark.skipif(not os.path.exists(BINARY), reason="seams test binary not built (needs the reference checkout)")
 
 
-def run_suite():
-    out = subprocess.run([BINARY], capture_output=True, text=True, timeout=600)
+SEAM_BINARY = os.path.join(ROOT, "ormi_b200", "csrc", "seams", "_build", "b200_seam_tests")
+
+
+def run_suite(binary=BINARY):
+    out = subprocess.run([binary], capture_output=True, text=True, timeout=600)
     m = re.search(r"(\d+) tests ran: (\d+) passed, (\d+) skipped, (\d+) failed", out.stdout)
     assert m, out.stdout[-2000:] + out.stderr[-2000:]
     return out, tuple(int(x) for x in m.groups())
@@ -37,3 +40,20 @@ def test_reference_suite_on_b200():
     and the CUDA-only suites (compiler source strings, execute_jit, cuda::matmul, cuda::sum) run too."""
     out, (ran, passed, skipped, failed) = run_suite()
     assert ran == 125 and failed == 0 and skipped == 0, out.stdout[-4000:]
+
+
+@pytest.mark.skipif(not os.path.exists(SEAM_BINARY), reason="seam test binary not built (needs the reference checkout)")
+def test_seam_additions_cpu_half():
+    """Own cases for what the seams add: a lowering registered in CUDALoweringRegistry shows in cuda::compile's source
+    (no GPU needed); the cases that launch skip themselves here."""
+    out, (ran, passed, skipped, failed) = run_suite(SEAM_BINARY)
+    assert ran == 3 and failed == 0 and passed >= 1, out.stdout[-3000:]
+
+
+@pytest.mark.skipif(not os.path.exists(SEAM_BINARY), reason="seam test binary not built (needs the reference checkout)")
+@pytest.mark.gpu
+def test_seam_additions_on_b200():
+    """On a B200: the registered lowering runs inside a fused kernel (and the stock one again once it is restored), a
+    graph runs on the device that owns its inputs, a node placed on another device is refused."""
+    out, (ran, passed, skipped, failed) = run_suite(SEAM_BINARY)
+    assert ran == 3 and failed == 0 and skipped == 0, out.stdout[-4000:]

@@ -333,3 +333,27 @@ def test_unaligned_inputs_get_scalar_kernels():
     assert "V=1" in plan["steps"][0]["what"]
     ref, _ = O.port_run([y])
     assert np.abs(outs[0] - ref[0]).max() <= REDUCE_TOL * np.abs(ref[0]).max()
+
+
+def test_registered_lowering_replaces_the_builtin_expression():
+    """ormi_b200_set_lowering, the C side of the reference's CUDALoweringRegistry: the expression given for an op is what
+    the fused kernels (and the guarded scalar kernel of ormi_b200_compile_source) evaluate, until it is taken back."""
+    import ctypes
+    from ormi_b200._lib import lib, check
+    x = G.leaf(W.normal(0, (6, 40)))
+    build = lambda: G.add(G.sin(x), G.sum_(G.sin(x), [1], True))
+    try:
+        check(lib.ormi_b200_set_lowering(int(G.OpEnum.SIN), b"cosf($0) * 2.0f"))
+        outs, plan = E.realize([build()])
+        assert "cosf(" in plan["steps"][0]["source"] and "sinf(" not in plan["steps"][0]["source"].split("#endif")[-1]
+        c = 2.0 * np.cos(x.data.host.astype(np.float64))
+        assert np.abs(outs[0] - (c + c.sum(axis=1, keepdims=True))).max() <= REDUCE_TOL * 100
+        arr, order, roots = G.flatten([G.sin(x)], host_pointers=True)
+        buf = ctypes.create_string_buffer(1 << 16)
+        n = ctypes.c_size_t()
+        check(lib.ormi_b200_compile_source(arr, len(order), roots[0], buf, len(buf), ctypes.byref(n), None, 0, None))
+        assert b"cosf(val_LEAF_0) * 2.0f" in buf.value
+        assert lib.ormi_b200_set_lowering(int(G.OpEnum.MATMUL), b"$0") != 0          # only pointwise ops have one
+    finally:
+        check(lib.ormi_b200_set_lowering(int(G.OpEnum.SIN), None))
+    compare([build()], 2 * REDUCE_TOL)           # the stock sine again
