@@ -917,18 +917,33 @@ GeneratedKernel generate_generic_sum(const std::vector<int>& shape, const std::v
     for (size_t d = 0; d < shape.size(); ++d) (reduced[d] ? n_red : n_out) *= shape[d];
     std::ostringstream s;
     s << device_prelude();
-    s << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const float* __restrict__ in, float* __restrict__ out) {\n"
-      << "    const int o = blockIdx.x * 256 + threadIdx.x;\n    if (o >= " << n_out << ") return;\n    int base = 0;\n    {\n        int rem = o;\n";
+    // Few outputs over many inputs (a global or near-global sum of a transposed or expanded tensor): one BLOCK per
+    // output — its threads stride over the reduced coordinates, then a fixed-order tree — instead of one thread
+    // walking 10^8 elements on its own.  Many outputs: one thread each, as the inputs of neighbouring threads then sit
+    // side by side.
+    const bool block_per_output = n_out < 4096 && n_red >= 1024;
+    s << "extern \"C\" __global__ void __launch_bounds__(256) " << name << "(const float* __restrict__ in, float* __restrict__ out) {\n";
+    if (block_per_output) s << "    const int o = blockIdx.x;\n";
+    else s << "    const int o = blockIdx.x * 256 + threadIdx.x;\n    if (o >= " << n_out << ") return;\n";
+    s << "    int base = 0;\n    {\n        int rem = o;\n";
     for (size_t d = shape.size(); d-- > 0;) if (!reduced[d]) s << "        base += (rem % " << shape[d] << ") * " << strides[d] << "; rem /= " << shape[d] << ";\n";
-    s << "    }\n    float a = " << red_ident(is_max) << ";\n    for (int e = 0; e < " << n_red << "; ++e) {\n        int rem = e, off = base;\n";
+    s << "    }\n    float a = " << red_ident(is_max) << ";\n";
+    s << "    for (int e = " << (block_per_output ? "threadIdx.x" : "0") << "; e < " << n_red << "; e += " << (block_per_output ? 256 : 1) << ") {\n        int rem = e, off = base;\n";
     for (size_t d = shape.size(); d-- > 0;) if (reduced[d]) s << "        off += (rem % " << shape[d] << ") * " << strides[d] << "; rem /= " << shape[d] << ";\n";
-    s << "        a = " << red_comb(is_max, "a", "in[off]") << ";\n    }\n    out[o] = a;\n}\n";
-    g.step.grid = (int)((n_out + 255) / 256);
+    s << "        a = " << red_comb(is_max, "a", "in[off]") << ";\n    }\n";
+    if (block_per_output) {
+        s << "    __shared__ float sm[8];\n    a = " << red_warp(is_max) << "(a, 32);\n    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = a;\n    __syncthreads();\n"
+          << "    if (threadIdx.x == 0) { float t = " << red_ident(is_max) << "; for (int w = 0; w < 8; ++w) t = " << red_comb(is_max, "t", "sm[w]") << "; out[o] = t; }\n}\n";
+        g.step.grid = (int)n_out;
+    } else {
+        s << "    out[o] = a;\n}\n";
+        g.step.grid = (int)((n_out + 255) / 256);
+    }
     g.step.block = 256;
     g.step.name = name;
     g.step.source = s.str();
     g.step.key = std::to_string(fnv1a(g.step.source));
-    g.step.what = "generic_sum[out=" + std::to_string(n_out) + ",red=" + std::to_string(n_red) + "]";
+    g.step.what = std::string("generic_sum[out=") + std::to_string(n_out) + ",red=" + std::to_string(n_red) + (block_per_output ? ",block" : "") + "]";
     g.step.bytes_read = n_out * n_red * 4;
     g.step.bytes_written = n_out * 4;
     return g;

@@ -109,7 +109,14 @@ struct Scheduler {
             I.strides.assign(nd.strides, nd.strides + nd.ndim);
             I.sq = squeeze(I.shape);
             for (int s : I.shape) { if (s <= 0) return fail("empty or negative dimension"); I.numel *= s; }
-            if (I.numel >= (int64_t(1) << 31)) return fail("tensor with 2^31 or more elements");
+            // Generated kernels index with 32-bit ints.  A grid-stride loop steps past the end by up to one grid of
+            // vector accesses (at most 148 * 8 blocks * 256 threads * 4 elements = 2^21 * 0.58) before its bound check,
+            // and strided views are addressed by their extent, not their element count: both must stay below 2^31.
+            constexpr int64_t kIndexLimit = (int64_t(1) << 31) - (int64_t(1) << 22);
+            if (I.numel >= kIndexLimit) return fail("tensor with 2^31 or more elements (the limit is 2^31 - 2^22: index arithmetic is 32-bit)");
+            int64_t extent = 1;
+            for (size_t d = 0; d < I.shape.size(); ++d) extent += (int64_t)(I.shape[d] - 1) * (I.strides[d] < 0 ? -(int64_t)I.strides[d] : (int64_t)I.strides[d]);
+            if (extent >= kIndexLimit) return fail("tensor view that spans 2^31 or more elements (index arithmetic is 32-bit)");
             for (int p = 0; p < nd.n_parents; ++p)
                 if (nd.parents[p] < 0 || nd.parents[p] >= i) return fail("graph is not in topological order");
         }

@@ -234,6 +234,13 @@ def test_more_than_2_31_elements_is_rejected_with_a_message():
     assert "2^31" in RT.plan([G.add(big, big)])["error"]
     ok = G.Node(G.OpEnum.LEAF, data=G.Buffer((1 << 15, 1 << 15), host=np.zeros(1, np.float32)))     # 2^30: the largest power of two
     assert not RT.plan([G.add(ok, ok)])["error"]
+    # the last grid-stride step of a kernel may overshoot the end by a grid of vector accesses before its bound check:
+    # sizes within 2^22 of 2^31 are refused too, and so is a strided view whose EXTENT (not its element count) gets there
+    near = G.Node(G.OpEnum.LEAF, data=G.Buffer(((1 << 31) - 1024,), host=np.zeros(1, np.float32)))
+    assert "2^31" in RT.plan([G.neg(near)])["error"]
+    wide = G.Node(G.OpEnum.LEAF, data=G.Buffer((1 << 16, 1 << 15), host=np.zeros(1, np.float32)))
+    wide.shape, wide.strides = [1 << 10, 1 << 10], [1 << 21, 1]                              # 2^20 elements spread over 2^31
+    assert "spans 2^31" in RT.plan([G.sum_(G.transpose(wide, [1, 0]), [0], False)])["error"]
 
 
 @pytest.mark.parametrize("shape", [(1, 1), (1, 7), (7, 1), (3, 33), (33, 3), (2, 1025), (129, 5)])
@@ -357,3 +364,15 @@ def test_registered_lowering_replaces_the_builtin_expression():
     finally:
         check(lib.ormi_b200_set_lowering(int(G.OpEnum.SIN), None))
     compare([build()], 2 * REDUCE_TOL)           # the stock sine again
+
+
+def test_sum_over_a_view_with_few_outputs_uses_a_block_per_output():
+    """A global (or near-global) sum whose operand is a view cannot take the fused templates; with few outputs each one
+    gets a block whose threads stride over the reduced coordinates, not one thread walking them all."""
+    a = W.normal(0, (64, 48))
+    t = G.transpose(G.leaf(a), [1, 0])
+    outs, plan = E.realize([G.sum_(t, [], False), G.sum_(t, [0], False)])
+    whats = [s["what"] for s in plan["steps"]]
+    assert any("generic_sum[out=1,red=3072,block]" in w for w in whats), whats
+    assert abs(float(outs[0]) - a.sum(dtype=np.float64)) <= REDUCE_TOL * np.abs(a).sum()
+    assert np.abs(outs[1] - a.sum(axis=1, dtype=np.float64)).max() <= REDUCE_TOL * np.abs(a).sum(axis=1).max()
