@@ -24,7 +24,7 @@ _BUILD_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "s
 
 
 def _load_backend():
-    hits = sorted(glob.glob(os.path.join(_BUILD_DIR, "ormi_backend*.so")))
+    hits = sorted(h for h in glob.glob(os.path.join(_BUILD_DIR, "ormi_backend*.so")) if "ormi_backend_extra" not in h)
     if not hits:
         raise ImportError("ormi_backend is not built: run `make -C ormi_b200/csrc/seams REF=<ormi checkout>` "
                           "(needs the ormi-core sources and pybind11)")
@@ -35,6 +35,28 @@ def _load_backend():
 
 
 backend = _load_backend()
+
+
+def _load_extra():
+    """The additive bindings (ormi_b200/csrc/seams/b200_bindings_extra.cpp): log / pow as functions, device selection."""
+    hits = sorted(glob.glob(os.path.join(_BUILD_DIR, "ormi_backend_extra*.so")))
+    if not hits:
+        return None
+    spec = importlib.util.spec_from_file_location("ormi_backend_extra", hits[0])
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+extra = _load_extra()
+
+
+def set_device(index: int) -> None:
+    """The GPU that later ``device="cuda"`` tensors are placed on (and their graphs run on).  One process per GPU calls
+    it once with its local rank; ormi-core itself always uses device 0.  Raises when there is no such device."""
+    if extra is None:
+        raise RuntimeError("ormi_backend_extra is not built")
+    extra.set_device(int(index))
 
 
 def _engine():
@@ -159,7 +181,7 @@ class Tensor:
     def exp(self): return self._wrap(backend.exp(self._node))
     def sin(self): return self._wrap(backend.sin(self._node))
     def cos(self): return self._wrap(backend.cos(self._node))
-    def log(self): return self._unary(OpEnum.LOG)
+    def log(self): return self._wrap(extra.log(self._node)) if extra is not None else self._unary(OpEnum.LOG)
 
     def sum(self, axes: Sequence[int] = (), keepdims: bool = False) -> "Tensor":
         """Sum over ``axes`` (all axes when empty), as ``ormi::ops::sum``."""
