@@ -223,3 +223,81 @@ def test_matmul_mode_and_fusion_knobs_on_cuda():
         T.set_option("fusion", "on")
     with pytest.raises(RuntimeError):
         T.set_option("matmul", "fp64")
+
+
+@pytest.mark.parametrize("dev", DEVICES)
+def test_known_answers_of_the_reference_python_tests(dev):
+    """The eight cases of ormi-core/tests/test_tensor.py:5-81 with their own numbers (that file is parametrised over
+    "cpu" and "cuda" by ormi-core/tests/conftest.py:3-5; it cannot be read on a machine without the ormi checkout, so its
+    known answers are restated here against the same extension module)."""
+    t = Tensor([1.0, 2.0, 3.0], device=dev, requires_grad=True)                       # initialization
+    assert t.shape == (3,) and t.requires_grad is True and t.device.type.name.lower() == dev
+    np.testing.assert_allclose(t.numpy(), [1.0, 2.0, 3.0])
+    a, b = Tensor([4.0, 6.0], device=dev), Tensor([2.0, 3.0], device=dev)               # binary operations
+    for got, want in (((a + b), [6.0, 9.0]), ((a - b), [2.0, 3.0]), ((a * b), [8.0, 18.0]), ((a / b), [2.0, 2.0]),
+                      ((-a), [-4.0, -6.0]), ((a ** 2.0), [16.0, 36.0])):
+        np.testing.assert_allclose(got.numpy(), want)
+    c = Tensor([2.0, 4.0], device=dev)                                                  # reverse operations
+    for got, want in (((10.0 + c), [12.0, 14.0]), ((10.0 - c), [8.0, 6.0]), ((10.0 * c), [20.0, 40.0]), ((10.0 / c), [5.0, 2.5])):
+        np.testing.assert_allclose(got.numpy(), want)
+    m = Tensor([[1.0, 2.0], [3.0, 4.0]], device=dev) @ Tensor([[2.0, 0.0], [0.0, 2.0]], device=dev)   # matmul
+    assert m.shape == (2, 2)
+    np.testing.assert_allclose(m.numpy(), [[2.0, 4.0], [6.0, 8.0]])
+    with pytest.raises(TypeError):                                                        # matmul type enforcement
+        _ = Tensor([[1.0, 2.0]], device=dev) @ 2.0
+    v = Tensor([[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]], device=dev)                           # view operations
+    r = v.reshape((3, 2))
+    assert r.shape == (3, 2)
+    np.testing.assert_allclose(r.numpy(), [[1.0, 2.0], [3.0, 4.0], [5.0, 6.0]])
+    tr = v.transpose()
+    assert tr.shape == (3, 2)
+    np.testing.assert_allclose(tr.numpy(), [[1.0, 4.0], [2.0, 5.0], [3.0, 6.0]])
+    p = Tensor([2.0, 3.0], device=dev, requires_grad=True)                               # autograd graph: z = p q + p
+    q = Tensor([4.0, 5.0], device=dev, requires_grad=True)
+    (p * q + p).backward()
+    np.testing.assert_allclose(p.grad.numpy(), [5.0, 6.0])
+    np.testing.assert_allclose(q.grad.numpy(), [2.0, 3.0])
+    z = Tensor([1.0], device=dev, requires_grad=True)                                    # zero_grad
+    (z * 2.0).backward()
+    assert z.grad is not None
+    z.zero_grad()
+    assert z.grad is None
+
+
+@pytest.mark.parametrize("dev", DEVICES)
+def test_additive_log_and_pow_function_bindings(dev):
+    """ormi-core's binding file leaves log and pow out (csrc/bindings/bind_pointwise.cpp:16-25) although the ops exist;
+    the additive module binds them as functions next to add, sub, ... of the stock module."""
+    from ormi_b200 import tensor as T
+    if T.extra is None:
+        pytest.skip("ormi_backend_extra not built")
+    x = Tensor([1.0, 2.0, 4.0], device=dev)
+    e = Tensor([0.5, 2.0, 3.0], device=dev)
+    np.testing.assert_allclose(x._wrap(T.extra.log(x._node)).numpy(), np.log([1.0, 2.0, 4.0]), rtol=1e-6)
+    np.testing.assert_allclose(x._wrap(T.extra.pow(x._node, e._node)).numpy(), [1.0, 4.0, 64.0], rtol=1e-6)
+    np.testing.assert_allclose(x.log().numpy(), np.log([1.0, 2.0, 4.0]), rtol=1e-6)
+
+
+@pytest.mark.gpu
+def test_tensors_follow_the_active_device():
+    """One backend context per GPU behind the module: after set_device(1) new CUDA tensors live on GPU 1 and their graphs
+    run there; tensors of two devices do not mix."""
+    import torch
+    from ormi_b200 import tensor as T
+    if torch.cuda.device_count() < 2 or T.extra is None:
+        pytest.skip("needs two GPUs and the additive module")
+    a0 = Tensor(np.arange(8, dtype=np.float32), device="cuda")
+    try:
+        T.set_device(1)
+        assert T.extra.active_device() == 1
+        before = T.extra.counter("launches")
+        a1 = Tensor(np.arange(8, dtype=np.float32), device="cuda")
+        np.testing.assert_allclose((a1 * a1 + 1.0).numpy(), np.arange(8.0) ** 2 + 1.0)
+        assert T.extra.counter("launches") > before            # the counter of GPU 1's context moved
+        with pytest.raises(RuntimeError, match="cuda:0 and cuda:1|cuda:1 and cuda:0"):
+            (a0 + a1).numpy()
+        with pytest.raises(RuntimeError):
+            T.set_device(64)
+    finally:
+        T.set_device(0)
+    np.testing.assert_allclose((a0 + a0).numpy(), 2 * np.arange(8.0))
