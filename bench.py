@@ -413,6 +413,34 @@ def mlp_sharded_vs_single(dev, W, rank, world, dist, d_in=2048, hidden=8192, row
     return err
 
 
+def run_mlp_sharded(args, rank, local_rank, world):
+    """configs[4] alone, under torch.distributed.run: the global batch of --rows x world rows split over the ranks."""
+    import torch
+    import torch.distributed as dist
+    from ormi_b200 import workloads as W
+    from ormi_b200.runtime import Device
+    from ormi_b200.train_step import init_comm
+    torch.cuda.set_device(local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = Device(local_rank)
+    for item in filter(None, args.set.split(",")):
+        k, v = item.split("=")
+        dev.set_option(k, v)
+
+    def bcast(payload):
+        obj = [payload]
+        dist.broadcast_object_list(obj, src=0)
+        return obj[0]
+    if world > 1:
+        init_comm(dev, rank, world, bcast)
+    res = mlp_steps_per_s(dev, torch, W, args.rows, 2048, 8192, "bf16", args.steps, rank, world, dist if world > 1 else None, args.rows * world)
+    if rank == 0:
+        emit(dict(res, only=args.only, rows_per_rank=args.rows, world=world, options=args.set))
+    dist.destroy_process_group()
+    dev.close()
+
+
 def run_only(args):
     """One graph, a few launches, nothing else: the small case profilers attach to."""
     import torch
@@ -470,11 +498,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, choices=["softmax", "softmax_stable", "layernorm", "rowsum", "gemm_bf16", "gemm_fp32", "gemm_tf32", "gemm_3xtf32", "mlp_bf16", "mlp_fp32"],
+    ap.add_argument("--only", default=None, choices=["softmax", "softmax_stable", "layernorm", "rowsum", "gemm_bf16", "gemm_fp32", "gemm_tf32", "gemm_3xtf32", "mlp_bf16", "mlp_fp32", "mlp_sharded"],
                     help="profiling aid: run just this graph --steps times on --rows rows and exit")
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--no-extras", action="store_true", help="skip the matmul sweep and the MLP training steps")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--set", default="", help="with --only mlp_sharded: backend options for the run, key=value,key=value")
     args = ap.parse_args()
     # Libraries (NCCL's version banner, for one) print to stdout; the contract is ONE JSON line there.  Everything but
     # that line goes to stderr.
@@ -489,6 +518,8 @@ def main():
         run_reference_arm(args, rank)
         return
     warmup = max(3, args.warmup)
+    if args.only == "mlp_sharded":
+        return run_mlp_sharded(args, rank, local_rank, world)
     if args.only:
         return run_only(args)
 

@@ -1,10 +1,10 @@
 /*
- * TEST INFRASTRUCTURE (oracle build only; nothing in the product links this file).
- *
- * cblas_sgemm for the reference CPU backend compiled under oracle/_ref.  The reference links an
- * un-pinned system OpenBLAS (ormi-core/CMakeLists.txt:31-36).  This shim forwards to the OpenBLAS
- * 0.3.15 shared object that the image carries inside a Python wheel when it can be dlopen'ed
- * (override the path with ORMI_ORACLE_OPENBLAS), and otherwise computes the same definition
+ * cblas_sgemm for the reference's CPU backend wherever this repository compiles it: the checker under oracle/_ref
+ * (test infrastructure) and the CPU half of ormi-core inside the engine library of ormi_b200/csrc/seams (ormi-core's
+ * DeviceEnum::CPU path; the B200 path never calls it).  The reference links an un-pinned system OpenBLAS
+ * (ormi-core/CMakeLists.txt:31-36).  This shim forwards to an OpenBLAS shared object when one can be dlopen'ed — the
+ * path in ORMI_ORACLE_OPENBLAS (the Python loaders set it to the library inside the running interpreter's scipy or
+ * opencv wheel), else the distribution's libopenblas — and otherwise computes the same definition
  *      C = alpha * op(A) * op(B) + beta * C        (fp32, accumulation over k in ascending order)
  * with plain loops.  oracle_cblas_backend() tells which one is active.
  */
@@ -45,10 +45,9 @@ static void load_once(void) {
     if (getenv("ORMI_ORACLE_NO_OPENBLAS")) return;
     try_load(getenv("ORMI_ORACLE_OPENBLAS"));
     const char* patterns[] = {
-        "/opt/prime-rl/.venv/lib/python3*/site-packages/opencv_python_headless.libs/libopenblas*.so",
         "/usr/lib/x86_64-linux-gnu/libopenblas.so.0",
         "/usr/lib/x86_64-linux-gnu/openblas-pthread/libopenblas.so.0",
-        "/opt/prime-rl/.venv/lib/python3*/site-packages/scipy.libs/libscipy_openblas*.so",
+        "/usr/lib64/libopenblas.so.0",
         0};
     for (int i = 0; patterns[i] && !g_sgemm; ++i) {
         glob_t g;

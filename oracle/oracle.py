@@ -27,7 +27,10 @@ _port = None
 def build(verbose=False):
     """Runs the Makefile: always builds the restatement, and the reference library when the reference
     checkout is present on this machine."""
-    out = subprocess.run(["make", "-C", _HERE], capture_output=True, text=True)
+    cmd = ["make", "-C", _HERE]
+    if os.environ.get("ORMI_REFERENCE"):
+        cmd.append("REF=" + os.environ["ORMI_REFERENCE"])
+    out = subprocess.run(cmd, capture_output=True, text=True)
     if out.returncode != 0:
         raise RuntimeError("oracle build failed:\n" + out.stdout + out.stderr)
     if verbose:
@@ -38,11 +41,27 @@ def ref_available() -> bool:
     return os.path.exists(REF_LIB)
 
 
+def locate_openblas() -> None:
+    """Points the cblas shim (ORMI_ORACLE_OPENBLAS) at an OpenBLAS inside the running interpreter's wheels — scipy's or
+    opencv's — unless the caller already chose one.  The reference's own dependency is an un-pinned system OpenBLAS."""
+    if os.environ.get("ORMI_ORACLE_OPENBLAS"):
+        return
+    import glob
+    import sysconfig
+    site = sysconfig.get_paths()["purelib"]
+    for pattern in ("scipy.libs/libscipy_openblas*.so", "opencv_python_headless.libs/libopenblas*.so", "numpy.libs/libscipy_openblas*.so"):
+        hits = sorted(glob.glob(os.path.join(site, pattern)))
+        if hits:
+            os.environ["ORMI_ORACLE_OPENBLAS"] = hits[0]
+            return
+
+
 def _load_ref():
     global _ref
     if _ref is None:
         if not ref_available():
             raise RuntimeError(f"{REF_LIB} is missing: run `make -C oracle` on a machine with the reference checkout")
+        locate_openblas()
         _ref = ctypes.CDLL(REF_LIB, mode=os.RTLD_LOCAL | os.RTLD_NOW)
         _ref.oracle_ref_last_error.restype = ctypes.c_char_p
         _ref.oracle_ref_blas.restype = ctypes.c_char_p

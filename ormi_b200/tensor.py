@@ -28,6 +28,15 @@ def _load_backend():
     if not hits:
         raise ImportError("ormi_backend is not built: run `make -C ormi_b200/csrc/seams REF=<ormi checkout>` "
                           "(needs the ormi-core sources and pybind11)")
+    # the CPU device's matmul is OpenBLAS' cblas_sgemm, looked up at first use: point the shim at the interpreter's own copy
+    if not os.environ.get("ORMI_ORACLE_OPENBLAS"):
+        import sysconfig
+        site = sysconfig.get_paths()["purelib"]
+        for pattern in ("scipy.libs/libscipy_openblas*.so", "opencv_python_headless.libs/libopenblas*.so"):
+            found = sorted(glob.glob(os.path.join(site, pattern)))
+            if found:
+                os.environ["ORMI_ORACLE_OPENBLAS"] = found[0]
+                break
     spec = importlib.util.spec_from_file_location("ormi_backend", hits[0])
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)

@@ -19,7 +19,8 @@ except ImportError as e:          # a checkout without the ormi-core sources can
     pytest.skip(str(e), allow_module_level=True)
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.environ.get("ORMI_REFERENCE", "/root/reference")      # the ormi checkout, where there is one
+REF = os.environ.get("ORMI_REFERENCE") or __import__("re").search(      # the ormi checkout, where there is one: the Makefile's default
+    r"^REF\s*\?=\s*(\S+)", open(os.path.join(ROOT, "oracle", "Makefile")).read(), __import__("re").M).group(1)
 DEVICES = ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)]
 PW_TOL, REDUCE_TOL = 1e-6, 1e-5
 
