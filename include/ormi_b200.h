@@ -42,6 +42,11 @@ enum ormi_b200_op {
 #define ORMI_NODE_KEEP   1u  /* somebody outside the graph holds this node: it must own a buffer after realize */
 #define ORMI_NODE_TWIN16 8u  /* "bf16" matmul arithmetic: a later matmul will read this root (a weight an update produces): write
                               * its bf16 copy along with it, so that no conversion pass is needed then */
+#define ORMI_NODE_BF16   16u /* "bf16" matmul arithmetic, first-class bf16 tensors (the reference has the DType enum and nothing behind it,
+                              * ormi-core/csrc/core/dtype.h:4-8, core/memory.cpp:88).  On an un-realized root or KEEP node: materialize
+                              * it as bf16 ONLY — `data` comes back as a contiguous bf16 matrix of data_bytes = 2 * elements, with this
+                              * flag set.  On a realized node: `data` is such a matrix.  A bf16 tensor can only be an operand of a
+                              * matmul that runs on the tensor cores (2-D, last dimension a multiple of 8); anything else is refused. */
 /* Node flags (out, set by ormi_b200_realize). */
 #define ORMI_NODE_OWNED  2u  /* `data` is a fresh pool buffer now owned by the caller (free with ormi_b200_free) */
 #define ORMI_NODE_ALIAS  4u  /* `data` aliases the buffer of the node's view base (ormi-core/csrc/backend/runtime.cpp:20-23) */

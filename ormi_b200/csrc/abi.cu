@@ -68,7 +68,6 @@ int ormi_b200_shutdown(ormi_b200_ctx* ctx) {
         for (auto& kv : ctx->kernel_cache) if (kv.second.module) ctx->drv.ModuleUnload(kv.second.module);
         for (auto& kv : ctx->shadows) cudaFree(kv.second.ptr);
         for (auto& kv : ctx->free_blocks) for (void* p : kv.second) cudaFree(p);
-        for (int i = 0; i < 2; ++i) if (ctx->stage[i]) cudaFree(ctx->stage[i]);
         if (ctx->gemm_err) cudaFree(ctx->gemm_err);
         if (ctx->up_stream) { cudaStreamSynchronize(ctx->up_stream); cudaStreamSynchronize(ctx->down_stream); cudaStreamDestroy(ctx->up_stream); cudaStreamDestroy(ctx->down_stream); cudaEventDestroy(ctx->copy_event); }
         cudaStreamDestroy(ctx->stream);

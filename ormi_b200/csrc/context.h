@@ -104,9 +104,6 @@ struct ormi_b200_ctx {
     std::unordered_map<const void*, ormi_b200::Shadow16> shadows;
     std::unordered_map<std::string, ormi_b200::TcKernel> tc_kernels;   // compiled variants of the tensor-core GEMM
     int tc_cta_group = 2;             // CTAs per tcgen05.mma of the bf16 GEMM: 2 = a pair of SMs per 256 x 256 tile
-    // operand staging of the tf32 / 3xTF32 GEMM path (grown on demand, reused across calls)
-    void* stage[2] = {nullptr, nullptr};
-    size_t stage_bytes[2] = {0, 0};
     // kErrorWords ints: word 0 is the error word, word kTileCounterWord (its own 128-byte line) the GEMM's tile counter
     int* gemm_err = nullptr;          // device word: non-zero when a bounded wait inside the tensor-core GEMM ran out
     bool gemm_err_pending = false;    // a kernel with bounded waits was launched since the word was last read

@@ -49,6 +49,7 @@ struct Info {
     int k = -1;                    // split; -1: any
     bool row_cls = false;          // value per row (row sum, or pointwise work on row sums)
     bool in_M = false;             // materialized
+    bool bf16_in = false;          // realized input whose buffer holds bf16 (ORMI_NODE_BF16): a matmul operand only
     int step = -1;                 // step that produces it
 };
 
@@ -134,7 +135,7 @@ struct Scheduler {
             Info& I = info[i];
             if (!I.needed) continue;
             const auto& nd = nodes[i];
-            if (nd.data) { I.kind = K_INPUT; continue; }
+            if (nd.data) { I.kind = K_INPUT; I.bf16_in = (nd.flags & ORMI_NODE_BF16) != 0; continue; }
             if (nd.op == ORMI_OP_LEAF || nd.op == ORMI_OP_CONST) return fail("leaf without data");
             if (is_view_op(nd.op)) {
                 if (nd.n_parents != 1) return fail("view op needs one parent");
@@ -302,6 +303,7 @@ struct Scheduler {
         const Info& O = info[o];
         size_t nd = w.D.size();
         if (O.kind == K_INPUT) {
+            if (O.bf16_in) fail("a bf16 tensor can only be an operand of a tensor-core matmul");
             std::vector<int64_t> st(nd, 0);
             if (!(O.shape.empty() || nodes[o].data_bytes == 4)) st = strides_over_domain(dm, O.strides, nd);
             return KRef{KRef::LOAD, add_load(w, o, st)};
@@ -309,6 +311,7 @@ struct Scheduler {
         if (O.kind == K_VIEW) {
             int b = O.base;
             const Info& B = info[b];
+            if (B.kind == K_INPUT && B.bf16_in) fail("a bf16 tensor can only be an operand of a tensor-core matmul");
             if (B.kind == K_INPUT) {
                 std::vector<int64_t> st(nd, 0);
                 if (nodes[b].data_bytes != 4) st = strides_over_domain(dm, O.strides, nd);
@@ -538,10 +541,15 @@ Plan Scheduler::run(const int* roots, int n_roots) {
     }
 
     // ---- 4b. matmuls on the tensor-core kernel: which qualify, what follows them, who writes their bf16 operands
-    std::vector<bool> need_twin(n, false), drop_f32(n, false);
+    std::vector<bool> need_twin(n, false), drop_f32(n, false), bf16_out(n, false);
     std::vector<std::pair<int, int>> twin_shape(n, {0, 0});
     std::vector<std::vector<int>> consumers(n);          // materialized node -> materialized nodes whose step reads it
     for (int x = 0; x < n; ++x) if (info[x].in_M) for (const Dep& d : deps[x]) consumers[d.node].push_back(x);
+    for (int x = 0; x < n; ++x)
+        if (info[x].needed && (nodes[x].flags & ORMI_NODE_BF16) && !(opt.bf16_matmul && opt.fusion)) {
+            plan.error = "bf16 tensors need the \"bf16\" matmul arithmetic (ormi_b200_set_option \"matmul\")";
+            return plan;
+        }
     if (opt.bf16_matmul && opt.fusion) {
         for (auto& S : steps) if (S.type == StepNode::GEMM) S.tc = tc_eligible(S.outputs[0]);
         // (a) epilogues: a flat kernel over the [M, N] domain of a qualifying matmul that reads the product moves into
@@ -610,6 +618,19 @@ Plan Scheduler::run(const int* roots, int n_roots) {
             const Kind pk = info[x].kind;
             if ((pk == K_MATMUL && steps[info[x].step].tc) || ((pk == K_PW || pk == K_IDSUM) && !info[x].row_cls)) want_twin(x, info[x].sq[0], info[x].sq[1]);
         }
+        // a root the caller wants as bf16 ONLY: the twin is the result, the fp32 form is never written
+        for (int x = 0; x < n; ++x) {
+            if (!info[x].in_M || !handed[x] || !(nodes[x].flags & ORMI_NODE_BF16)) continue;
+            const Kind pk = info[x].kind;
+            const bool producer_ok = (pk == K_MATMUL && steps[info[x].step].tc) || ((pk == K_PW || pk == K_IDSUM) && !info[x].row_cls);
+            if (!producer_ok || info[x].sq.size() != 2 || info[x].sq[1] % 8 != 0 || info[x].sq != info[x].shape) {
+                plan.error = "a node can be materialized as bf16 only when it is a 2-D pointwise result or tensor-core product whose last dimension is a multiple of 8";
+                return plan;
+            }
+            want_twin(x, info[x].sq[0], info[x].sq[1]);
+            bf16_out[x] = true;
+            drop_f32[x] = true;
+        }
         // (c) a pointwise result nobody but tensor-core matmuls reads is not written as fp32 at all
         for (int x = 0; x < n; ++x) {
             if (!need_twin[x] || handed[x] || info[x].kind == K_MATMUL) continue;
@@ -673,6 +694,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
         for (int t : steps[s].succ) if (--indeg[t] == 0) ready.insert({steps[t].outputs[0], t});
     }
     if (order.size() != live_steps) { plan.error = "internal: cyclic kernel graph"; return plan; }
+    if (!error.empty()) { plan.error = error; return plan; }
 
     int kernel_serial = 0;
     for (int s : order) {
@@ -738,13 +760,21 @@ Plan Scheduler::run(const int* roots, int n_roots) {
                 }
             }
             g.tc = S.tc;
+            if (!S.tc) for (int p = 0; p < 2; ++p) if (info[srcs[p]].kind == K_INPUT && info[srcs[p]].bf16_in) {
+                plan.error = "a bf16 tensor can only be an operand of a tensor-core matmul (this one does not qualify: see the shape rules)";
+                return plan;
+            }
             if (S.tc) {
-                for (int p = 0; p < 2; ++p) {      // operands some earlier step of this plan writes as bf16
+                for (int p = 0; p < 2; ++p) {      // operands some earlier step of this plan writes as bf16, or the caller holds as bf16
                     OperandView v = matmul_operand(nd.parents[p], false);
                     if (info[v.src].kind != K_INPUT && need_twin[v.src] && v.dense) (p == 0 ? g.a16 : g.b16) = twin_for(v.src);
+                    if (info[v.src].kind == K_INPUT && info[v.src].bf16_in) {
+                        if (!v.dense) { plan.error = "a bf16 matmul operand must be the whole contiguous matrix (or its transpose)"; return plan; }
+                        (p == 0 ? g.a16 : g.b16) = bufs[p];
+                    }
                 }
                 const bool twin_c = need_twin[m];
-                bool c_read = handed[m] || (S.epi_outputs.empty() && !twin_c);
+                bool c_read = (handed[m] && !bf16_out[m]) || (S.epi_outputs.empty() && !twin_c);
                 for (int y : consumers[m]) if (info[y].step != s) c_read = true;
                 g.store_c = c_read;
                 if (!c_read) drop_f32[m] = true;
@@ -812,6 +842,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
             int m = S.outputs[0];
             int src; std::vector<int> sh, st;
             operand_view(nodes[m].parents[0], src, sh, st, false);
+            if (info[src].kind == K_INPUT && info[src].bf16_in) { plan.error = "a bf16 tensor can only be an operand of a tensor-core matmul"; return plan; }
             std::vector<bool> red(sh.size(), nodes[m].n_axes == 0);
             for (int a = 0; a < nodes[m].n_axes; ++a) red[nodes[m].axes[a]] = true;
             if (info[src].kind == K_INPUT && nodes[src].data_bytes == 4) std::fill(st.begin(), st.end(), 0);
@@ -892,6 +923,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
     for (int i = 0; i < n; ++i) {
         if (!info[i].needed || info[i].kind == K_INPUT) continue;
         if (info[i].in_M && !drop_f32[i]) plan.results.push_back(NodeResult{i, buffer_for(i), false});
+        if (info[i].in_M && bf16_out[i]) { NodeResult r{i, twin_for(i), false}; r.bf16 = true; plan.results.push_back(r); }
     }
     auto alias_result = [&](int i) {
         if (info[i].kind != K_VIEW) return;
@@ -900,6 +932,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
     };
     for (int r = 0; r < n_roots; ++r) alias_result(roots[r]);
     for (int i = 0; i < n; ++i) if (info[i].needed && (nodes[i].flags & ORMI_NODE_KEEP)) alias_result(i);
+    if (!error.empty() && plan.error.empty()) plan.error = error;
     return plan;
 }
 
@@ -963,7 +996,7 @@ std::string plan_to_json(const Plan& plan) {
     o << "], \"results\": [";
     for (size_t i = 0; i < plan.results.size(); ++i) {
         const auto& r = plan.results[i];
-        o << (i ? ", " : "") << "{\"node\": " << r.node << ", \"buffer\": " << r.buffer << ", \"alias\": " << (r.alias ? "true" : "false") << "}";
+        o << (i ? ", " : "") << "{\"node\": " << r.node << ", \"buffer\": " << r.buffer << ", \"alias\": " << (r.alias ? "true" : "false") << ", \"bf16\": " << (r.bf16 ? "true" : "false") << "}";
     }
     o << "]}";
     return o.str();

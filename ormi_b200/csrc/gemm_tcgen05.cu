@@ -450,14 +450,15 @@ void convert(ormi_b200_ctx* ctx, const CvtJob& a, const CvtJob& b, int parts = 0
     ctx->counters["launches"]++;
 }
 
-void* stage_buffer(ormi_b200_ctx* ctx, int which, size_t bytes) {
-    if (ctx->stage_bytes[which] < bytes) {
-        if (ctx->stage[which]) { ORMI_CUDA(cudaStreamSynchronize(ctx->stream)); ORMI_CUDA(cudaFree(ctx->stage[which])); ctx->stage[which] = nullptr; }
-        ORMI_CUDA(cudaMalloc(&ctx->stage[which], bytes));
-        ctx->stage_bytes[which] = bytes;
-    }
-    return ctx->stage[which];
-}
+// Staging copies of one GEMM call: blocks of the context's pool, taken before the conversion pass and given back as soon
+// as the GEMM is queued (the pool is ordered by the stream, so the next call may get the same blocks) — nothing here
+// synchronises the stream or calls cudaFree in the middle of a step.
+struct Staging {
+    ormi_b200_ctx* ctx; void* p[2] = {nullptr, nullptr}; size_t n[2] = {0, 0};
+    explicit Staging(ormi_b200_ctx* c) : ctx(c) {}
+    void* get(int which, size_t bytes) { p[which] = pool_alloc(ctx, bytes); n[which] = bytes; return p[which]; }
+    ~Staging() { for (int i = 0; i < 2; ++i) if (p[i]) pool_free(ctx, p[i], n[i]); }
+};
 
 void make_map(ormi_b200_ctx* ctx, CUtensorMap* map, void* ptr, int rows, int Kp, int box_rows, bool fp32 = false) {
     cuuint64_t dims[2] = {(cuuint64_t)Kp, (cuuint64_t)rows};
@@ -479,8 +480,9 @@ void gemm_bf16(ormi_b200_ctx* ctx, const GemmArgs& g) {
     // operands whose rows are whole 16-byte pieces of bf16 go to the run-time compiled kernel, in their own layout
     if (ctx->tc_cta_group != 0 && gemm_tc_supported(g)) { gemm_tc_from_fp32(ctx, g); return; }
     const int Kp = (g.K + BK - 1) / BK * BK;
-    __nv_bfloat16* a16 = (__nv_bfloat16*)stage_buffer(ctx, 0, (size_t)g.M * Kp * 2);
-    __nv_bfloat16* b16 = (__nv_bfloat16*)stage_buffer(ctx, 1, (size_t)g.N * Kp * 2);
+    Staging staging(ctx);
+    __nv_bfloat16* a16 = (__nv_bfloat16*)staging.get(0, (size_t)g.M * Kp * 2);
+    __nv_bfloat16* b16 = (__nv_bfloat16*)staging.get(1, (size_t)g.N * Kp * 2);
     // A(m,k) = A[m*lda + k] (or A[k*lda + m] when stored transposed); B(k,n) = B[k*ldb + n] (or B[n*ldb + k])
     convert(ctx, cvt_job(g.A, g.trans_a ? 1 : g.lda, g.trans_a ? g.lda : 1, g.M, g.K, Kp, a16),
             cvt_job(g.B, g.trans_b ? g.ldb : 1, g.trans_b ? 1 : g.ldb, g.N, g.K, Kp, b16));
@@ -518,8 +520,9 @@ void gemm_tf32(ormi_b200_ctx* ctx, const GemmArgs& g, int parts) {
     const int KB = BK / 2;                                   // 32 fp32 words per stage row
     const int Kp = (g.K + KB - 1) / KB * KB;
     const size_t ld = (size_t)Kp * parts;
-    float* a32 = (float*)stage_buffer(ctx, 0, (size_t)g.M * ld * 4);
-    float* b32 = (float*)stage_buffer(ctx, 1, (size_t)g.N * ld * 4);
+    Staging staging(ctx);
+    float* a32 = (float*)staging.get(0, (size_t)g.M * ld * 4);
+    float* b32 = (float*)staging.get(1, (size_t)g.N * ld * 4);
     convert(ctx, cvt_job(g.A, g.trans_a ? 1 : g.lda, g.trans_a ? g.lda : 1, g.M, g.K, Kp, a32, 0),
             cvt_job(g.B, g.trans_b ? g.ldb : 1, g.trans_b ? 1 : g.ldb, g.N, g.K, Kp, b32, 1), parts);
     CUtensorMap map_a, map_b;

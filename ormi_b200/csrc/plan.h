@@ -70,6 +70,7 @@ struct NodeResult {
     int node;
     int buffer;     // plan buffer id holding the node's value
     bool alias;     // view: shares the buffer of its base
+    bool bf16 = false;   // the buffer is the node's bf16-only form (ORMI_NODE_BF16)
 };
 
 struct Plan {

@@ -225,7 +225,7 @@ static std::string graph_key(const ormi_b200_ctx* ctx, const ormi_b200_node* nod
         for (int d = 0; d < nd.ndim; ++d) { mix((uint64_t)(uint32_t)nd.shape[d]); mix((uint64_t)(uint32_t)nd.strides[d]); }
         mix((uint64_t)nd.n_axes);
         for (int a = 0; a < nd.n_axes; ++a) mix((uint64_t)nd.axes[a]);
-        mix((uint64_t)nd.keepdims); mix((uint64_t)(nd.flags & (ORMI_NODE_KEEP | ORMI_NODE_TWIN16)));
+        mix((uint64_t)nd.keepdims); mix((uint64_t)(nd.flags & (ORMI_NODE_KEEP | ORMI_NODE_TWIN16 | ORMI_NODE_BF16)));
         mix(nd.data ? (nd.data_bytes == 4 ? 2 : 1) : 0);
     }
     mix(0xffffffffu);
@@ -342,6 +342,7 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
         ormi_b200_node& nd = nodes[r.node];
         nd.data = bufs[r.buffer];
         nd.data_bytes = plan.buffers[r.buffer].bytes;
+        if (r.bf16) nd.flags |= ORMI_NODE_BF16; else nd.flags &= ~ORMI_NODE_BF16;
         if (r.alias) nd.flags |= ORMI_NODE_ALIAS;
         else if (handed[r.buffer]) nd.flags |= ORMI_NODE_ALIAS;   // caller-owned target
         else { nd.flags |= ORMI_NODE_OWNED; handed[r.buffer] = true; }

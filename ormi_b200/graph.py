@@ -63,6 +63,7 @@ NODE_KEEP = 1
 NODE_OWNED = 2
 NODE_ALIAS = 4
 NODE_TWIN16 = 8           # in: also write this root's bf16 copy ("bf16" matmul arithmetic; a later matmul reads it)
+NODE_BF16 = 16            # in: materialize this root as bf16 only / this realized node's buffer holds bf16; out: the buffer is bf16
 NODE_REQUIRES_GRAD = 0x100  # only read by the oracle driver
 
 
@@ -139,7 +140,7 @@ class Buffer:
 class Node:
     """Mirror of ormi::Node (ormi-core/csrc/core/node.h:12-37)."""
     __slots__ = ("op", "parents", "data", "grad", "requires_grad", "shape", "strides",
-                 "axes", "keepdims", "keep", "twin16", "name", "__weakref__")
+                 "axes", "keepdims", "keep", "twin16", "bf16", "name", "__weakref__")
 
     def __init__(self, op, parents=(), *, data: Buffer | None = None, requires_grad=False,
                  axes: Sequence[int] = (), keepdims=False, shape: Sequence[int] | None = None):
@@ -151,6 +152,7 @@ class Node:
         self.keepdims = bool(keepdims)
         self.keep = False
         self.twin16 = False
+        self.bf16 = False          # a matmul operand kept as bf16 only (ORMI_NODE_BF16)
         self.name = None
         if self.op == OpEnum.LEAF:
             # leaf constructor, node.cpp:8-13
@@ -633,7 +635,8 @@ def flatten(roots: Sequence[Node], *, host_pointers=False, stop_at_realized=True
         for d, a in enumerate(n.axes):
             c.axes[d] = a
         c.keepdims = int(n.keepdims)
-        c.flags = (NODE_KEEP if n.keep else 0) | (NODE_TWIN16 if n.twin16 else 0) | (NODE_REQUIRES_GRAD if n.requires_grad else 0)
+        c.flags = ((NODE_KEEP if n.keep else 0) | (NODE_TWIN16 if n.twin16 else 0) | (NODE_BF16 if n.bf16 else 0) |
+                   (NODE_REQUIRES_GRAD if n.requires_grad else 0))
         if n.is_realized and stop_at_realized or n.op == OpEnum.LEAF:
             c.n_parents = 0
             buf = n.data

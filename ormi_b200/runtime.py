@@ -20,6 +20,7 @@ class Device:
         check(lib.ormi_b200_init(index, ctypes.byref(handle)))
         self.handle = handle
         self.index = index
+        self._options: dict[str, str] = {}
 
     def close(self):
         if self.handle:
@@ -59,6 +60,11 @@ class Device:
 
     def set_option(self, key: str, value: str):
         check(lib.ormi_b200_set_option(self.handle, key.encode(), value.encode()))
+        self._options[key] = value
+
+    def get_option(self, key: str) -> str:
+        """The value last set through this object ("matmul" and "fusion" start as "fp32" and "on")."""
+        return self._options.get(key, {"matmul": "fp32", "fusion": "on", "tc_pair": "on"}.get(key, ""))
 
     def counter(self, name: str) -> int:
         v = ctypes.c_int64()
@@ -126,9 +132,10 @@ class Device:
             if n.is_realized or not c.data:
                 continue
             if c.flags & G.NODE_OWNED:
-                buf = G.Buffer(n.shape if c.data_bytes == 4 * max(1, n.numel()) else [c.data_bytes // 4])
+                buf = G.Buffer(n.shape if c.data_bytes == 4 * max(1, n.numel()) or c.flags & G.NODE_BF16 else [c.data_bytes // 4])
                 buf.dev_ptr, buf._release = c.data, self.free
                 buf.nbytes = c.data_bytes
+                n.bf16 = bool(c.flags & G.NODE_BF16)       # came back as a bf16 matrix: from now on a matmul operand only
                 n.data = buf
                 base_of[c.data] = buf
         for i, n in enumerate(order):
@@ -140,6 +147,10 @@ class Device:
         """Tensor.numpy(): realize, copy the buffer to the host and apply the node's view strides
         (ormi-core/src/ormi_core/tensor.py:165-174)."""
         self.realize([node])
+        if node.bf16:                                  # a bf16 tensor: widen on the host (exact)
+            half = np.empty(node.data.nbytes // 2, dtype=np.uint16)
+            self.d2h(half, node.data.dev_ptr)
+            return (half.astype(np.uint32) << 16).view(np.float32).reshape(node.shape)
         raw = np.empty(node.data.nbytes // 4, dtype=np.float32)
         self.d2h(raw, node.data.dev_ptr)
         if not node.shape:

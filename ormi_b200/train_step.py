@@ -115,8 +115,10 @@ class MLPTrainer:
     """
 
     def __init__(self, dev, x, t, w1, b1, w2, b2, lr: float, global_batch: int | None = None, world: int = 1,
-                 overlap: bool = True):
+                 overlap: bool = True, bf16_matmuls: bool | None = None):
         self.dev, self.world, self.overlap = dev, world, overlap
+        if bf16_matmuls is None:
+            bf16_matmuls = dev.get_option("matmul") == "bf16"
         B, D = x.shape[0], t.shape[1]
         self.global_batch = global_batch or B * world
         scale = 1.0 / (self.global_batch * D)
@@ -154,6 +156,9 @@ class MLPTrainer:
             taps["xw1"].keep = True
             if taps["out"].grad is not None:
                 taps["out"].grad.keep = True
+            # h is read by two matmuls of later phases and by nothing else: in "bf16" arithmetic it leaves phase F as a
+            # bf16 matrix only (the backend hands back what it made; with other arithmetics the flag is not set)
+            taps["h"].bf16 = bf16_matmuls
             p.add_phase([taps["h"]])                             # F
             p.add_phase([up["w2"], up["b2"]])                    # U2
             p.add_phase([loss, grads["w1"], grads["b1"]])        # B1

@@ -47,7 +47,10 @@ def run_plan(plan: dict) -> dict:
             bufs.append(np.zeros(64, dtype=np.float32))    # the device word buffer: error word, counters (ints; all-zero bits)
         elif b["kind"] == "external":
             host = order[b["node"]].data.host
-            bufs.append(np.ascontiguousarray(host, dtype=np.float32).reshape(-1))
+            if order[b["node"]].bf16:            # a bf16 tensor the caller holds: raw 16-bit words
+                bufs.append(np.ascontiguousarray(host, dtype=np.uint16).reshape(-1))
+            else:
+                bufs.append(np.ascontiguousarray(host, dtype=np.float32).reshape(-1))
         elif b["kind"] == "twin16":
             bufs.append(np.full(max(1, b["bytes"] // 2), 0x7fc0, dtype=np.uint16))      # bf16 NaN until written
         else:
@@ -107,7 +110,7 @@ def _gemm_tc(s, bufs, lib, epi_name):
 
     def operand(buf, twin, rows, cols, trans, ld):
         srows, scols = (cols, rows) if trans else (rows, cols)          # the stored matrix
-        if twin >= 0:
+        if twin >= 0:      # a bf16 twin written earlier in the plan, or a bf16 tensor of the caller (then twin == buf)
             mat = (bufs[twin][: srows * scols].astype(np.uint32) << 16).view(np.float32).reshape(srows, scols)
         else:
             mat = _to_bf16(np.lib.stride_tricks.as_strided(bufs[buf], shape=(srows, scols), strides=(4 * ld, 4)))
@@ -156,6 +159,8 @@ def realize(roots, options=""):
             raw = np.ascontiguousarray(root.data.host).reshape(-1)
         else:
             raw = res[r]
+        if raw.dtype == np.uint16:       # a root materialized as bf16 only: widen (exact)
+            raw = (raw.astype(np.uint32) << 16).view(np.float32)
         if not root.shape:
             outs.append(raw[:1].reshape(()).copy())
         else:

@@ -376,3 +376,42 @@ def test_sum_over_a_view_with_few_outputs_uses_a_block_per_output():
     assert any("generic_sum[out=1,red=3072,block]" in w for w in whats), whats
     assert abs(float(outs[0]) - a.sum(dtype=np.float64)) <= REDUCE_TOL * np.abs(a).sum()
     assert np.abs(outs[1] - a.sum(axis=1, dtype=np.float64)).max() <= REDUCE_TOL * np.abs(a).sum(axis=1).max()
+
+
+def _bf16_words(x):
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return ((u + 0x7fff + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def test_first_class_bf16_tensors_cross_realize_calls():
+    """ORMI_NODE_BF16: a root materialized as bf16 ONLY (no fp32 copy is written), handed back, and read by the matmuls
+    of a later call as a bf16 tensor — the way the sharded trainer carries the hidden activation from one phase to the
+    next.  Anything but a tensor-core matmul refuses such a tensor."""
+    B, D, H = 256, 128, 512
+    x, w1, b1, w2 = W.normal(0, (B, D)), W.kaiming_uniform(2, D, (D, H)), W.normal(4, (H,), 0.1), W.kaiming_uniform(3, H, (H, D))
+    # call 1: h = gelu(x W1 + b1) as a bf16-only root
+    h = W.gelu_tanh(G.add(G.matmul(G.leaf(x), G.leaf(w1)), G.leaf(b1)))
+    h.bf16 = True
+    (want_h,), _ = O.port_run([W.gelu_tanh(G.add(G.matmul(G.leaf(x), G.leaf(w1)), G.leaf(b1)))])
+    outs, plan = E.realize([h], options="matmul=bf16")
+    gemm = [s for s in plan["steps"] if s["type"] == "gemm"][0]
+    assert len(plan["steps"]) == 1 and "outs=h" in gemm["epilogue"] and not gemm["store_c"]      # one kernel, nothing fp32 leaves it
+    assert [r["bf16"] for r in plan["results"]] == [True]
+    assert np.abs(outs[0] - want_h).max() <= BF16_TOL * np.abs(want_h).max()
+    # call 2: the bf16 tensor as operand of two matmuls, plain and transposed
+    h16 = G.Node(G.OpEnum.LEAF, data=G.Buffer((B, H), host=_bf16_words(outs[0])))
+    h16.data.nbytes = B * H * 2
+    h16.bf16 = True
+    g = W.normal(5, (B, D))
+    roots = [G.matmul(h16, G.leaf(w2)), G.matmul(G.transpose(h16, [1, 0]), G.leaf(g))]
+    outs2, plan2 = E.realize(roots, options="matmul=bf16")
+    gemms = [s for s in plan2["steps"] if s["type"] == "gemm"]
+    assert all(s["tc"] and s["a16"] == s["a"] for s in gemms)                                    # read in place, no conversion
+    assert np.abs(outs2[0] - outs[0] @ w2).max() <= BF16_TOL * np.abs(outs[0] @ w2).max()
+    assert np.abs(outs2[1] - outs[0].T @ g).max() <= BF16_TOL * np.abs(outs[0].T @ g).max()
+    # refused: pointwise work on a bf16 tensor, a bf16 root of another arithmetic, a shape the tensor cores do not take
+    assert "bf16 tensor can only be" in RT.plan([G.exp(h16)], options="matmul=bf16")["error"]
+    assert "need the" in RT.plan([G.matmul(h16, G.leaf(w2))])["error"]
+    small = G.mul(G.leaf(W.normal(0, (4, 6))), G.leaf(W.normal(1, (4, 6))))
+    small.bf16 = True
+    assert "bf16 only when" in RT.plan([small], options="matmul=bf16")["error"]
