@@ -35,11 +35,11 @@ WORKLOAD = "configs[1]: row softmax + layernorm, forward + autograd backward, x[
 BYTES_SOFTMAX = 4 * R * C * 4
 BYTES_LAYERNORM = 4 * R * C * 4 + 4 * C * 4
 BYTES_STEP = BYTES_SOFTMAX + BYTES_LAYERNORM
-# DRAM traffic of the dominant kernel from its ncu capture (profiles/rows_layernorm_fwd_bwd_8192x4096.md): 269.5 MB read +
-# 225.4 MB written per launch over 8192 rows; the traffic is proportional to the rows, the bench launch covers 16384.
-LN_TRAFFIC_BYTES = 2 * (269_485_568 + 225_356_800)
-LN_TRAFFIC_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 8192 rows (494.8 MB), times 2 for 16384 rows"
-LN_KERNEL = "fused layernorm forward+backward (rows template) + 2 finalize launches"
+# DRAM traffic of the dominant kernel from its ncu capture (profiles/rows_layernorm_fwd_bwd_8192x4096.md): 270.0 MB read +
+# 226.5 MB written per launch over 8192 rows; the traffic is proportional to the rows, the bench launch covers 16384.
+LN_TRAFFIC_BYTES = 2 * (270_039_552 + 226_531_328)
+LN_TRAFFIC_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 8192 rows (496.6 MB), times 2 for 16384 rows"
+LN_KERNEL = "fused layernorm forward+backward (rows template) + its finalize launch (partials of dg and db)"
 
 
 _REAL_STDOUT = None

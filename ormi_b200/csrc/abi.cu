@@ -229,7 +229,7 @@ int ormi_b200_plan_json_opts(const ormi_b200_node* nodes, int n_nodes, const int
             else if (k == "fusion") opt.fusion = (v != "off");
             else if (k == "aligned") opt.aligned = (v != "0");
             else if (k.rfind("tune.", 0) == 0) {
-                static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist"};
+                static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist", "epi_unroll", "epi_wpq"};
                 int which = -1;
                 for (int i = 0; i < kTuneKnobs; ++i) if (k.substr(5) == names[i]) which = i;
                 if (which < 0) throw Error("unknown option: " + k);
@@ -426,7 +426,7 @@ int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value)
             if (v == "on") ctx->tc_cta_group = 2; else if (v == "off") ctx->tc_cta_group = 1; else throw Error("tc_pair must be on or off");
         } else if (k.rfind("tune.", 0) == 0) {
             // overrides of the code generator's measured defaults (experiments); "0" restores the default
-            static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist"};
+            static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist", "epi_unroll", "epi_wpq"};
             int which = -1;
             for (int i = 0; i < kTuneKnobs; ++i) if (k.substr(5) == names[i]) which = i;
             if (which < 0) throw Error("unknown option: " + k);

@@ -858,8 +858,10 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
     g.body = body.str();
     g.end = end.str();
     g.unroll = spec.nodes.size() <= 4 ? 8 : (spec.nodes.size() <= 10 ? 2 : 1);
+    if (spec.tune[TUNE_EPI_UNROLL] == 1 || spec.tune[TUNE_EPI_UNROLL] == 2 || spec.tune[TUNE_EPI_UNROLL] == 4 || spec.tune[TUNE_EPI_UNROLL] == 8) g.unroll = spec.tune[TUNE_EPI_UNROLL];
     // exact exp / division chains cost tens of instructions per element: give them more epilogue warps
     g.wpq = spec.nodes.size() <= 2 ? 1 : (spec.nodes.size() <= 6 ? 2 : 4);
+    if (spec.tune[TUNE_EPI_WPQ] == 1 || spec.tune[TUNE_EPI_WPQ] == 2 || spec.tune[TUNE_EPI_WPQ] == 4) g.wpq = spec.tune[TUNE_EPI_WPQ];
     return g;
 }
 

@@ -441,3 +441,52 @@ def test_bounded_wait_gives_up_and_reports(device):
     (want,), _ = O.port_run([check_])
     assert rel(device.numpy(check_), want) <= REDUCE_TOL
     assert lib.ormi_b200_selftest_wait_timeout(device.handle, 5000) != 0      # limits outside 1..1000 ms are refused
+
+
+def test_unaligned_caller_pointer_gets_scalar_kernels():
+    """A device pointer that is not on a 16-byte boundary (a caller's own sub-buffer): the plan is generated without
+    128-bit accesses or bulk copies and gives the same result; the aligned call right after uses the vector plan again."""
+    from ormi_b200._lib import lib, check as ok
+    from ormi_b200.runtime import Device
+    dev = Device(0)
+    try:
+        R, C = 96, 512
+        host = W.normal(0, (R * C + 1,))
+        base = dev.upload(host)
+        out = dev.buffer([R])
+        shape, strides, axes = (ctypes.c_int32 * 2)(R, C), (ctypes.c_int32 * 2)(C, 1), (ctypes.c_int32 * 1)(1)
+        compiled = dev.counter("kernels_compiled")
+        ok(lib.ormi_b200_sum(dev.handle, ctypes.c_void_p(base.dev_ptr + 4), 2, shape, strides, axes, 1, ctypes.c_void_p(out.dev_ptr)))
+        want = host[1:].reshape(R, C).astype(np.float64).sum(axis=1)
+        assert rel(dev.download(out), want) <= REDUCE_TOL
+        ok(lib.ormi_b200_sum(dev.handle, ctypes.c_void_p(base.dev_ptr), 2, shape, strides, axes, 1, ctypes.c_void_p(out.dev_ptr)))
+        assert rel(dev.download(out), host[:-1].reshape(R, C).astype(np.float64).sum(axis=1)) <= REDUCE_TOL
+        assert dev.counter("kernels_compiled") == compiled + 2          # two different plans: scalar and vector
+    finally:
+        dev.close()
+
+
+def test_pool_byte_cap_walks_the_out_of_memory_path():
+    """"pool_limit_bytes": an allocation that would take the pool past the cap first gives the cached blocks back and
+    then fails with the driver's out-of-memory text; the context keeps working; lifting the cap lifts the failure."""
+    from ormi_b200.runtime import Device
+    dev = Device(0)
+    try:
+        dev.set_option("pool_limit_bytes", str(8 << 20))
+        a = dev.alloc(3 << 20)
+        b = dev.alloc(3 << 20)
+        dev.free(b, 3 << 20)                                   # cached by the pool: still counts until it is trimmed
+        trims = dev.counter("pool_trims")
+        c = dev.alloc(4 << 20)                                 # 3 + 3 (cached) + 4 > 8: trim, then 3 + 4 fits
+        assert dev.counter("pool_trims") == trims + 1
+        with pytest.raises(RuntimeError, match="out of memory"):
+            dev.alloc(2 << 20)                                 # 3 + 4 + 2 > 8 even after a trim
+        x = G.leaf(np.full((16,), 3.0, np.float32))
+        with pytest.raises(RuntimeError, match="out of memory"):
+            dev.realize([G.mul(dev.leaf(W.normal(0, (1 << 19,))), dev.const(2.0))])
+        dev.set_option("pool_limit_bytes", "0")
+        np.testing.assert_array_equal(dev.numpy(G.mul(x, x)), np.full((16,), 9.0, np.float32))
+        dev.free(a, 3 << 20)
+        dev.free(c, 4 << 20)
+    finally:
+        dev.close()
