@@ -613,9 +613,9 @@ def main():
 
     # ------------------------------------------------------------------------------------------------ end to end
     # Host buffers in, host buffers out, through the public Device API, pipelined: the step is row independent, so it
-    # runs in chunks of E2E_CHUNK rows — while the kernels of chunk k run, chunk k+1 is uploaded on the upload stream
-    # and the results of chunk k-1 go back on the download stream.  dg, db come back as one partial per chunk and are
-    # added on the host (and, with N > 1, summed over the ranks on the device first).
+    # runs in chunks of E2E_CHUNK rows — uploads on the upload stream, the kernels of chunk k as soon as its rows have
+    # arrived, its results back on the download stream while later chunks upload and compute.  dg, db come back as one
+    # partial per chunk and are added on the host (and, with N > 1, summed over the ranks on the device first).
     E2E_CHUNK = 1024
     n_chunks = R // E2E_CHUNK
     host_in = {k: torch.from_numpy(np.ascontiguousarray(v.data.host if v.data.host is not None else dev.download(v.data))).pin_memory()
@@ -624,9 +624,10 @@ def main():
     host_part = torch.empty(n_chunks * 2 * C, dtype=torch.float32).pin_memory()
     h2d = sum(t.numel() * 4 for t in host_in.values())
     d2h = sum(t.numel() * 4 for t in host_out) + host_part.numel() * 4
-    # two sets of chunk-sized device inputs (one being computed on, one being uploaded into) and their graphs
+    # every chunk has device inputs of its own (together: the full-size x and gy), so the uploads of a step are all
+    # queued at its start and run at the full one-direction rate; the kernels of chunk k wait for exactly chunk k's upload
     chunk_sets = []
-    for _ in range(2):
+    for _ in range(n_chunks):
         csm, cln, cin = build_graphs(G, W, lambda a, rg=False: dev.leaf(a, rg), rows=E2E_CHUNK, shard=rank)
         chunk_sets.append((StepRunner(dev, G, [csm, cln]), cin))
     np_in = {k: t.numpy() for k, t in host_in.items()}
@@ -634,22 +635,22 @@ def main():
     np_part = host_part.numpy()
 
     def upload(k):
-        _, cin = chunk_sets[k % 2]
+        _, cin = chunk_sets[k]
         rows = slice(k * E2E_CHUNK * C, (k + 1) * E2E_CHUNK * C)
-        dev.h2d_async(cin["x"].data.dev_ptr, np_in["x"].reshape(-1)[rows])
-        dev.h2d_async(cin["gy"].data.dev_ptr, np_in["gy"].reshape(-1)[rows])
-        if k < 2:      # the two parameter vectors, once per buffer set
-            dev.h2d_async(cin["g"].data.dev_ptr, np_in["g"].reshape(-1))
-            dev.h2d_async(cin["b"].data.dev_ptr, np_in["b"].reshape(-1))
+        # nothing on the device still reads these buffers: the previous step ended with the host waiting for its downloads
+        dev.h2d_async(cin["x"].data.dev_ptr, np_in["x"].reshape(-1)[rows], False)
+        dev.h2d_async(cin["gy"].data.dev_ptr, np_in["gy"].reshape(-1)[rows], False)
+        dev.h2d_async(cin["g"].data.dev_ptr, np_in["g"].reshape(-1), False)
+        dev.h2d_async(cin["b"].data.dev_ptr, np_in["b"].reshape(-1), False)
+        dev.upload_mark(k)
 
     def e2e_step():
         held = []
-        upload(0)
         for k in range(n_chunks):
-            if k + 1 < n_chunks:
-                upload(k + 1)                    # waits (on the device) for the kernels that still read that buffer set
-            dev.copy_wait(0)                     # the compute stream waits for the uploads queued so far
-            outs = chunk_sets[k % 2][0].run(keep=True)
+            upload(k)
+        for k in range(n_chunks):
+            dev.upload_wait(k)                   # the compute stream waits for chunk k's upload, not for the later ones
+            outs = chunk_sets[k][0].run(keep=True)
             if dist is not None:
                 bufs = (ctypes.c_void_p * 2)(outs[-2][0], outs[-1][0])
                 counts = (ctypes.c_size_t * 2)(C, C)
@@ -744,7 +745,7 @@ def main():
                        "cpu_sample": f"the reference arm and cpu_baseline step over workers x {CPU_ROWS_PER_WORKER} rows of the same workload"},
             "clocks": clocks,
             "e2e": {"value": world * BYTES_STEP / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms, "pipeline": f"{n_chunks} chunks of {E2E_CHUNK} rows: upload k+1 | kernels k | download k-1",
+                    "ms_per_step": e2e_ms, "pipeline": f"{n_chunks} chunks of {E2E_CHUNK} rows: all uploads queued first | kernels k after upload k | download k behind kernels k",
                     "pinned_h2d_gbps": h2d_gbps, "pinned_d2h_gbps": d2h_gbps},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "kernel": LN_KERNEL,

@@ -123,6 +123,13 @@ int ormi_b200_fill_u8(ormi_b200_ctx* ctx, void* dst, uint8_t pattern, size_t cou
 int ormi_b200_memcpy_h2d_async(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes, int after_compute);
 int ormi_b200_memcpy_d2h_async(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes);
 int ormi_b200_copy_wait(ormi_b200_ctx* ctx, int direction);
+/* Finer than copy_wait(ctx, 0), for loops that queue uploads well ahead of the kernels that read them:
+ *   upload_mark(slot)  remembers the upload stream's current tail in one of 32 slots (call it right after queueing the
+ *                      uploads of one batch);
+ *   upload_wait(slot)  makes the compute stream wait for exactly that point (call it right before the kernels of that
+ *                      batch), not for uploads queued later.  A slot never marked is already complete. */
+int ormi_b200_upload_mark(ormi_b200_ctx* ctx, int slot);
+int ormi_b200_upload_wait(ormi_b200_ctx* ctx, int slot);
 /* Waits for everything queued on the context's stream. */
 int ormi_b200_sync(ormi_b200_ctx* ctx);
 /* The context's compute stream as a cudaStream_t, for callers that time with CUDA events. */

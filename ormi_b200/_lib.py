@@ -32,6 +32,8 @@ _SIGNATURES = {
     "ormi_b200_memcpy_h2d_async": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_int]),
     "ormi_b200_memcpy_d2h_async": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t]),
     "ormi_b200_copy_wait": (c_int, [c_void_p, c_int]),
+    "ormi_b200_upload_mark": (c_int, [c_void_p, c_int]),
+    "ormi_b200_upload_wait": (c_int, [c_void_p, c_int]),
     "ormi_b200_fill_u32": (c_int, [c_void_p, c_void_p, ctypes.c_uint32, c_size_t]),
     "ormi_b200_fill_u8": (c_int, [c_void_p, c_void_p, ctypes.c_uint8, c_size_t]),
     "ormi_b200_sync": (c_int, [c_void_p]),

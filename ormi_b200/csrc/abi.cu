@@ -69,7 +69,7 @@ int ormi_b200_shutdown(ormi_b200_ctx* ctx) {
         for (auto& kv : ctx->shadows) cudaFree(kv.second.ptr);
         for (auto& kv : ctx->free_blocks) for (void* p : kv.second) cudaFree(p);
         if (ctx->gemm_err) cudaFree(ctx->gemm_err);
-        if (ctx->up_stream) { cudaStreamSynchronize(ctx->up_stream); cudaStreamSynchronize(ctx->down_stream); cudaStreamDestroy(ctx->up_stream); cudaStreamDestroy(ctx->down_stream); cudaEventDestroy(ctx->copy_event); }
+        if (ctx->up_stream) { cudaStreamSynchronize(ctx->up_stream); cudaStreamSynchronize(ctx->down_stream); cudaStreamDestroy(ctx->up_stream); cudaStreamDestroy(ctx->down_stream); cudaEventDestroy(ctx->copy_event); for (auto& e : ctx->upload_marks) cudaEventDestroy(e); }
         cudaStreamDestroy(ctx->stream);
         delete ctx;
     });
@@ -124,6 +124,7 @@ static void copy_streams(ormi_b200_ctx* ctx) {
     ORMI_CUDA(cudaStreamCreateWithFlags(&ctx->up_stream, cudaStreamNonBlocking));
     ORMI_CUDA(cudaStreamCreateWithFlags(&ctx->down_stream, cudaStreamNonBlocking));
     ORMI_CUDA(cudaEventCreateWithFlags(&ctx->copy_event, cudaEventDisableTiming));
+    for (auto& e : ctx->upload_marks) ORMI_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
 }
 
 int ormi_b200_memcpy_h2d_async(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes, int after_compute) {
@@ -163,6 +164,24 @@ int ormi_b200_copy_wait(ormi_b200_ctx* ctx, int direction) {
             comm_guarded_sync(ctx, ctx->down_stream);
             check_gemm_error(ctx);
         }
+    });
+}
+
+int ormi_b200_upload_mark(ormi_b200_ctx* ctx, int slot) {
+    return guarded([&] {
+        bind(ctx, "ormi_b200_upload_mark");
+        need(slot >= 0 && slot < 32, "ormi_b200_upload_mark: slot must be 0..31");
+        copy_streams(ctx);
+        ORMI_CUDA(cudaEventRecord(ctx->upload_marks[slot], ctx->up_stream));
+    });
+}
+
+int ormi_b200_upload_wait(ormi_b200_ctx* ctx, int slot) {
+    return guarded([&] {
+        bind(ctx, "ormi_b200_upload_wait");
+        need(slot >= 0 && slot < 32, "ormi_b200_upload_wait: slot must be 0..31");
+        copy_streams(ctx);
+        ORMI_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->upload_marks[slot], 0));
     });
 }
 

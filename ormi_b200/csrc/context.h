@@ -87,6 +87,7 @@ struct ormi_b200_ctx {
     // asynchronous host copies (abi.cu): one stream per direction, created on first use
     cudaStream_t up_stream = nullptr, down_stream = nullptr;
     cudaEvent_t copy_event = nullptr;
+    cudaEvent_t upload_marks[32] = {};   // ormi_b200_upload_mark / ormi_b200_upload_wait
     ormi_b200::DriverApi drv;
 
     std::mutex pool_mutex;

@@ -55,6 +55,14 @@ class Device:
     def copy_wait(self, direction: int):
         check(lib.ormi_b200_copy_wait(self.handle, direction))
 
+    def upload_mark(self, slot: int):
+        """Remembers the upload stream's tail (the uploads queued so far) in one of 32 slots."""
+        check(lib.ormi_b200_upload_mark(self.handle, slot))
+
+    def upload_wait(self, slot: int):
+        """The compute stream waits for the uploads that were queued when ``upload_mark(slot)`` was called, no later ones."""
+        check(lib.ormi_b200_upload_wait(self.handle, slot))
+
     def sync(self):
         check(lib.ormi_b200_sync(self.handle))
 
