@@ -441,8 +441,12 @@ int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value)
             // exhausted (0 = no limit): lets a host test walk the out-of-memory path without exhausting a GPU
             ctx->pool_limit_bytes = std::atoll(v.c_str());
         } else if (k == "tc_pair") {
-            // bf16 GEMM: "on" = one tcgen05.mma per pair of SMs (256 x 256 tiles, default), "off" = one per SM (128 x 256)
-            if (v == "on") ctx->tc_cta_group = 2; else if (v == "off") ctx->tc_cta_group = 1; else throw Error("tc_pair must be on or off");
+            // bf16 GEMM: "on" = one tcgen05.mma per pair of SMs (256 x 256 tiles), "off" = one per SM (128 x 256), "auto"
+            // (default) = pairs, except while an overlapped all-reduce is in flight beside the GEMM
+            if (v == "auto") { ctx->tc_cta_group = 2; ctx->tc_pair_auto = true; }
+            else if (v == "on") { ctx->tc_cta_group = 2; ctx->tc_pair_auto = false; }
+            else if (v == "off") { ctx->tc_cta_group = 1; ctx->tc_pair_auto = false; }
+            else throw Error("tc_pair must be auto, on or off");
         } else if (k.rfind("tune.", 0) == 0) {
             // overrides of the code generator's measured defaults (experiments); "0" restores the default
             static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist", "epi_unroll", "epi_wpq"};

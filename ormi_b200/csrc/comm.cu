@@ -181,6 +181,7 @@ void comm_allreduce(ormi_b200_ctx* ctx, void* const* bufs, const size_t* counts,
     // non-blocking communicator: the group may still be on its way to the stream when ncclGroupEnd returns; events
     // recorded behind it (ormi_b200_comm_mark / join) must come after its kernels, so wait until it is queued
     settle(ctx, st, api().GroupEnd(), "ncclGroupEnd (all-reduce)");
+    if (overlap) ctx->comm_inflight++;
     ctx->counters["allreduce_calls"] += n;
     for (int i = 0; i < n; ++i) ctx->counters["allreduce_bytes"] += (int64_t)counts[i] * 4;
 }
@@ -189,18 +190,21 @@ void comm_join(ormi_b200_ctx* ctx) {
     CommState* st = state(ctx);
     ORMI_CUDA(cudaEventRecord(st->done, st->stream));
     ORMI_CUDA(cudaStreamWaitEvent(ctx->stream, st->done, 0));
+    ctx->comm_inflight = 0;            // everything queued on the second stream so far is now ahead of the compute stream
 }
 
 void comm_mark(ormi_b200_ctx* ctx, int slot) {
     CommState* st = state(ctx);
     if (slot < 0 || slot >= kCommMarks) throw Error("NCCL Error: mark slot out of range");
     ORMI_CUDA(cudaEventRecord(st->marks[slot], st->stream));
+    ctx->comm_last_mark = slot;
 }
 
 void comm_wait(ormi_b200_ctx* ctx, int slot) {
     CommState* st = state(ctx);
     if (slot < 0 || slot >= kCommMarks) throw Error("NCCL Error: mark slot out of range");
     ORMI_CUDA(cudaStreamWaitEvent(ctx->stream, st->marks[slot], 0));   // a slot never marked is already complete
+    if (slot == ctx->comm_last_mark) ctx->comm_inflight = 0;           // the latest bucket: nothing of the second stream is left beside us
 }
 
 // Host-side wait for `stream` that cannot outlast the collective deadline while a communicator exists: polls the

@@ -105,6 +105,9 @@ struct ormi_b200_ctx {
     std::unordered_map<const void*, ormi_b200::Shadow16> shadows;
     std::unordered_map<std::string, ormi_b200::TcKernel> tc_kernels;   // compiled variants of the tensor-core GEMM
     int tc_cta_group = 2;             // CTAs per tcgen05.mma of the bf16 GEMM: 2 = a pair of SMs per 256 x 256 tile
+    bool tc_pair_auto = true;         // ... but one SM per MMA while a collective of the second stream may run beside the GEMM
+    int comm_inflight = 0;            // overlapped all-reduces queued and not yet waited for (host order = stream order)
+    int comm_last_mark = -1;
     // kErrorWords ints: word 0 is the error word, word kTileCounterWord (its own 128-byte line) the GEMM's tile counter
     int* gemm_err = nullptr;          // device word: non-zero when a bounded wait inside the tensor-core GEMM ran out
     bool gemm_err_pending = false;    // a kernel with bounded waits was launched since the word was last read

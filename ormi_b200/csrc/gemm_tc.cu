@@ -172,7 +172,9 @@ void gemm_tc(ormi_b200_ctx* ctx, const void* a16, int a_mn, const void* b16, int
     if (M <= 0 || N <= 0 || K <= 0) throw Error("gemm_tc: empty problem");
     if ((a_mn ? M : K) % 8 || (b_mn ? N : K) % 8 || N % 4) throw Error("gemm_tc: the contiguous dimension of each bf16 operand must be a multiple of 8 and N a multiple of 4");
     if (((uintptr_t)a16 | (uintptr_t)b16 | (uintptr_t)C) & 15) throw Error("gemm_tc: operands must be 16-byte aligned");
-    int cg = ctx->tc_cta_group;
+    // A collective running beside the GEMM holds single SMs; a pair needs both SMs of a TPC, so every SM the collective
+    // sits on takes its neighbour out of the GEMM too.  While an overlapped all-reduce is in flight: one SM per MMA.
+    int cg = (ctx->tc_pair_auto && ctx->comm_inflight > 0) ? 1 : ctx->tc_cta_group;
     // the kernel of this variant: looked up by its few parameters and the epilogue text, not by the whole source
     std::string vkey = std::to_string(cg) + "|" + std::to_string(a_mn) + "|" + std::to_string(b_mn);
     if (epi) vkey += "|" + std::to_string(epi->wpq) + "|" + std::to_string(epi->unroll) + "|" + epi->params + "|" + epi->init + "|" + epi->cols + "|" + epi->pre + "|" + epi->body + "|" + epi->end;
