@@ -44,22 +44,31 @@ std::string device_prelude() {
 #endif
 __device__ ORMI_NOINLINE float ormi_pow_general(float x, float y) { return powf(x, y); }
 __device__ ORMI_NOINLINE float ormi_cube_wide(float x) { return (float)((double)x * (double)x * (double)x); }
-__device__ __forceinline__ float ormi_pow(float x, float y) {
-    if (y == 0.5f) return sqrtf(x);
-    if (y == 2.0f) return __fmul_rn(x, x);
-    if (y == 3.0f) {
-        // x*x = x2 + e2 and x2*x = hi + e3 exactly (fused multiply-add residuals), so hi + (e3 + e2*x) is the cube to
-        // about 2^-46 before the last rounding — no trip through fp64 and its conversion pipe.
-        const float x2 = __fmul_rn(x, x), e2 = __fmaf_rn(x, x, -x2);
-        const float hi = __fmul_rn(x2, x), e3 = __fmaf_rn(x2, x, -hi);
-        const float ah = fabsf(hi);
-        if (ah > 1e-25f && ah < 1e38f) return __fadd_rn(hi, __fmaf_rn(e2, x, e3));
-        return ormi_cube_wide(x);                                // residuals under- or overflow out here
-    }
-    if (y == 1.0f) return x;
-    if (y == -1.0f) return __fdiv_rn(1.0f, x);
-    return ormi_pow_general(x, y);
+// x * x * x as a correctly rounded cube: x*x = x2 + e2 and x2*x = hi + e3 exactly (fused multiply-add residuals), so
+// hi + (e3 + e2*x) is the cube to about 2^-46 before the last rounding — no trip through fp64 and its conversion pipe.
+__device__ __forceinline__ float ormi_cube(float x) {
+    const float x2 = __fmul_rn(x, x), e2 = __fmaf_rn(x, x, -x2);
+    const float hi = __fmul_rn(x2, x), e3 = __fmaf_rn(x2, x, -hi);
+    const float ah = fabsf(hi);
+    if (ah > 1e-25f && ah < 1e38f) return __fadd_rn(hi, __fmaf_rn(e2, x, e3));
+    return ormi_cube_wide(x);                                // residuals under- or overflow out here
 }
+// Which of the special exponents y is: decided ONCE per thread (or row) when the exponent does not depend on the
+// element, so that the element loop pays one jump instead of five comparisons.
+__device__ __forceinline__ int ormi_pow_mode(float y) {
+    return y == 0.5f ? 1 : (y == 2.0f ? 2 : (y == 3.0f ? 3 : (y == 1.0f ? 4 : (y == -1.0f ? 5 : 0))));
+}
+__device__ __forceinline__ float ormi_pow_m(float x, float y, int mode) {
+    switch (mode) {
+        case 1: return sqrtf(x);
+        case 2: return __fmul_rn(x, x);
+        case 3: return ormi_cube(x);
+        case 4: return x;
+        case 5: return __fdiv_rn(1.0f, x);
+        default: return ormi_pow_general(x, y);
+    }
+}
+__device__ __forceinline__ float ormi_pow(float x, float y) { return ormi_pow_m(x, y, ormi_pow_mode(y)); }
 // GEMM epilogue: sum over the four lanes that hold the same columns of a 32-row block (lanes l, l^8, l^16, l^24)
 #ifndef ORMI_EMULATE
 __device__ __forceinline__ float ormi_epi_rows(float v, bool is_max) {
@@ -191,6 +200,49 @@ std::string op_expr(int op, const std::string& a, const std::string& b) {
     return "0.0f /* unknown op */";
 }
 
+// POW by an exponent that does not depend on the element (a constant leaf, or arithmetic on such): the special-case
+// decision is emitted once, in front of the element loop, and the loop calls ormi_pow_m with it.  `uniform_load(l)`
+// tells whether load l is such a value and `load_name(l)` its variable; `decls` receives the hoisted declarations.
+struct PowHoist {
+    const KernelSpec& spec;
+    std::function<bool(int)> uniform_load;
+    std::function<std::string(int)> load_name;
+    std::map<int, const KNode*> by_id;
+    std::map<int, std::string> mode_var;      // POW node -> name of its hoisted mode variable
+    std::ostringstream decls;
+
+    PowHoist(const KernelSpec& sp, std::function<bool(int)> ul, std::function<std::string(int)> ln)
+        : spec(sp), uniform_load(std::move(ul)), load_name(std::move(ln)) {
+        for (const KNode& kn : spec.nodes) by_id[kn.node] = &kn;
+    }
+    bool uniform(const KRef& r) const {
+        if (r.t == KRef::LOAD) return uniform_load(r.id);
+        auto it = by_id.find(r.id);
+        if (it == by_id.end() || it->second->op >= 1000) return false;
+        for (const KRef& o : it->second->operands) if (!uniform(o)) return false;
+        return true;
+    }
+    std::string expr(const KRef& r) const {
+        if (r.t == KRef::LOAD) return load_name(r.id);
+        const KNode* kn = by_id.at(r.id);
+        return op_expr(kn->op, expr(kn->operands[0]), kn->operands.size() > 1 ? expr(kn->operands[1]) : "");
+    }
+    void prepare(const std::string& indent) {
+        if (lowering_for(ORMI_OP_POW, nullptr)) return;           // a registered lowering is emitted as written
+        for (const KNode& kn : spec.nodes) {
+            if (kn.op != ORMI_OP_POW || kn.operands.size() < 2 || !uniform(kn.operands[1])) continue;
+            const std::string name = "pm" + std::to_string(kn.node);
+            decls << indent << "const int " << name << " = ormi_pow_mode(" << expr(kn.operands[1]) << ");\n";
+            mode_var[kn.node] = name;
+        }
+    }
+    std::string emit(const KNode& kn, const std::string& a, const std::string& b) const {
+        auto it = mode_var.find(kn.node);
+        if (it != mode_var.end()) return "ormi_pow_m(" + a + ", " + b + ", " + it->second + ")";
+        return op_expr(kn.op, a, b);
+    }
+};
+
 // identity element, combining expression and warp reduction of a reduction (sum, or maximum for ORMI_OP_MAX)
 std::string red_ident(bool is_max) { return is_max ? "ORMI_NEG_INF" : "0.0f"; }
 std::string red_comb(bool is_max, const std::string& a, const std::string& b) { return (is_max ? "ormi_max(" : "__fadd_rn(") + a + ", " + b + ")"; }
@@ -268,6 +320,9 @@ GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
         if (scalar[l]) s << "    const float S" << l << " = in" << l << "[0];\n";
     }
     for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) s << "    float gacc" << o << " = " << red_ident(spec.outputs[o].is_max) << ";\n";
+    PowHoist hoist(spec, [&](int l) { return (bool)scalar[l]; }, [&](int l) { return "S" + std::to_string(l); });
+    hoist.prepare("    ");
+    s << hoist.decls.str();
     {   // long arithmetic chains are bound by instruction issue, not by memory: two iterations in flight hide the
         // load latency behind the other iteration's arithmetic (measured: GELU forward 165 -> 151 us at 8192 x 8192)
         const int unroll = spec.tune[TUNE_FLAT_UNROLL] > 0 ? spec.tune[TUNE_FLAT_UNROLL] : (spec.nodes.size() >= 8 ? 2 : 1);
@@ -307,7 +362,7 @@ GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
     for (const KNode& kn : spec.nodes) {
         std::string a = ref(kn.operands[0]);
         std::string b = kn.operands.size() > 1 ? ref(kn.operands[1]) : "";
-        s << "            v" << kn.node << "[j] = " << op_expr(kn.op, a, b) << ";\n";
+        s << "            v" << kn.node << "[j] = " << hoist.emit(kn, a, b) << ";\n";
     }
     s << "        }\n";
     for (size_t o = 0; o < spec.outputs.size(); ++o) {
@@ -522,6 +577,9 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         if (li[l].scalar) s << "    const float L" << l << " = in" << l << "[0];\n";
         else emit_array_load(l, "0", "    ", false);
     }
+    PowHoist ph(spec, [&](int l) { return li[l].scalar && !li[l].row_var; }, [&](int l) { return "L" + std::to_string(l); });
+    ph.prepare("    ");
+    s << ph.decls.str();
     for (size_t o = 0; o < spec.outputs.size(); ++o) {
         const std::string ident = red_ident(spec.outputs[o].is_max);
         if (spec.outputs[o].kind == KOutput::COLSUM) { s << "    float cacc" << o << "[" << VPT << "];\n    #pragma unroll\n    for (int j = 0; j < " << VPT << "; ++j) cacc" << o << "[j] = " << ident << ";\n"; }
@@ -599,7 +657,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         for (const KNode& kn : spec.nodes) {
             if (!rowv(&kn) || kn.op == KNode::OP_ROWSUM || level[kn.node] != lv) continue;
             std::string a = ref(kn.operands[0], "0"), b = kn.operands.size() > 1 ? ref(kn.operands[1], "0") : "";
-            s << "        const float v" << kn.node << " = " << op_expr(kn.op, a, b) << ";\n";
+            s << "        const float v" << kn.node << " = " << ph.emit(kn, a, b) << ";\n";
         }
         // (b) per-element values of this level
         bool any = false;
@@ -620,7 +678,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
                 if (kn.op == ORMI_OP_DIV && !is_elem(kn.operands[1]) && !custom_div)
                     s << "            v" << kn.node << "[j] = __fmul_rn(" << a << ", rcp" << kn.node << ");\n";
                 else
-                    s << "            v" << kn.node << "[j] = " << op_expr(kn.op, a, b) << ";\n";
+                    s << "            v" << kn.node << "[j] = " << ph.emit(kn, a, b) << ";\n";
             }
             s << "        }\n";
         }
@@ -804,6 +862,10 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
         }
         return "v" + std::to_string(r.id) + "[j]";
     };
+    PowHoist ph(spec, [&](int l) { return !spec.loads[l].acc && spec.loads[l].st[0] == 0 && spec.loads[l].st[1] == 0; },
+                [&](int l) { return "S" + std::to_string(l); });
+    ph.prepare("");
+    { std::string d = ph.decls.str(); for (char& c : d) if (c == '\n') c = ' '; init << d; }
     body << "const float A[4] = {acc.x, acc.y, acc.z, acc.w}; ";
     for (const KNode& kn : spec.nodes) body << "float v" << kn.node << "[4]; ";
     if (!spec.nodes.empty()) {
@@ -811,7 +873,7 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
         for (const KNode& kn : spec.nodes) {
             std::string a = ref(kn.operands[0]);
             std::string b = kn.operands.size() > 1 ? ref(kn.operands[1]) : "";
-            body << "v" << kn.node << "[j] = " << op_expr(kn.op, a, b) << "; ";
+            body << "v" << kn.node << "[j] = " << ph.emit(kn, a, b) << "; ";
         }
         body << "} ";
     }
