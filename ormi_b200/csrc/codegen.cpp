@@ -53,31 +53,33 @@ __device__ __forceinline__ float ormi_cube(float x) {
     if (ah > 1e-25f && ah < 1e38f) return __fadd_rn(hi, __fmaf_rn(e2, x, e3));
     return ormi_cube_wide(x);                                // residuals under- or overflow out here
 }
-// Which of the special exponents y is: decided ONCE per thread (or row) when the exponent does not depend on the
-// element, so that the element loop pays one jump instead of five comparisons.
-__device__ __forceinline__ int ormi_pow_mode(float y) {
-    return y == 0.5f ? 1 : (y == 2.0f ? 2 : (y == 3.0f ? 3 : (y == 1.0f ? 4 : (y == -1.0f ? 5 : 0))));
+// The comparisons are on a value that does not change inside an element loop (the exponent is a constant leaf in every
+// graph seen so far): the compiler hoists them out of the loop by itself.  (Passing a precomputed integer "mode" and
+// switching on it was tried: the switch is lowered to an indirect branch per element and cost 10-15 % on the row
+// kernels.)
+__device__ __forceinline__ float ormi_pow(float x, float y) {
+    if (y == 0.5f) return sqrtf(x);
+    if (y == 2.0f) return __fmul_rn(x, x);
+    if (y == 3.0f) return ormi_cube(x);
+    if (y == 1.0f) return x;
+    if (y == -1.0f) return __fdiv_rn(1.0f, x);
+    return ormi_pow_general(x, y);
 }
-__device__ __forceinline__ float ormi_pow_m(float x, float y, int mode) {
-    switch (mode) {
-        case 1: return sqrtf(x);
-        case 2: return __fmul_rn(x, x);
-        case 3: return ormi_cube(x);
-        case 4: return x;
-        case 5: return __fdiv_rn(1.0f, x);
-        default: return ormi_pow_general(x, y);
-    }
-}
-__device__ __forceinline__ float ormi_pow(float x, float y) { return ormi_pow_m(x, y, ormi_pow_mode(y)); }
 // GEMM epilogue: sum over the four lanes that hold the same columns of a 32-row block (lanes l, l^8, l^16, l^24)
 #ifndef ORMI_EMULATE
+// ... and over all 32 lanes (a global sum: one value per 32-row block and 32-column chunk)
+__device__ __forceinline__ float ormi_epi_all(float v, bool is_max) {
+    for (int o = 16; o > 0; o >>= 1) { const float t = __shfl_xor_sync(0xffffffffu, v, o); v = is_max ? (t > v ? t : v) : __fadd_rn(v, t); }
+    return v;
+}
 __device__ __forceinline__ float ormi_epi_rows(float v, bool is_max) {
     float o = __shfl_xor_sync(0xffffffffu, v, 8);  v = is_max ? (o > v ? o : v) : __fadd_rn(v, o);
     o = __shfl_xor_sync(0xffffffffu, v, 16);       v = is_max ? (o > v ? o : v) : __fadd_rn(v, o);
     return v;
 }
 #else
-__device__ __forceinline__ float ormi_epi_rows(float v, bool) { return v; }   /* the emulator walks the 32 rows in one go */
+__device__ __forceinline__ float ormi_epi_rows(float v, bool) { return v; }   /* the emulator walks the lanes one after the other and carries the sums */
+__device__ __forceinline__ float ormi_epi_all(float v, bool) { return v; }
 #endif
 __device__ __forceinline__ float ormi_warp_sum(float v, int width) {
     for (int o = width >> 1; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -200,49 +202,6 @@ std::string op_expr(int op, const std::string& a, const std::string& b) {
     return "0.0f /* unknown op */";
 }
 
-// POW by an exponent that does not depend on the element (a constant leaf, or arithmetic on such): the special-case
-// decision is emitted once, in front of the element loop, and the loop calls ormi_pow_m with it.  `uniform_load(l)`
-// tells whether load l is such a value and `load_name(l)` its variable; `decls` receives the hoisted declarations.
-struct PowHoist {
-    const KernelSpec& spec;
-    std::function<bool(int)> uniform_load;
-    std::function<std::string(int)> load_name;
-    std::map<int, const KNode*> by_id;
-    std::map<int, std::string> mode_var;      // POW node -> name of its hoisted mode variable
-    std::ostringstream decls;
-
-    PowHoist(const KernelSpec& sp, std::function<bool(int)> ul, std::function<std::string(int)> ln)
-        : spec(sp), uniform_load(std::move(ul)), load_name(std::move(ln)) {
-        for (const KNode& kn : spec.nodes) by_id[kn.node] = &kn;
-    }
-    bool uniform(const KRef& r) const {
-        if (r.t == KRef::LOAD) return uniform_load(r.id);
-        auto it = by_id.find(r.id);
-        if (it == by_id.end() || it->second->op >= 1000) return false;
-        for (const KRef& o : it->second->operands) if (!uniform(o)) return false;
-        return true;
-    }
-    std::string expr(const KRef& r) const {
-        if (r.t == KRef::LOAD) return load_name(r.id);
-        const KNode* kn = by_id.at(r.id);
-        return op_expr(kn->op, expr(kn->operands[0]), kn->operands.size() > 1 ? expr(kn->operands[1]) : "");
-    }
-    void prepare(const std::string& indent) {
-        if (lowering_for(ORMI_OP_POW, nullptr)) return;           // a registered lowering is emitted as written
-        for (const KNode& kn : spec.nodes) {
-            if (kn.op != ORMI_OP_POW || kn.operands.size() < 2 || !uniform(kn.operands[1])) continue;
-            const std::string name = "pm" + std::to_string(kn.node);
-            decls << indent << "const int " << name << " = ormi_pow_mode(" << expr(kn.operands[1]) << ");\n";
-            mode_var[kn.node] = name;
-        }
-    }
-    std::string emit(const KNode& kn, const std::string& a, const std::string& b) const {
-        auto it = mode_var.find(kn.node);
-        if (it != mode_var.end()) return "ormi_pow_m(" + a + ", " + b + ", " + it->second + ")";
-        return op_expr(kn.op, a, b);
-    }
-};
-
 // identity element, combining expression and warp reduction of a reduction (sum, or maximum for ORMI_OP_MAX)
 std::string red_ident(bool is_max) { return is_max ? "ORMI_NEG_INF" : "0.0f"; }
 std::string red_comb(bool is_max, const std::string& a, const std::string& b) { return (is_max ? "ormi_max(" : "__fadd_rn(") + a + ", " + b + ")"; }
@@ -320,9 +279,6 @@ GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
         if (scalar[l]) s << "    const float S" << l << " = in" << l << "[0];\n";
     }
     for (size_t o = 0; o < spec.outputs.size(); ++o) if (spec.outputs[o].kind == KOutput::GLOBALSUM) s << "    float gacc" << o << " = " << red_ident(spec.outputs[o].is_max) << ";\n";
-    PowHoist hoist(spec, [&](int l) { return (bool)scalar[l]; }, [&](int l) { return "S" + std::to_string(l); });
-    hoist.prepare("    ");
-    s << hoist.decls.str();
     {   // long arithmetic chains are bound by instruction issue, not by memory: two iterations in flight hide the
         // load latency behind the other iteration's arithmetic (measured: GELU forward 165 -> 151 us at 8192 x 8192)
         const int unroll = spec.tune[TUNE_FLAT_UNROLL] > 0 ? spec.tune[TUNE_FLAT_UNROLL] : (spec.nodes.size() >= 8 ? 2 : 1);
@@ -362,7 +318,7 @@ GeneratedKernel generate_flat(const KernelSpec& spec, const std::string& name) {
     for (const KNode& kn : spec.nodes) {
         std::string a = ref(kn.operands[0]);
         std::string b = kn.operands.size() > 1 ? ref(kn.operands[1]) : "";
-        s << "            v" << kn.node << "[j] = " << hoist.emit(kn, a, b) << ";\n";
+        s << "            v" << kn.node << "[j] = " << op_expr(kn.op, a, b) << ";\n";
     }
     s << "        }\n";
     for (size_t o = 0; o < spec.outputs.size(); ++o) {
@@ -577,9 +533,6 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         if (li[l].scalar) s << "    const float L" << l << " = in" << l << "[0];\n";
         else emit_array_load(l, "0", "    ", false);
     }
-    PowHoist ph(spec, [&](int l) { return li[l].scalar && !li[l].row_var; }, [&](int l) { return "L" + std::to_string(l); });
-    ph.prepare("    ");
-    s << ph.decls.str();
     for (size_t o = 0; o < spec.outputs.size(); ++o) {
         const std::string ident = red_ident(spec.outputs[o].is_max);
         if (spec.outputs[o].kind == KOutput::COLSUM) { s << "    float cacc" << o << "[" << VPT << "];\n    #pragma unroll\n    for (int j = 0; j < " << VPT << "; ++j) cacc" << o << "[j] = " << ident << ";\n"; }
@@ -657,7 +610,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         for (const KNode& kn : spec.nodes) {
             if (!rowv(&kn) || kn.op == KNode::OP_ROWSUM || level[kn.node] != lv) continue;
             std::string a = ref(kn.operands[0], "0"), b = kn.operands.size() > 1 ? ref(kn.operands[1], "0") : "";
-            s << "        const float v" << kn.node << " = " << ph.emit(kn, a, b) << ";\n";
+            s << "        const float v" << kn.node << " = " << op_expr(kn.op, a, b) << ";\n";
         }
         // (b) per-element values of this level
         bool any = false;
@@ -678,7 +631,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
                 if (kn.op == ORMI_OP_DIV && !is_elem(kn.operands[1]) && !custom_div)
                     s << "            v" << kn.node << "[j] = __fmul_rn(" << a << ", rcp" << kn.node << ");\n";
                 else
-                    s << "            v" << kn.node << "[j] = " << ph.emit(kn, a, b) << ";\n";
+                    s << "            v" << kn.node << "[j] = " << op_expr(kn.op, a, b) << ";\n";
             }
             s << "        }\n";
         }
@@ -851,6 +804,7 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
     for (size_t o = 0; o < spec.outputs.size(); ++o)
         if (spec.outputs[o].kind == KOutput::COLSUM) cols << "float cs" << o << "[4] = {" << red_ident(spec.outputs[o].is_max) << ", " << red_ident(spec.outputs[o].is_max) << ", "
                                                           << red_ident(spec.outputs[o].is_max) << ", " << red_ident(spec.outputs[o].is_max) << "}; ";
+        else if (spec.outputs[o].kind == KOutput::GLOBALSUM) cols << "float gs" << o << " = " << red_ident(spec.outputs[o].is_max) << "; ";
     std::string cols_text = cols.str();
     if (col_loads) cols_text = "const int gc = gcol < N ? gcol : 0; " + cols_text;
     auto ref = [&](const KRef& r) {
@@ -862,10 +816,6 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
         }
         return "v" + std::to_string(r.id) + "[j]";
     };
-    PowHoist ph(spec, [&](int l) { return !spec.loads[l].acc && spec.loads[l].st[0] == 0 && spec.loads[l].st[1] == 0; },
-                [&](int l) { return "S" + std::to_string(l); });
-    ph.prepare("");
-    { std::string d = ph.decls.str(); for (char& c : d) if (c == '\n') c = ' '; init << d; }
     body << "const float A[4] = {acc.x, acc.y, acc.z, acc.w}; ";
     for (const KNode& kn : spec.nodes) body << "float v" << kn.node << "[4]; ";
     if (!spec.nodes.empty()) {
@@ -873,7 +823,7 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
         for (const KNode& kn : spec.nodes) {
             std::string a = ref(kn.operands[0]);
             std::string b = kn.operands.size() > 1 ? ref(kn.operands[1]) : "";
-            body << "v" << kn.node << "[j] = " << ph.emit(kn, a, b) << "; ";
+            body << "v" << kn.node << "[j] = " << op_expr(kn.op, a, b) << "; ";
         }
         body << "} ";
     }
@@ -881,7 +831,7 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
     if (store_c) body << "*reinterpret_cast<float4*>(C" << at << ") = acc; ";
     for (size_t o = 0; o < spec.outputs.size(); ++o) {
         const KOutput& ko = spec.outputs[o];
-        if (ko.kind != KOutput::FULL && ko.kind != KOutput::COLSUM) { g.error = "epilogue: only full and column-sum outputs"; return g; }
+        if (ko.kind != KOutput::FULL && ko.kind != KOutput::COLSUM && ko.kind != KOutput::GLOBALSUM) { g.error = "epilogue: row outputs are not supported"; return g; }
         auto val = [&](int j) {
             std::string r = ref(ko.value);
             size_t p = r.find("[j]");
@@ -897,6 +847,14 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
             for (int j = 0; j < 4; ++j) end << "cs" << o << "[" << j << "] = ormi_epi_rows(cs" << o << "[" << j << "], " << (ko.is_max ? "true" : "false") << "); ";
             end << "if (rsub == 0 && gcol < N) *reinterpret_cast<float4*>(eout" << o << " + (long long)(row0 >> 5) * " << N << " + gcol) = make_float4(cs" << o << "[0], cs" << o
                 << "[1], cs" << o << "[2], cs" << o << "[3]); } ";
+            continue;
+        }
+        if (ko.kind == KOutput::GLOBALSUM) {
+            // one partial per 32-row block and 32-column chunk: [row block][chunk], added up in that order by a finalize kernel
+            params << ", float* __restrict__ eout" << o;
+            for (int j = 0; j < 4; ++j) body << "gs" << o << " = " << red_comb(ko.is_max, "gs" + std::to_string(o), val(j)) << "; ";
+            end << "{ gs" << o << " = ormi_epi_all(gs" << o << ", " << (ko.is_max ? "true" : "false") << "); if (lane == 0) eout" << o << "[(long long)(row0 >> 5) * "
+                << (N + 31) / 32 << " + (col0 >> 5)] = gs" << o << "; } ";
             continue;
         }
         if (ko.store) {

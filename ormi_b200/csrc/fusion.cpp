@@ -567,7 +567,8 @@ Plan Scheduler::run(const int* roots, int n_roots) {
                     // full pointwise results, and column sums over the rows of the product (a bias gradient)
                     const bool full = (info[o].kind == K_PW || info[o].kind == K_IDSUM) && !info[o].row_cls;
                     const bool colsum = info[o].kind == K_COLSUM && info[o].k == 1 && info[o].D == Fs.D;
-                    if (!full && !colsum) ok = false;
+                    const bool globalsum = info[o].kind == K_GLOBALSUM && info[o].D == Fs.D;      // e.g. the loss behind the last matmul
+                    if (!full && !colsum && !globalsum) ok = false;
                     for (const Dep& d : deps[o]) {
                         if (d.node == m) { reads_m = true; continue; }
                         const int ds = info[d.node].step;
@@ -807,13 +808,15 @@ Plan Scheduler::run(const int* roots, int n_roots) {
                     g.epi_wpq = ge.wpq; g.epi_unroll = ge.unroll;
                     for (const KLoad& l : ks.loads) if (!l.acc) g.epi_args.push_back(buffer_for(l.src_node));
                     for (const KOutput& o : ks.outputs) {
-                        if (o.kind == KOutput::COLSUM) {
-                            // one partial row per 32-row block of the product; blocks past the last row (the tile grid
-                            // is rounded up to 256 rows) are written too, as zeros, and not read
-                            const int64_t blocks = (g.M + 31) / 32, padded = ((g.M + 255) / 256) * 8;
-                            int tmp = temp_buffer(padded * g.N * 4);
+                        if (o.kind == KOutput::COLSUM || o.kind == KOutput::GLOBALSUM) {
+                            // one partial row per 32-row block of the product (a global sum: one value per block and
+                            // 32-column chunk); blocks past the last row (the tile grid is rounded up to 256 rows) are
+                            // written too, as zeros, and not read
+                            const bool col = o.kind == KOutput::COLSUM;
+                            const int64_t blocks = (g.M + 31) / 32, padded = ((g.M + 255) / 256) * 8, chunks = (g.N + 31) / 32;
+                            int tmp = temp_buffer(padded * (col ? (int64_t)g.N : chunks) * 4);
                             g.epi_args.push_back(tmp);
-                            GeneratedKernel fk = generate_finalize((int)blocks, g.N, "ormi_finalize_" + std::to_string(kernel_serial++), o.is_max);
+                            GeneratedKernel fk = generate_finalize((int)(col ? blocks : blocks * chunks), col ? (int64_t)g.N : 1, "ormi_finalize_" + std::to_string(kernel_serial++), o.is_max);
                             Step fs; fs.type = Step::Kernel; fs.k = fk.step;
                             fs.k.args = {tmp, buffer_for(o.node)};
                             finalizes.push_back(fs);
@@ -825,7 +828,7 @@ Plan Scheduler::run(const int* roots, int n_roots) {
                     if (twin_c) g.epi_args.push_back(twin_for(m));
                     std::ostringstream what;
                     what << "epilogue[nodes=" << ks.nodes.size() << ",loads=" << ks.loads.size() - 1 << ",outs=";
-                    for (const KOutput& o : ks.outputs) what << (o.kind == KOutput::COLSUM ? "C" : "") << (o.kind == KOutput::FULL && o.store ? "F" : "") << (o.twin ? "h" : "");
+                    for (const KOutput& o : ks.outputs) what << (o.kind == KOutput::COLSUM ? "C" : "") << (o.kind == KOutput::GLOBALSUM ? "G" : "") << (o.kind == KOutput::FULL && o.store ? "F" : "") << (o.twin ? "h" : "");
                     what << ",product=" << (g.store_c ? "F" : "") << (twin_c ? "h" : "") << ",wpq=" << ge.wpq << "]";
                     g.epi_what = what.str();
                 }

@@ -72,30 +72,32 @@ def run_plan(plan: dict) -> dict:
 
 
 def _epilogue_source(name, s):
-    """The generated epilogue text of a tensor-core GEMM step as a plain loop over (32-row block, 4 columns)."""
+    """The generated epilogue text of a tensor-core GEMM step as plain loops.  The 32 lanes of a warp (8 column groups
+    `cq` x 4 row groups `rsub`) are walked one after the other over a 32-row block x 32-column chunk; column sums are
+    carried from one row group to the next of the same column group, global sums from every lane to the next (the
+    emulator's ormi_epi_rows / ormi_epi_all are the identity), and the lane that is walked last plays lane 0."""
     import re
-    sums = sorted(set(re.findall(r"float cs(\d+)\[4\]", s["epi_cols"])))
-    carry_in = " ".join(f"if (have) for (int j = 0; j < 4; ++j) cs{o}[j] = carry[{k}][j];" for k, o in enumerate(sums))
-    carry_out = " ".join(f"for (int j = 0; j < 4; ++j) carry[{k}][j] = cs{o}[j];" for k, o in enumerate(sums)) + " have = true;"
-    text = _epilogue_template(name, s)
-    return text.replace("EMUL_CARRY_IN", carry_in).replace("EMUL_CARRY_OUT", carry_out)
-
-
-def _epilogue_template(name, s):
+    csums = sorted(set(re.findall(r"float cs(\d+)\[4\]", s["epi_cols"])))
+    gsums = sorted(set(re.findall(r"float gs(\d+) =", s["epi_cols"])))
+    carry_in = " ".join(f"if (have_c) for (int j = 0; j < 4; ++j) cs{o}[j] = ccarry[{k}][j];" for k, o in enumerate(csums))
+    carry_in += " " + " ".join(f"if (have_g) gs{o} = gcarry[{k}];" for k, o in enumerate(gsums))
+    carry_out = " ".join(f"for (int j = 0; j < 4; ++j) ccarry[{k}][j] = cs{o}[j];" for k, o in enumerate(csums)) + " have_c = true; "
+    carry_out += " ".join(f"gcarry[{k}] = gs{o};" for k, o in enumerate(gsums)) + " have_g = true;"
     return (s["epi_prelude"] + f'\nextern "C" void {name}(float* C, const float* P, int M, int N{s["epi_params"]}) {{\n'
             f'    {s["epi_init"]}\n'
-            # the four lane groups of a warp (rsub = 0..3) walk rows row0 + rsub + 4 p one after the other; their column
-            # partials are combined by carrying cs<o> over (the emulator's ormi_epi_rows is the identity)
-            f'    for (int row0 = 0; row0 < M; row0 += 32) for (int gcol = 0; gcol < N; gcol += 4) {{\n'
-            f'        float carry[8][4]; bool have = false;\n'
-            f'        for (int rsub_i = 0; rsub_i < 4; ++rsub_i) {{\n            const int rsub = rsub_i == 3 ? 0 : rsub_i + 1;\n'   # rsub 0 last: it writes the partial
-            f'            {s["epi_cols"]}\n            EMUL_CARRY_IN\n'
-            f'            for (int p = 0; p < 8; ++p) {{\n                const int grow = row0 + 4 * p + rsub;\n'
-            f'                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);\n'
-            f'                if (grow < M) acc = make_float4(P[(long long)grow * N + gcol], P[(long long)grow * N + gcol + 1], '
+            f'    for (int row0 = 0; row0 < M; row0 += 32) for (int col0 = 0; col0 < N; col0 += 32) {{\n'
+            f'        float gcarry[8]; bool have_g = false;\n'
+            f'        for (int cq = 0; cq < 8; ++cq) {{\n            const int gcol = col0 + 4 * cq;\n'
+            f'            float ccarry[8][4]; bool have_c = false;\n'
+            f'            for (int rsub_i = 0; rsub_i < 4; ++rsub_i) {{\n                const int rsub = rsub_i == 3 ? 0 : rsub_i + 1;\n'
+            f'                const int lane = (cq == 7 && rsub == 0) ? 0 : 1 + 8 * rsub + cq;\n'
+            f'                {s["epi_cols"]}\n                {carry_in}\n'
+            f'                for (int p = 0; p < 8; ++p) {{\n                    const int grow = row0 + 4 * p + rsub;\n'
+            f'                    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);\n'
+            f'                    if (grow < M && gcol < N) acc = make_float4(P[(long long)grow * N + gcol], P[(long long)grow * N + gcol + 1], '
             f'P[(long long)grow * N + gcol + 2], P[(long long)grow * N + gcol + 3]);\n'
-            f'                {s["epi_pre"]}\n                if (grow < M && gcol < N) {{ {s["epi_body"]} }}\n            }}\n'
-            f'            EMUL_CARRY_OUT\n            if (rsub == 0) {{ {s["epi_end"]} }}\n        }}\n    }}\n}}\n')
+            f'                    {s["epi_pre"]}\n                    if (grow < M && gcol < N) {{ {s["epi_body"]} }}\n                }}\n'
+            f'                {carry_out}\n                if (rsub == 0) {{ {s["epi_end"]} }}\n            }}\n        }}\n    }}\n}}\n')
 
 
 def _to_bf16(x):
