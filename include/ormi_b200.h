@@ -261,11 +261,16 @@ int ormi_b200_selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms);
  *              bf16 copies beside their fp32 buffers — those buffers must then only be written through this ABI),
  *              "tf32", "3xtf32".
  *   "fusion":  "on" (default) / "off" (one kernel per node, like the reference scheduler).
+ *   "intermediates": "keep" (default): every node a plan materializes comes back realized, as the reference realizes
+ *              every node it executes (runtime.cpp:13-39).  "free": only roots and ORMI_NODE_KEEP nodes come back; a
+ *              materialized node nobody outside the call holds is scratch, returned to the pool after the last step
+ *              that reads it (a later call that reaches it again recomputes it).
  *   "tc_pair": "auto" (default) / "on" (one tcgen05.mma per pair of SMs, 256 x 256 tiles) / "off" (one per SM, 128 x 256).
  *              auto = pairs, except for GEMMs queued while an overlapped all-reduce is in flight: a collective holds
  *              single SMs, and a pair needs both SMs of a TPC.
  *   "tune.rows_vpt", "tune.rows_minb", "tune.rows_grid", "tune.rows_stage", "tune.rows_nstage", "tune.rows_dynamic",
- *   "tune.flat_unroll", "tune.rows_hoist", "tune.epi_unroll", "tune.epi_wpq": integer overrides of the code generator's measured defaults, for
+ *   "tune.flat_unroll", "tune.rows_hoist", "tune.epi_unroll", "tune.epi_wpq", "tune.gemm_bn" (128 / 256 columns per
+ *   tensor-core GEMM tile): integer overrides of the code generator's measured defaults, for
  *              experiments ("0" = default; for the on/off ones 1 = off, 2 = on). */
 int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value);
 

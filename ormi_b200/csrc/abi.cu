@@ -246,9 +246,10 @@ int ormi_b200_plan_json_opts(const ormi_b200_node* nodes, int n_nodes, const int
             const std::string k = item.substr(0, eq), v = item.substr(eq + 1);
             if (k == "matmul") opt.bf16_matmul = (v == "bf16");
             else if (k == "fusion") opt.fusion = (v != "off");
+            else if (k == "intermediates") opt.free_intermediates = (v == "free");
             else if (k == "aligned") opt.aligned = (v != "0");
             else if (k.rfind("tune.", 0) == 0) {
-                static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist", "epi_unroll", "epi_wpq"};
+                static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist", "epi_unroll", "epi_wpq", "gemm_bn"};
                 int which = -1;
                 for (int i = 0; i < kTuneKnobs; ++i) if (k.substr(5) == names[i]) which = i;
                 if (which < 0) throw Error("unknown option: " + k);
@@ -449,13 +450,17 @@ int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value)
             else throw Error("tc_pair must be auto, on or off");
         } else if (k.rfind("tune.", 0) == 0) {
             // overrides of the code generator's measured defaults (experiments); "0" restores the default
-            static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist", "epi_unroll", "epi_wpq"};
+            static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist", "epi_unroll", "epi_wpq", "gemm_bn"};
             int which = -1;
             for (int i = 0; i < kTuneKnobs; ++i) if (k.substr(5) == names[i]) which = i;
             if (which < 0) throw Error("unknown option: " + k);
             ctx->tune[which] = std::atoi(v.c_str());
         } else if (k == "fusion") {
             if (v == "on") ctx->fusion = true; else if (v == "off") ctx->fusion = false; else throw Error("fusion must be on or off");
+        } else if (k == "intermediates") {
+            // "keep" (default): every node a plan materializes is handed back, as the reference realizes every node.
+            // "free": only roots and ORMI_NODE_KEEP nodes are; the other materialized nodes are scratch of the call.
+            if (v == "keep") ctx->free_intermediates = false; else if (v == "free") ctx->free_intermediates = true; else throw Error("intermediates must be keep or free");
         } else throw Error("unknown option: " + k);
     });
 }

@@ -925,7 +925,12 @@ Plan Scheduler::run(const int* roots, int n_roots) {
     // ---- results: every materialized node, plus roots / KEEP nodes that are views (aliases)
     for (int i = 0; i < n; ++i) {
         if (!info[i].needed || info[i].kind == K_INPUT) continue;
-        if (info[i].in_M && !drop_f32[i]) plan.results.push_back(NodeResult{i, buffer_for(i), false});
+        if (info[i].in_M && !drop_f32[i]) {
+            // A materialized node nobody outside the call can reach again is scratch under "intermediates=free": its
+            // block goes back to the pool right after the last step that reads it.
+            if (opt.free_intermediates && !handed[i]) plan.buffers[buffer_for(i)].kind = BufKind::Temp;
+            else plan.results.push_back(NodeResult{i, buffer_for(i), false});
+        }
         if (info[i].in_M && bf16_out[i]) { NodeResult r{i, twin_for(i), false}; r.bf16 = true; plan.results.push_back(r); }
     }
     auto alias_result = [&](int i) {

@@ -24,11 +24,11 @@ const char* kTemplate =
 
 constexpr int kMaxSmem = 232448;     // 227 KB: the opt-in limit of dynamic shared memory per block on sm_100
 
-struct Variant { int cta_group, a_mn, b_mn, wpq, stages, smem; };
+struct Variant { int cta_group, a_mn, b_mn, wpq, bn, stages, smem; };
 
-Variant make_variant(int cta_group, int a_mn, int b_mn, int wpq) {
-    Variant v{cta_group, a_mn, b_mn, wpq, 0, 0};
-    const int stage_bytes = 128 * 64 * 2 + (256 / cta_group) * 64 * 2;
+Variant make_variant(int cta_group, int a_mn, int b_mn, int wpq, int bn) {
+    Variant v{cta_group, a_mn, b_mn, wpq, bn, 0, 0};
+    const int stage_bytes = 128 * 64 * 2 + (bn / cta_group) * 64 * 2;
     const int fixed = 1024 /* alignment slack */ + 4 * wpq * 4096 /* staging */ + 64 /* flags, schedule slots */;
     int s = (kMaxSmem - fixed - 8 * 12) / (stage_bytes + 16);
     v.stages = std::min(s, 8);
@@ -46,6 +46,7 @@ KernelStep make_kernel(const Variant& v, const TcEpilogue* epi) {
     def("G_A_MN", std::to_string(v.a_mn));
     def("G_B_MN", std::to_string(v.b_mn));
     def("G_EPI_WPQ", std::to_string(v.wpq));
+    def("G_BN", std::to_string(v.bn));
     def("G_STAGES", std::to_string(v.stages));
     def("G_EPI_PARAMS", epi ? one_line(epi->params) : "");
     def("G_EPI_INIT", epi ? one_line(epi->init) : "");
@@ -175,12 +176,21 @@ void gemm_tc(ormi_b200_ctx* ctx, const void* a16, int a_mn, const void* b16, int
     // A collective running beside the GEMM holds single SMs; a pair needs both SMs of a TPC, so every SM the collective
     // sits on takes its neighbour out of the GEMM too.  While an overlapped all-reduce is in flight: one SM per MMA.
     int cg = (ctx->tc_pair_auto && ctx->comm_inflight > 0) ? 1 : ctx->tc_cta_group;
+    // Tile width: 256 columns.  The MMA takes as long for N = 128 as for N = 256 (measured: 128-column tiles halve the
+    // throughput of every large shape), so narrow tiles only pay where 256-column tiles would leave more than half of the
+    // SMs without one: the drain of an accumulator is bound by the SM's store path (~25 bytes per clock, whatever the
+    // number of epilogue warps), and 128 x 128 tiles on single SMs spread it over twice as many SMs as 256 x 256 tiles on pairs.
+    int bn = ctx->tune[TUNE_GEMM_BN] ? ctx->tune[TUNE_GEMM_BN] : 256;
+    if (bn != 128 && bn != 256) throw Error("tune.gemm_bn must be 128 or 256");
+    if (!ctx->tune[TUNE_GEMM_BN] && ((M + 127) / 128) * ((N + 127) / 128) <= ctx->num_sms / 2 + 2) { cg = 1; bn = 128; }
+    const int wpq = epi ? epi->wpq : (ctx->tune[TUNE_EPI_WPQ] ? ctx->tune[TUNE_EPI_WPQ] : 1);
+    if (wpq != 1 && wpq != 2 && wpq != 4) throw Error("tune.epi_wpq must be 1, 2 or 4");
     // the kernel of this variant: looked up by its few parameters and the epilogue text, not by the whole source
-    std::string vkey = std::to_string(cg) + "|" + std::to_string(a_mn) + "|" + std::to_string(b_mn);
-    if (epi) vkey += "|" + std::to_string(epi->wpq) + "|" + std::to_string(epi->unroll) + "|" + epi->params + "|" + epi->init + "|" + epi->cols + "|" + epi->pre + "|" + epi->body + "|" + epi->end;
+    std::string vkey = std::to_string(cg) + "|" + std::to_string(a_mn) + "|" + std::to_string(b_mn) + "|" + std::to_string(bn) + "|" + std::to_string(wpq);
+    if (epi) vkey += "|" + std::to_string(epi->unroll) + "|" + epi->params + "|" + epi->init + "|" + epi->cols + "|" + epi->pre + "|" + epi->body + "|" + epi->end;
     auto found = ctx->tc_kernels.find(vkey);
     if (found == ctx->tc_kernels.end()) {
-        const Variant v = make_variant(cg, a_mn, b_mn, epi ? epi->wpq : 1);
+        const Variant v = make_variant(cg, a_mn, b_mn, wpq, bn);
         const KernelStep made = make_kernel(v, epi);
         TcKernel tk;
         tk.kernel = get_kernel(ctx, made);
@@ -193,10 +203,10 @@ void gemm_tc(ormi_b200_ctx* ctx, const void* a16, int a_mn, const void* b16, int
     if (a_mn) make_map(ctx, &map_a, a16, K, M, M, 64);            // stored [K][M]
     else make_map(ctx, &map_a, a16, M, K, K, 128);                // stored [M][K]
     if (b_mn) make_map(ctx, &map_b, b16, K, N, N, 64);            // stored [K][N]
-    else make_map(ctx, &map_b, b16, N, K, K, 256 / cg);           // stored [N][K]
+    else make_map(ctx, &map_b, b16, N, K, K, bn / cg);            // stored [N][K]
     int* err = device_error_word(ctx);
     int* counter = err + kTileCounterWord;
-    int tiles_m = (M + 128 * cg - 1) / (128 * cg), tiles_n = (N + 255) / 256, num_kb = (K + 63) / 64;
+    int tiles_m = (M + 128 * cg - 1) / (128 * cg), tiles_n = (N + bn - 1) / bn, num_kb = (K + 63) / 64;
     const int grid = cg * std::min(tiles_m * tiles_n, ctx->num_sms / cg);
     std::vector<void*> argv = {&map_a, &map_b, &C, &M, &N, &num_kb, &tiles_m, &tiles_n, &err, &counter};
     std::vector<void*> extra;

@@ -47,7 +47,7 @@ struct __align__(64) TensorMap { unsigned long long opaque[16]; };
 
 constexpr int CG = G_CTA_GROUP;
 constexpr int BM = 128;                       // rows of A (and of D) per CTA
-constexpr int BN = 256;                       // columns of D per tile
+constexpr int BN = G_BN;                      // columns of D per tile: 256, or 128 for problems of few tiles
 constexpr int BNC = BN / CG;                  // columns of B this CTA loads
 constexpr int BK = 64;                        // k per stage (128 bytes of bf16)
 constexpr int UMMA_K = 16;
@@ -252,6 +252,13 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
     const unsigned rank = cluster_rank();                                  // 0 = leader of the pair
     const unsigned peer = rank ^ 1u;
     const int num_tiles = tiles_m * tiles_n;
+    // The first tile of every CTA (pair) is its own index: nobody waits for the scheduler before the first load.  Later
+    // tiles come from the counter, offset by the number of CTAs (pairs).  With no more tiles than CTAs (pairs) there is
+    // no later tile and the scheduler (its atomics, its slot ring and the round trip that tells every role to stop) is
+    // left out altogether.
+    const int groups = (int)(gridDim.x / CG);
+    const int first_tile = (int)(blockIdx.x / CG);
+    const bool one_wave = num_tiles <= groups;
 
     if (threadIdx.x == 0) {
         sh.abort_flag = 0;
@@ -294,11 +301,13 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
                 if (other != tmem_base) { raise_abort(sh, 8); ok = false; }   // the pair must see one accumulator address
             }
 #endif
-            while (ok) {
+            for (int it = 0; ok; ++it) {
                 int t;
-                if (rank == 0) {
+                if (it == 0) t = first_tile;
+                else if (one_wave) break;
+                else if (rank == 0) {
                     if (!mbar_wait<true>(sempty_bar(q), qphase ^ 1u, sh, 5)) break;
-                    t = atomicAdd(tile_counter, 1);
+                    t = groups + atomicAdd(tile_counter, 1);
                     if (t >= num_tiles) {
                         // Every leader draws exactly one index past the end; the one that draws the last leaves the
                         // counter pair zeroed for the next launch on the stream.
@@ -311,12 +320,13 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
                     mbar_arrive_release_cluster(in_cta(sfull_bar(q), 1u));
 #endif
                     mbar_arrive_release_cluster(in_cta(sfull_bar(q), 0u));
+                    if (++q == SCHED) { q = 0; qphase ^= 1u; }
                 } else {
                     if (!mbar_wait<true>(sfull_bar(q), qphase, sh, 5)) break;
                     t = sched_tile[q];
                     mbar_arrive_release_cluster(in_cta(sempty_bar(q), 0u));
+                    if (++q == SCHED) { q = 0; qphase ^= 1u; }
                 }
-                if (++q == SCHED) { q = 0; qphase ^= 1u; }
                 if (t < 0) break;
                 int mb, nb; tile_coords(t, tiles_m, tiles_n, mb, nb);
                 const int m0 = mb * (BM * CG) + (int)rank * BM;            // first row of A this CTA loads
@@ -355,10 +365,14 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
             int s = 0; unsigned phase = 0;
             int q = 0; unsigned qphase = 0;
             for (int it = 0;; ++it) {
-                if (!mbar_wait<true>(sfull_bar(q), qphase, sh, 6)) break;
-                const int t = sched_tile[q];
-                mbar_arrive_release_cluster(in_cta(sempty_bar(q), 0u));
-                if (++q == SCHED) { q = 0; qphase ^= 1u; }
+                int t = first_tile;
+                if (it > 0) {
+                    if (one_wave) break;
+                    if (!mbar_wait<true>(sfull_bar(q), qphase, sh, 6)) break;
+                    t = sched_tile[q];
+                    mbar_arrive_release_cluster(in_cta(sempty_bar(q), 0u));
+                    if (++q == SCHED) { q = 0; qphase ^= 1u; }
+                }
                 if (t < 0) break;
                 const int a = it & 1;
                 const unsigned aphase = (unsigned)(it >> 1) & 1u;
@@ -391,13 +405,17 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
         G_EPI_INIT
         int q = 0; unsigned qphase = 0;
         for (int it = 0;; ++it) {
-            bool got = mbar_wait<true>(sfull_bar(q), qphase, sh, 7);
-            got = __all_sync(0xffffffffu, got);
-            if (!got) break;
-            const int t = sched_tile[q];
-            __syncwarp();                                     // every lane has read the slot
-            if (lane == 0) mbar_arrive_release_cluster(in_cta(sempty_bar(q), 0u));
-            if (++q == SCHED) { q = 0; qphase ^= 1u; }
+            int t = first_tile;
+            if (it > 0) {
+                if (one_wave) break;
+                bool got = mbar_wait<true>(sfull_bar(q), qphase, sh, 7);
+                got = __all_sync(0xffffffffu, got);
+                if (!got) break;
+                t = sched_tile[q];
+                __syncwarp();                                 // every lane has read the slot
+                if (lane == 0) mbar_arrive_release_cluster(in_cta(sempty_bar(q), 0u));
+                if (++q == SCHED) { q = 0; qphase ^= 1u; }
+            }
             if (t < 0) break;
             int mb, nb; tile_coords(t, tiles_m, tiles_n, mb, nb);
             const int a = it & 1;

@@ -214,7 +214,7 @@ static std::string graph_key(const ormi_b200_ctx* ctx, const ormi_b200_node* nod
     std::string key;
     key.reserve((size_t)n * 48 + 64);
     auto mix = [&](uint64_t v) { const uint32_t w = (uint32_t)v; key.append(reinterpret_cast<const char*>(&w), 4); };
-    mix((uint64_t)n); mix(ctx->fusion ? 1 : 0); mix((uint64_t)ctx->matmul_mode); mix(aligned ? 1 : 0); mix((uint64_t)ctx->tc_cta_group);
+    mix((uint64_t)n); mix((ctx->fusion ? 1 : 0) | (ctx->free_intermediates ? 2 : 0)); mix((uint64_t)ctx->matmul_mode); mix(aligned ? 1 : 0); mix((uint64_t)ctx->tc_cta_group);
     for (int v : ctx->tune) mix((uint64_t)(uint32_t)v);
     mix(lowering_generation());
     for (int i = 0; i < n; ++i) {
@@ -249,6 +249,7 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
         SchedOptions opt;
         opt.num_sms = ctx->num_sms;
         opt.fusion = ctx->fusion;
+        opt.free_intermediates = ctx->free_intermediates;
         opt.bf16_matmul = ctx->matmul_mode == MatmulMode::BF16;
         opt.aligned = aligned;
         std::copy(std::begin(ctx->tune), std::end(ctx->tune), opt.tune);
@@ -267,18 +268,21 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
             std::vector<int> used = s.type == Step::Kernel ? s.k.args : std::vector<int>{s.g.a, s.g.b, s.g.c, s.g.a16, s.g.b16};
             if (s.type == Step::Gemm) used.insert(used.end(), s.g.epi_args.begin(), s.g.epi_args.end());
             for (int b : used) {
-                if (b < 0 || (p.buffers[b].kind != BufKind::Temp && p.buffers[b].kind != BufKind::Twin16)) continue;
+                if (b < 0 || p.buffers[b].kind == BufKind::External || p.buffers[b].kind == BufKind::ErrorWord) continue;
                 if (fresh->first_use[b] < 0) fresh->first_use[b] = (int)si;
                 fresh->last_use[b] = (int)si;
             }
         }
-        for (const NodeResult& r : p.results) { fresh->first_use[r.buffer] = -1; fresh->last_use[r.buffer] = -1; }   // handed out: never scratch
+        // what is handed out is taken from the pool as late as scratch is (a block that scratch gave back may serve it),
+        // but never goes back
+        for (size_t b = 0; b < p.buffers.size(); ++b) if (p.buffers[b].kind == BufKind::NodeOut) fresh->last_use[b] = -1;
+        for (const NodeResult& r : p.results) fresh->last_use[r.buffer] = -1;
         // the bf16 twin of a node that is handed out stays with the context (later calls find it by the fp32 pointer)
         fresh->twin_result.assign(p.buffers.size(), -1);
         for (size_t b = 0; b < p.buffers.size(); ++b) {
             if (p.buffers[b].kind != BufKind::Twin16) continue;
             for (const NodeResult& r : p.results)
-                if (!r.alias && r.node == p.buffers[b].node) { fresh->twin_result[b] = r.buffer; fresh->first_use[b] = -1; fresh->last_use[b] = -1; }
+                if (!r.alias && r.node == p.buffers[b].node) { fresh->twin_result[b] = r.buffer; fresh->last_use[b] = -1; }
         }
         cp = fresh.get();
         ctx->plan_cache[key] = std::move(fresh);
@@ -304,7 +308,7 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
         for (size_t s = 0; s < plan.steps.size(); ++s) {
             const Step& st = plan.steps[s];
             for (size_t b = 0; b < plan.buffers.size(); ++b)
-                if (cp->first_use[b] == (int)s) bufs[b] = pool_alloc(ctx, (size_t)plan.buffers[b].bytes);
+                if (cp->first_use[b] == (int)s && !bufs[b]) bufs[b] = pool_alloc(ctx, (size_t)plan.buffers[b].bytes);
             if (st.type == Step::Kernel) {
                 std::vector<void*> args;
                 for (int a : st.k.args) args.push_back(bufs[a]);

@@ -58,6 +58,16 @@ class StepProgram:
         self.externals: dict[int, str] = {}                # id(node) -> name
         self.ext_ptr: dict[str, tuple[int, int]] = {}      # name -> (ptr, bytes)
         self._keepalive = []
+        # "free": what a phase materializes without being asked for (no root, not flagged keep) is scratch of that call
+        # instead of coming back to be freed here
+        self.intermediates = "keep"
+
+    def _realize_options(self):
+        """Sets the program's "intermediates" option for one realize call; returns what to restore."""
+        before = self.dev.get_option("intermediates") or "keep"
+        if before != self.intermediates:
+            self.dev.set_option("intermediates", self.intermediates)
+        return before
 
     def external(self, name: str, node: G.Node):
         self.dev.ensure_on_device([node])
@@ -70,7 +80,12 @@ class StepProgram:
         ph = _Phase(self.dev, roots, self.produced, self.externals)
         self.phases.append(ph)
         pending = [n for n in ph.order if not n.is_realized]
-        self.dev.realize(list(roots))
+        before = self._realize_options()
+        try:
+            self.dev.realize(list(roots))
+        finally:
+            if before != self.intermediates:
+                self.dev.set_option("intermediates", before)
         for n in pending:               # what this phase wrote to memory: inputs of later phases
             if n.is_realized:
                 self.produced.setdefault(id(n), (n.data.dev_ptr, n.data.nbytes))
@@ -86,7 +101,12 @@ class StepProgram:
             ph.arr[i].data = self.ext_ptr[name][0]
         for i, key in ph.bind_produced:
             ph.arr[i].data = step_outputs[key][0]
-        check(lib.ormi_b200_realize(self.dev.handle, ph.arr, ph.n, ph.ridx, len(ph.roots)))
+        before = self._realize_options()
+        try:
+            check(lib.ormi_b200_realize(self.dev.handle, ph.arr, ph.n, ph.ridx, len(ph.roots)))
+        finally:
+            if before != self.intermediates:
+                self.dev.set_option("intermediates", before)
         for i in range(ph.n):
             c = ph.arr[i]
             if c.flags & (G.NODE_OWNED | G.NODE_ALIAS) and c.data:
@@ -139,6 +159,8 @@ class MLPTrainer:
             node.twin16 = k in ("w1", "w2")
             return node
         if world == 1:
+            # one realize call per step whose roots are all that is read afterwards
+            p.intermediates = "free"
             ups = [weight_update(W.sgd_update(params[k], lr), k) for k in self.names]
             p.add_phase([loss] + ups)
         else:

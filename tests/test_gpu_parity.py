@@ -490,3 +490,28 @@ def test_pool_byte_cap_walks_the_out_of_memory_path():
         dev.free(c, 4 << 20)
     finally:
         dev.close()
+
+
+def test_intermediates_free_reuses_blocks_inside_the_call():
+    """"intermediates=free": a materialized node the caller does not hold is scratch of the realize call — its block is
+    back in the pool for a later step of the same call — and does not come back realized.  Values are unchanged."""
+    from ormi_b200.runtime import Device
+    a_h, b_h = W.normal(0, (512, 512), 0.05), W.normal(1, (512, 512), 0.05)
+    got = {}
+    for mode in ("keep", "free"):
+        dev = Device(0)
+        try:
+            dev.set_option("intermediates", mode)
+            a, b = dev.leaf(a_h), dev.leaf(b_h)
+            p1 = G.matmul(a, b)
+            e1 = G.exp(p1)
+            p2 = G.matmul(e1, b)
+            root = G.exp(p2)
+            before = dev.counter("bytes_allocated")
+            dev.realize([root])
+            got[mode] = (dev.numpy(root), dev.counter("bytes_allocated") - before, [n.is_realized for n in (p1, e1, p2)])
+        finally:
+            dev.close()
+    np.testing.assert_array_equal(got["keep"][0], got["free"][0])
+    assert got["keep"][2] == [True, True, True] and got["free"][2] == [False, False, False]
+    assert got["keep"][1] == 4 << 20 and got["free"][1] == 2 << 20      # the block of p1 serves p2, that of e1 the root

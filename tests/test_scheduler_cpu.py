@@ -415,3 +415,30 @@ def test_first_class_bf16_tensors_cross_realize_calls():
     small = G.mul(G.leaf(W.normal(0, (4, 6))), G.leaf(W.normal(1, (4, 6))))
     small.bf16 = True
     assert "bf16 only when" in RT.plan([small], options="matmul=bf16")["error"]
+
+
+def test_intermediates_free_makes_unheld_nodes_scratch():
+    """With "intermediates=free" only roots (and KEEP nodes) come back; a materialized node nobody outside the call holds
+    — the product x W1 that the backward epilogue reads again, for one — is a scratch buffer of the plan.  Same steps,
+    same values."""
+    loss, params = _mlp(256, 128, 512)
+    roots = [loss] + [W.sgd_update(p, 0.1) for p in params]
+    keep = RT.plan(roots, options="matmul=bf16")
+    free = RT.plan(roots, options="matmul=bf16,intermediates=free")
+    assert not keep["error"] and not free["error"]
+    assert [s["type"] for s in keep["steps"]] == [s["type"] for s in free["steps"]]
+    assert len(free["results"]) == len(roots) < len(keep["results"])
+    dropped = {r["buffer"] for r in keep["results"]} - {r["buffer"] for r in free["results"]}
+    assert dropped and all(free["buffers"][b]["kind"] == "temp" and keep["buffers"][b]["kind"] == "node" for b in dropped)
+    a, _ = E.realize(roots, options="matmul=bf16")
+    b, _ = E.realize(roots, options="matmul=bf16,intermediates=free")
+    for x, y in zip(a, b):
+        assert np.array_equal(x, y)
+    # a node the caller keeps stays a result
+    loss2, params2 = _mlp(64, 32, 64)
+    hidden = loss2
+    while hidden.op != G.OpEnum.MATMUL:
+        hidden = hidden.parents[0]
+    hidden.keep = True
+    plan = RT.plan([loss2], options="intermediates=free")
+    assert len(plan["results"]) == 2
