@@ -24,12 +24,12 @@ const char* kTemplate =
 
 constexpr int kMaxSmem = 232448;     // 227 KB: the opt-in limit of dynamic shared memory per block on sm_100
 
-struct Variant { int cta_group, a_mn, b_mn, wpq, bn, stages, smem; };
+struct Variant { int cta_group, a_mn, b_mn, wpq, bn, tma_store, stages, smem; };
 
-Variant make_variant(int cta_group, int a_mn, int b_mn, int wpq, int bn) {
-    Variant v{cta_group, a_mn, b_mn, wpq, bn, 0, 0};
+Variant make_variant(int cta_group, int a_mn, int b_mn, int wpq, int bn, int tma_store) {
+    Variant v{cta_group, a_mn, b_mn, wpq, bn, tma_store, 0, 0};
     const int stage_bytes = 128 * 64 * 2 + (bn / cta_group) * 64 * 2;
-    const int fixed = 1024 /* alignment slack */ + 4 * wpq * 4096 /* staging */ + 64 /* flags, schedule slots */;
+    const int fixed = 1024 /* alignment slack */ + 4 * wpq * 4096 * (tma_store ? 2 : 1) /* staging */ + 64 /* flags, schedule slots */;
     int s = (kMaxSmem - fixed - 8 * 12) / (stage_bytes + 16);
     v.stages = std::min(s, 8);
     v.smem = fixed + v.stages * stage_bytes + 8 * (2 * v.stages + 12);
@@ -47,6 +47,7 @@ KernelStep make_kernel(const Variant& v, const TcEpilogue* epi) {
     def("G_B_MN", std::to_string(v.b_mn));
     def("G_EPI_WPQ", std::to_string(v.wpq));
     def("G_BN", std::to_string(v.bn));
+    def("G_TMA_STORE", std::to_string(v.tma_store));
     def("G_STAGES", std::to_string(v.stages));
     def("G_EPI_PARAMS", epi ? one_line(epi->params) : "");
     def("G_EPI_INIT", epi ? one_line(epi->init) : "");
@@ -68,12 +69,13 @@ KernelStep make_kernel(const Variant& v, const TcEpilogue* epi) {
 
 // Tensor map over a bf16 matrix stored [rows][ld] (ld >= cols, both multiples of 8); box = 64 contiguous elements
 // (128 bytes, the swizzle span) x box_rows.
-void make_map(ormi_b200_ctx* ctx, CUtensorMap* map, const void* ptr, int rows, int cols, long long ld, int box_rows) {
+// With fp32 = true: a map over an fp32 matrix, box = 32 contiguous elements (the same 128 bytes) x box_rows.
+void make_map(ormi_b200_ctx* ctx, CUtensorMap* map, const void* ptr, int rows, int cols, long long ld, int box_rows, bool fp32 = false) {
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * (fp32 ? 4 : 2)};
+    cuuint32_t box[2] = {fp32 ? 32u : 64u, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    ctx->drv.check(ctx->drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+    ctx->drv.check(ctx->drv.TensorMapEncodeTiled(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
                    "cuTensorMapEncodeTiled");
@@ -186,11 +188,12 @@ void gemm_tc(ormi_b200_ctx* ctx, const void* a16, int a_mn, const void* b16, int
     const int wpq = epi ? epi->wpq : (ctx->tune[TUNE_EPI_WPQ] ? ctx->tune[TUNE_EPI_WPQ] : 1);
     if (wpq != 1 && wpq != 2 && wpq != 4) throw Error("tune.epi_wpq must be 1, 2 or 4");
     // the kernel of this variant: looked up by its few parameters and the epilogue text, not by the whole source
-    std::string vkey = std::to_string(cg) + "|" + std::to_string(a_mn) + "|" + std::to_string(b_mn) + "|" + std::to_string(bn) + "|" + std::to_string(wpq);
+    const int tma_store = epi ? 0 : 1;      // the product itself, nothing else: whole chunks leave through TMA stores
+    std::string vkey = std::to_string(cg) + "|" + std::to_string(a_mn) + "|" + std::to_string(b_mn) + "|" + std::to_string(bn) + "|" + std::to_string(wpq) + "|" + std::to_string(tma_store);
     if (epi) vkey += "|" + std::to_string(epi->unroll) + "|" + epi->params + "|" + epi->init + "|" + epi->cols + "|" + epi->pre + "|" + epi->body + "|" + epi->end;
     auto found = ctx->tc_kernels.find(vkey);
     if (found == ctx->tc_kernels.end()) {
-        const Variant v = make_variant(cg, a_mn, b_mn, wpq, bn);
+        const Variant v = make_variant(cg, a_mn, b_mn, wpq, bn, tma_store);
         const KernelStep made = make_kernel(v, epi);
         TcKernel tk;
         tk.kernel = get_kernel(ctx, made);
@@ -199,7 +202,7 @@ void gemm_tc(ormi_b200_ctx* ctx, const void* a16, int a_mn, const void* b16, int
     }
     CompiledKernel* k = found->second.kernel;
     struct { int block, dyn_smem; } ks{found->second.block, found->second.smem};
-    CUtensorMap map_a, map_b;
+    CUtensorMap map_a, map_b, map_c;
     if (a_mn) make_map(ctx, &map_a, a16, K, M, M, 64);            // stored [K][M]
     else make_map(ctx, &map_a, a16, M, K, K, 128);                // stored [M][K]
     if (b_mn) make_map(ctx, &map_b, b16, K, N, N, 64);            // stored [K][N]
@@ -209,6 +212,7 @@ void gemm_tc(ormi_b200_ctx* ctx, const void* a16, int a_mn, const void* b16, int
     int tiles_m = (M + 128 * cg - 1) / (128 * cg), tiles_n = (N + bn - 1) / bn, num_kb = (K + 63) / 64;
     const int grid = cg * std::min(tiles_m * tiles_n, ctx->num_sms / cg);
     std::vector<void*> argv = {&map_a, &map_b, &C, &M, &N, &num_kb, &tiles_m, &tiles_n, &err, &counter};
+    if (tma_store) { make_map(ctx, &map_c, C, M, N, N, 32, true); argv.push_back(&map_c); }
     std::vector<void*> extra;
     if (epi) { extra = epi->args; for (auto& p : extra) argv.push_back(&p); }
     ctx->drv.check(ctx->drv.LaunchKernel(k->func, (unsigned)grid, 1, 1, (unsigned)ks.block, 1, 1, (unsigned)ks.dyn_smem, (CUstream)ctx->stream,

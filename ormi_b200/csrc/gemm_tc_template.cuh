@@ -58,7 +58,7 @@ constexpr int EPI_UNROLL = G_EPI_UNROLL;
 constexpr int EPI_WARPS = 4 * EPI_WPQ;
 constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNC * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STG_BYTES = 4096;               // per epilogue warp: 32 rows x 128 bytes
+constexpr int STG_BYTES = 4096 * (G_TMA_STORE ? 2 : 1);   // per epilogue warp: 32 rows x 128 bytes (two such buffers when TMA stores them)
 constexpr int GROUP_M = 16 / CG;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
@@ -231,6 +231,9 @@ __cluster_dims__(2, 1, 1)
 #endif
 G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ TensorMap map_b,
               float* __restrict__ C, int M, int N, int num_kb, int tiles_m, int tiles_n, int* err, int* tile_counter
+#if G_TMA_STORE
+              , const __grid_constant__ TensorMap map_c
+#endif
               G_EPI_PARAMS) {
     extern __shared__ unsigned char smem_raw[];
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;       // swizzled tiles need 1024-byte alignment
@@ -403,6 +406,9 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
         const unsigned stg = stg_base + (unsigned)(warp - 2) * STG_BYTES;
         const int cq = lane & 7, rsub = lane >> 3;            // read-back: 8 lanes x 16 bytes per row, 4 rows per instruction
         G_EPI_INIT
+#if G_TMA_STORE
+        int nstore = 0;
+#endif
         int q = 0; unsigned qphase = 0;
         for (int it = 0;; ++it) {
             int t = first_tile;
@@ -425,6 +431,33 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
             if (!ok) break;
             tc_fence_after();
             const int row0 = mb * (BM * CG) + (int)rank * BM + quarter * 32;
+#if G_TMA_STORE
+            // Plain store of the product: the 32 x 32 chunk goes from the swizzled staging buffer to C as one TMA store
+            // (the tensor map clips the M and N tails); two buffers per warp, so the store of a chunk drains while the
+            // next one is read from tensor memory.  The SM's ordinary store path is about half as fast.
+            #pragma unroll 1
+            for (int c = sub; c < BN / 32; c += EPI_WPQ) {
+                const int col0 = nb * BN + c * 32;
+                if (col0 >= N) break;                         // uniform for the warp
+                const unsigned sbuf = stg + (unsigned)(nstore & 1) * 4096u;
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the store before last has read this buffer
+                __syncwarp();
+                unsigned r[32];
+                tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(a * BN + c * 32), r);
+                #pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sbuf + (unsigned)lane * 128u + (unsigned)((i ^ (lane & 7)) << 4)),
+                                 "r"(r[4 * i]), "r"(r[4 * i + 1]), "r"(r[4 * i + 2]), "r"(r[4 * i + 3]) : "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0 && row0 < M) {
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                                 ::"l"(&map_c), "r"(col0), "r"(row0), "r"(sbuf) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                ++nstore;
+            }
+#else
             #pragma unroll 1
             for (int c = sub; c < BN / 32; c += EPI_WPQ) {
                 const int col0 = nb * BN + c * 32;
@@ -453,10 +486,14 @@ G_KERNEL_NAME(const __grid_constant__ TensorMap map_a, const __grid_constant__ T
                 G_EPI_END
                 __syncwarp();                                 // the staging buffer is rewritten by the next chunk
             }
+#endif
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(in_cta(tempty_bar(a), 0u));
         }
+#if G_TMA_STORE
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");    // every store of this warp has landed
+#endif
     }
 
     // ------------------------------------------------------------------ teardown
