@@ -265,9 +265,9 @@ int ormi_b200_selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms);
  *              every node it executes (runtime.cpp:13-39).  "free": only roots and ORMI_NODE_KEEP nodes come back; a
  *              materialized node nobody outside the call holds is scratch, returned to the pool after the last step
  *              that reads it (a later call that reaches it again recomputes it).
- *   "tc_pair": "auto" (default) / "on" (one tcgen05.mma per pair of SMs, 256 x 256 tiles) / "off" (one per SM, 128 x 256).
- *              auto = pairs, except for GEMMs queued while an overlapped all-reduce is in flight: a collective holds
- *              single SMs, and a pair needs both SMs of a TPC.
+ *   "tc_pair": "on" (default: one tcgen05.mma per pair of SMs, 256 x 256 tiles) / "off" (one per SM, 128 x 256) /
+ *              "auto" (pairs, except for GEMMs queued while an overlapped all-reduce is in flight: a collective holds
+ *              single SMs, and a pair needs both SMs of a TPC — measured 5 % slower than "on" on 2 and on 4 GPUs).
  *   "tune.rows_vpt", "tune.rows_minb", "tune.rows_grid", "tune.rows_stage", "tune.rows_nstage", "tune.rows_dynamic",
  *   "tune.flat_unroll", "tune.rows_hoist", "tune.epi_unroll", "tune.epi_wpq", "tune.gemm_bn" (128 / 256 columns per
  *   tensor-core GEMM tile): integer overrides of the code generator's measured defaults, for

@@ -22,6 +22,17 @@ static void need(bool cond, const char* msg) { if (!cond) throw Error(msg); }
 static void bind(ormi_b200_ctx* ctx, const char* who) {
     if (!ctx) throw Error(std::string(who) + ": ctx is NULL");
     ORMI_CUDA(cudaSetDevice(ctx->device));
+    // An error that an earlier runtime call of this thread left behind and nobody consumed (another library in the
+    // process, or a collective library called from here, may do that with a call it expected to fail) must not be
+    // blamed on the next kernel this library launches: it is taken off here and counted.  Sticky errors stay and are
+    // reported by the call that meets them.  ORMI_B200_CHECK_STALE=1 reports the leftover instead, naming the entry
+    // point that found it.
+    const cudaError_t stale = cudaGetLastError();
+    if (stale != cudaSuccess) {
+        static const bool report = std::getenv("ORMI_B200_CHECK_STALE") != nullptr;
+        if (report) throw Error(std::string("CUDA Error: ") + cudaGetErrorString(stale) + " (left behind before " + who + ")");
+        ctx->counters["stale_errors_cleared"]++;
+    }
 }
 
 namespace ormi_b200 {
@@ -88,8 +99,15 @@ int ormi_b200_trim(ormi_b200_ctx* ctx) {
         bind(ctx, "ormi_b200_trim");
         ORMI_CUDA(cudaStreamSynchronize(ctx->stream));
         std::lock_guard<std::mutex> lock(ctx->pool_mutex);
-        for (auto& kv : ctx->free_blocks) for (void* p : kv.second) { cudaFree(p); ctx->pool_held_bytes -= (long long)kv.first; }
+        cudaError_t first = cudaSuccess;
+        for (auto& kv : ctx->free_blocks) for (void* p : kv.second) {
+            const cudaError_t e = cudaFree(p);
+            if (e != cudaSuccess && first == cudaSuccess) first = e;
+            ctx->pool_held_bytes -= (long long)kv.first;
+        }
         ctx->free_blocks.clear();
+        ctx->pooled.clear();
+        if (first != cudaSuccess) { cudaGetLastError(); throw Error(std::string("CUDA Error: ") + cudaGetErrorString(first) + " (cudaFree of a pool block)"); }
     });
 }
 
@@ -442,8 +460,8 @@ int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value)
             // exhausted (0 = no limit): lets a host test walk the out-of-memory path without exhausting a GPU
             ctx->pool_limit_bytes = std::atoll(v.c_str());
         } else if (k == "tc_pair") {
-            // bf16 GEMM: "on" = one tcgen05.mma per pair of SMs (256 x 256 tiles), "off" = one per SM (128 x 256), "auto"
-            // (default) = pairs, except while an overlapped all-reduce is in flight beside the GEMM
+            // bf16 GEMM: "on" (default) = one tcgen05.mma per pair of SMs (256 x 256 tiles), "off" = one per SM (128 x 256),
+            // "auto" = pairs, except while an overlapped all-reduce is in flight beside the GEMM
             if (v == "auto") { ctx->tc_cta_group = 2; ctx->tc_pair_auto = true; }
             else if (v == "on") { ctx->tc_cta_group = 2; ctx->tc_pair_auto = false; }
             else if (v == "off") { ctx->tc_cta_group = 1; ctx->tc_pair_auto = false; }

@@ -10,6 +10,7 @@
 #include <stdexcept>
 #include <string>
 #include <unordered_map>
+#include <unordered_set>
 #include <vector>
 
 #include "plan.h"
@@ -93,6 +94,7 @@ struct ormi_b200_ctx {
     std::mutex pool_mutex;
     long long pool_limit_bytes = 0, pool_held_bytes = 0;   // option "pool_limit_bytes": simulated memory exhaustion
     std::unordered_map<size_t, std::vector<void*>> free_blocks;
+    std::unordered_set<void*> pooled;      // every block that sits in free_blocks: a block returned twice is caught, not handed to two owners
 
     std::unordered_map<std::string, ormi_b200::CompiledKernel> kernel_cache;   // source hash -> module
     std::unordered_map<std::string, std::unique_ptr<ormi_b200::CachedPlan>> plan_cache;   // by graph_key (runtime.cu)
@@ -106,7 +108,7 @@ struct ormi_b200_ctx {
     std::unordered_map<const void*, ormi_b200::Shadow16> shadows;
     std::unordered_map<std::string, ormi_b200::TcKernel> tc_kernels;   // compiled variants of the tensor-core GEMM
     int tc_cta_group = 2;             // CTAs per tcgen05.mma of the bf16 GEMM: 2 = a pair of SMs per 256 x 256 tile
-    bool tc_pair_auto = true;         // ... but one SM per MMA while a collective of the second stream may run beside the GEMM
+    bool tc_pair_auto = false;        // "auto": one SM per MMA while a collective of the second stream may run beside the GEMM (measured slower: off by default)
     int comm_inflight = 0;            // overlapped all-reduces queued and not yet waited for (host order = stream order)
     int comm_last_mark = -1;
     // kErrorWords ints: word 0 is the error word, word kTileCounterWord (its own 128-byte line) the GEMM's tile counter

@@ -54,6 +54,7 @@ void* pool_alloc(ormi_b200_ctx* ctx, size_t bytes) {
         if (it != ctx->free_blocks.end() && !it->second.empty()) {
             void* p = it->second.back();
             it->second.pop_back();
+            ctx->pooled.erase(p);
             ctx->counters["pool_hits"]++;
             return p;
         }
@@ -68,6 +69,7 @@ void* pool_alloc(ormi_b200_ctx* ctx, size_t bytes) {
             cudaStreamSynchronize(ctx->stream);
             for (auto& kv : ctx->free_blocks) for (void* q : kv.second) { cudaFree(q); ctx->pool_held_bytes -= (long long)kv.first; }
             ctx->free_blocks.clear();
+            ctx->pooled.clear();
             ctx->counters["pool_trims"]++;
         }
         e = over_limit() ? cudaErrorMemoryAllocation : cudaMalloc(&p, bytes);
@@ -83,6 +85,7 @@ void pool_free(ormi_b200_ctx* ctx, void* ptr, size_t bytes) {
     if (bytes == 0) bytes = 4;
     shadow_drop(ctx, ptr, bytes);      // a bf16 twin of this buffer goes back to the pool with it
     std::lock_guard<std::mutex> lock(ctx->pool_mutex);
+    if (!ctx->pooled.insert(ptr).second) throw Error("internal: a pool block was returned twice (" + std::to_string(bytes) + " bytes)");
     ctx->free_blocks[bytes].push_back(ptr);
 }
 

@@ -71,8 +71,8 @@ class Device:
         self._options[key] = value
 
     def get_option(self, key: str) -> str:
-        """The value last set through this object (the defaults: "matmul" "fp32", "fusion" "on", "tc_pair" "auto", "intermediates" "keep")."""
-        return self._options.get(key, {"matmul": "fp32", "fusion": "on", "tc_pair": "auto", "intermediates": "keep"}.get(key, ""))
+        """The value last set through this object (the defaults: "matmul" "fp32", "fusion" "on", "tc_pair" "on", "intermediates" "keep")."""
+        return self._options.get(key, {"matmul": "fp32", "fusion": "on", "tc_pair": "on", "intermediates": "keep"}.get(key, ""))
 
     def counter(self, name: str) -> int:
         v = ctypes.c_int64()
