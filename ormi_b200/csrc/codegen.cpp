@@ -591,11 +591,17 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         else if (li[l].elem) emit_array_load(l, ro, "        ", row_pred);
         else s << "        const float L" << l << " = " << (row_pred ? "rok ? " : "") << "in" << l << "[" << ro << "]" << (row_pred ? " : 0.0f" : "") << ";\n";
     }
-    if (stages) {
-        // every thread now holds its part of the row: the stage of the previous row can be refilled
-        s << "        if (__syncthreads_or(!arrived)) {\n            if (threadIdx.x == 0) atomicExch(err, 101);\n            ormi_drain();\n            break;\n        }\n";
-        s << "        if (threadIdx.x == 0 && it + " << stages - 1 << " < n_mine) { ormi_async_fence(); issue(it + " << stages - 1 << "); }\n";
-    }
+    // The stage that the next bulk copy refills was read at the top of an earlier row, and every thread has passed a block
+    // barrier since then if the row body has one (a reduction level over more than one warp).  The vote on whether this
+    // row's copy arrived then rides on the first such barrier instead of costing one of its own; until then the row's
+    // values are only summed, nothing is stored.
+    bool level_barrier = false;
+    if (NW > 1) for (const KNode& kn : spec.nodes) if (kn.op == KNode::OP_ROWSUM) level_barrier = true;
+    const std::string arrival_vote =
+        "        if (__syncthreads_or(!arrived)) {\n            if (threadIdx.x == 0) atomicExch(err, 101);\n            ormi_drain();\n            break;\n        }\n"
+        "        if (threadIdx.x == 0 && it + " + std::to_string(stages - 1) + " < n_mine) { ormi_async_fence(); issue(it + " + std::to_string(stages - 1) + "); }\n";
+    bool vote_pending = stages > 0;
+    if (stages && !level_barrier) { s << arrival_vote; vote_pending = false; }
     for (const KNode& kn : spec.nodes) if (!rowv(&kn)) s << "        float v" << kn.node << "[" << VPT << "];\n";
 
     auto ok_expr = [&](const std::string& j) {
@@ -603,6 +609,39 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         if (row_pred) p = "rok";
         if (col_pred) p += std::string(p.empty() ? "" : " && ") + "(" + col_of(j + " / " + std::to_string(V), j + " % " + std::to_string(V)) + ") < " + std::to_string(C);
         return p;
+    };
+    // An output is written as soon as its value exists (at the end of the level that computes it), not after the last
+    // level: a block barrier keeps the compiler from moving a store up, so a late store holds its registers through every
+    // level in between.  Nothing is stored before the arrival vote of a staged row.
+    std::vector<bool> out_done(spec.outputs.size(), false);
+    auto emit_output = [&](size_t o) {
+        const KOutput& ko = spec.outputs[o];
+        bool elem = is_elem(ko.value);
+        if (ko.kind == KOutput::FULL) {
+            s << "        #pragma unroll\n        for (int q = 0; q < " << NV << "; ++q) {\n            const int col = " << col_of("q", "0") << ";\n";
+            std::string pred;
+            if (row_pred) pred = "rok";
+            if (col_pred) pred += std::string(pred.empty() ? "" : " && ") + "col < " + std::to_string(C);
+            auto v = [&](int e) { return elem ? ref(ko.value, std::to_string(V) + " * q + " + std::to_string(e)) : ref(ko.value, "0"); };
+            s << "            " << (pred.empty() ? "" : "if (" + pred + ") ") << "{\n";
+            if (V == 4) {
+                if (ko.store) s << "                *reinterpret_cast<float4*>(out" << o << " + r * " << C << " + col) = make_float4(" << v(0) << ", " << v(1) << ", " << v(2) << ", " << v(3) << ");\n";
+                if (ko.twin) s << "                ormi_store_bf16x4(out16_" << o << " + r * " << C << " + col, " << v(0) << ", " << v(1) << ", " << v(2) << ", " << v(3) << ");\n";
+            } else {
+                if (ko.store) s << "                out" << o << "[r * " << C << " + col] = " << v(0) << ";\n";
+                if (ko.twin) s << "                out16_" << o << "[r * " << C << " + col] = ormi_bf16(" << v(0) << ");\n";
+            }
+            s << "            }\n        }\n";
+        } else if (ko.kind == KOutput::ROW) {
+            s << "        if (tid == 0" << (row_pred ? " && rok" : "") << ") out" << o << "[r] = " << ref(ko.value, "0") << ";\n";
+        } else if (ko.kind == KOutput::COLSUM) {
+            s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) cacc" << o << "[j] = "
+              << red_comb(ko.is_max, "cacc" + std::to_string(o) + "[j]", row_pred ? "(rok ? " + ref(ko.value, "j") + " : " + red_ident(ko.is_max) + ")" : ref(ko.value, "j")) << ";\n";
+        } else {
+            s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) {\n";
+            std::string ok = ok_expr("j");
+            s << "            gacc" << o << " = " << red_comb(ko.is_max, "gacc" + std::to_string(o), ok.empty() ? ref(ko.value, "j") : "((" + ok + ") ? " + ref(ko.value, "j") + " : " + red_ident(ko.is_max) + ")") << ";\n        }\n";
+        }
     };
     const bool custom_div = lowering_for(ORMI_OP_DIV, nullptr);     // a registered lowering for DIV is emitted as written
     for (int lv = 0; lv <= max_level; ++lv) {
@@ -652,42 +691,19 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
             if (NW > 1) {
                 s << "        if ((threadIdx.x & 31) == 0) {";
                 for (size_t i = 0; i < sums.size(); ++i) s << " red[rpar][" << lv << "][" << i << "][grp][tid >> 5] = v" << sums[i]->node << ";";
-                s << " }\n        __syncthreads();\n";
+                s << " }\n";
+                if (vote_pending) { s << arrival_vote; vote_pending = false; }
+                else s << "        __syncthreads();\n";
                 for (size_t i = 0; i < sums.size(); ++i)
                     s << "        { float a = " << red_ident(sums[i]->is_max) << "; for (int w = 0; w < " << NW << "; ++w) a = " << red_comb(sums[i]->is_max, "a", "red[rpar][" + std::to_string(lv) + "][" + std::to_string(i) + "][grp][w]") << "; v" << sums[i]->node << " = a; }\n";
             }
         }
+        if (!vote_pending)
+            for (size_t o = 0; o < spec.outputs.size(); ++o)
+                if (!out_done[o] && ref_level(spec.outputs[o].value) <= lv) { emit_output(o); out_done[o] = true; }
     }
-    // outputs
-    for (size_t o = 0; o < spec.outputs.size(); ++o) {
-        const KOutput& ko = spec.outputs[o];
-        bool elem = is_elem(ko.value);
-        if (ko.kind == KOutput::FULL) {
-            s << "        #pragma unroll\n        for (int q = 0; q < " << NV << "; ++q) {\n            const int col = " << col_of("q", "0") << ";\n";
-            std::string pred;
-            if (row_pred) pred = "rok";
-            if (col_pred) pred += std::string(pred.empty() ? "" : " && ") + "col < " + std::to_string(C);
-            auto v = [&](int e) { return elem ? ref(ko.value, std::to_string(V) + " * q + " + std::to_string(e)) : ref(ko.value, "0"); };
-            s << "            " << (pred.empty() ? "" : "if (" + pred + ") ") << "{\n";
-            if (V == 4) {
-                if (ko.store) s << "                *reinterpret_cast<float4*>(out" << o << " + r * " << C << " + col) = make_float4(" << v(0) << ", " << v(1) << ", " << v(2) << ", " << v(3) << ");\n";
-                if (ko.twin) s << "                ormi_store_bf16x4(out16_" << o << " + r * " << C << " + col, " << v(0) << ", " << v(1) << ", " << v(2) << ", " << v(3) << ");\n";
-            } else {
-                if (ko.store) s << "                out" << o << "[r * " << C << " + col] = " << v(0) << ";\n";
-                if (ko.twin) s << "                out16_" << o << "[r * " << C << " + col] = ormi_bf16(" << v(0) << ");\n";
-            }
-            s << "            }\n        }\n";
-        } else if (ko.kind == KOutput::ROW) {
-            s << "        if (tid == 0" << (row_pred ? " && rok" : "") << ") out" << o << "[r] = " << ref(ko.value, "0") << ";\n";
-        } else if (ko.kind == KOutput::COLSUM) {
-            s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) cacc" << o << "[j] = "
-              << red_comb(ko.is_max, "cacc" + std::to_string(o) + "[j]", row_pred ? "(rok ? " + ref(ko.value, "j") + " : " + red_ident(ko.is_max) + ")" : ref(ko.value, "j")) << ";\n";
-        } else {
-            s << "        #pragma unroll\n        for (int j = 0; j < " << VPT << "; ++j) {\n";
-            std::string ok = ok_expr("j");
-            s << "            gacc" << o << " = " << red_comb(ko.is_max, "gacc" + std::to_string(o), ok.empty() ? ref(ko.value, "j") : "((" + ok + ") ? " + ref(ko.value, "j") + " : " + red_ident(ko.is_max) + ")") << ";\n        }\n";
-        }
-    }
+    if (vote_pending) { s << arrival_vote; vote_pending = false; }
+    for (size_t o = 0; o < spec.outputs.size(); ++o) if (!out_done[o]) { emit_output(o); out_done[o] = true; }
     if (use_red) s << "        rpar ^= 1;\n";
     s << "    }\n";
     if (dyn_rows)   // every block drew exactly one index past the end; the last one to say so leaves the pair at zero
