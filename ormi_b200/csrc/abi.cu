@@ -251,29 +251,7 @@ int ormi_b200_plan_json_opts(const ormi_b200_node* nodes, int n_nodes, const int
                              char* buf, size_t cap, size_t* out_len) {
     return guarded([&] {
         need(nodes && roots && n_nodes > 0 && n_roots > 0, "ormi_b200_plan_json_opts: bad arguments");
-        SchedOptions opt;
-        std::string text = options ? options : "";
-        size_t pos = 0;
-        while (pos < text.size()) {
-            size_t end = text.find(',', pos);
-            if (end == std::string::npos) end = text.size();
-            const std::string item = text.substr(pos, end - pos);
-            pos = end + 1;
-            const size_t eq = item.find('=');
-            if (eq == std::string::npos) throw Error("option without a value: " + item);
-            const std::string k = item.substr(0, eq), v = item.substr(eq + 1);
-            if (k == "matmul") opt.bf16_matmul = (v == "bf16");
-            else if (k == "fusion") opt.fusion = (v != "off");
-            else if (k == "intermediates") opt.free_intermediates = (v == "free");
-            else if (k == "aligned") opt.aligned = (v != "0");
-            else if (k.rfind("tune.", 0) == 0) {
-                static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist", "epi_unroll", "epi_wpq", "gemm_bn"};
-                int which = -1;
-                for (int i = 0; i < kTuneKnobs; ++i) if (k.substr(5) == names[i]) which = i;
-                if (which < 0) throw Error("unknown option: " + k);
-                opt.tune[which] = std::atoi(v.c_str());
-            } else throw Error("unknown option: " + k);
-        }
+        const SchedOptions opt = parse_sched_options(options);
         Plan p = build_plan(nodes, n_nodes, roots, n_roots, opt);
         std::string js = plan_to_json(p);
         if (out_len) *out_len = js.size();
@@ -459,6 +437,9 @@ int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value)
             // refuse allocations that would take the pool past this many bytes, as the driver does when memory is
             // exhausted (0 = no limit): lets a host test walk the out-of-memory path without exhausting a GPU
             ctx->pool_limit_bytes = std::atoll(v.c_str());
+        } else if (k == "pool_canary") {
+            // debugging aid: a 256-byte guard zone behind every block taken from now on, checked when the block comes back
+            if (v == "on") ctx->pool_canary = true; else if (v == "off") ctx->pool_canary = false; else throw Error("pool_canary must be on or off");
         } else if (k == "tc_pair") {
             // bf16 GEMM: "on" (default) = one tcgen05.mma per pair of SMs (256 x 256 tiles), "off" = one per SM (128 x 256),
             // "auto" = pairs, except while an overlapped all-reduce is in flight beside the GEMM
@@ -468,9 +449,7 @@ int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value)
             else throw Error("tc_pair must be auto, on or off");
         } else if (k.rfind("tune.", 0) == 0) {
             // overrides of the code generator's measured defaults (experiments); "0" restores the default
-            static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic", "flat_unroll", "rows_hoist", "epi_unroll", "epi_wpq", "gemm_bn"};
-            int which = -1;
-            for (int i = 0; i < kTuneKnobs; ++i) if (k.substr(5) == names[i]) which = i;
+            const int which = tune_knob_index(k.substr(5));
             if (which < 0) throw Error("unknown option: " + k);
             ctx->tune[which] = std::atoi(v.c_str());
         } else if (k == "fusion") {

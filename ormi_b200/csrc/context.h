@@ -94,6 +94,8 @@ struct ormi_b200_ctx {
     std::mutex pool_mutex;
     long long pool_limit_bytes = 0, pool_held_bytes = 0;   // option "pool_limit_bytes": simulated memory exhaustion
     std::unordered_map<size_t, std::vector<void*>> free_blocks;
+    bool pool_canary = false;              // option "pool_canary": a guard zone behind every block, checked when the block comes back
+    std::unordered_map<void*, size_t> canaries;   // block -> bytes asked for, of the blocks that carry a guard zone
     std::unordered_set<void*> pooled;      // every block that sits in free_blocks: a block returned twice is caught, not handed to two owners
 
     std::unordered_map<std::string, ormi_b200::CompiledKernel> kernel_cache;   // source hash -> module

@@ -23,6 +23,7 @@
 #include <map>
 #include <set>
 #include <sstream>
+#include <stdexcept>
 
 #include "kernel_ir.h"
 #include "plan.h"
@@ -960,6 +961,36 @@ std::string json_escape(const std::string& s) {
 }
 
 }  // namespace
+
+int tune_knob_index(const std::string& name) {
+    static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic",
+                                            "flat_unroll", "rows_hoist", "epi_unroll", "epi_wpq", "gemm_bn"};
+    for (int i = 0; i < kTuneKnobs; ++i) if (name == names[i]) return i;
+    return -1;
+}
+
+SchedOptions parse_sched_options(const char* options) {
+    SchedOptions opt;
+    const std::string text = options ? options : "";
+    size_t pos = 0;
+    while (pos < text.size()) {
+        size_t end = text.find(',', pos);
+        if (end == std::string::npos) end = text.size();
+        const std::string item = text.substr(pos, end - pos);
+        pos = end + 1;
+        if (item.empty()) continue;
+        const size_t eq = item.find('=');
+        if (eq == std::string::npos) throw std::runtime_error("option without a value: " + item);
+        const std::string k = item.substr(0, eq), v = item.substr(eq + 1);
+        if (k == "matmul") opt.bf16_matmul = (v == "bf16");
+        else if (k == "fusion") opt.fusion = (v != "off");
+        else if (k == "intermediates") opt.free_intermediates = (v == "free");
+        else if (k == "aligned") opt.aligned = (v != "0");
+        else if (k.rfind("tune.", 0) == 0 && tune_knob_index(k.substr(5)) >= 0) opt.tune[tune_knob_index(k.substr(5))] = std::atoi(v.c_str());
+        else throw std::runtime_error("unknown option: " + k);
+    }
+    return opt;
+}
 
 Plan build_plan(const ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots, const SchedOptions& opt) {
     Scheduler s(nodes, n_nodes, opt);

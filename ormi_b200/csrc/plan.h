@@ -98,6 +98,11 @@ struct SchedOptions {
 };
 
 Plan build_plan(const ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots, const SchedOptions& opt);
+// "rows_vpt" -> TUNE_ROWS_VPT, ...; -1 for a name that is no knob.
+int tune_knob_index(const std::string& name);
+// "matmul=bf16,fusion=on,intermediates=free,aligned=0,tune.rows_vpt=8": the schedule-shaping options as one string (what
+// ormi_b200_plan_json_opts takes).  Throws std::runtime_error on an unknown key.
+SchedOptions parse_sched_options(const char* text);
 std::string plan_to_json(const Plan& plan);
 
 // The reference-shaped single-kernel compiler (ormi::cuda::compile): guarded scalar `fused_kernel`.

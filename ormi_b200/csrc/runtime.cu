@@ -46,37 +46,52 @@ void DriverApi::check(CUresult r, const char* what) const {
 }
 
 // ------------------------------------------------------------------------------------------------ pool
-void* pool_alloc(ormi_b200_ctx* ctx, size_t bytes) {
-    if (bytes == 0) bytes = 4;
+// Debug option "pool_canary": every block gets kCanaryBytes more than was asked for, filled with a pattern; when the block
+// comes back the pattern is read (a synchronous copy: slow, a debugging aid) and an overwritten zone is reported with the
+// block's size — a kernel that wrote past the end of its output.  The pool is keyed by the real size.
+constexpr size_t kCanaryBytes = 256;
+constexpr int kCanaryByte = 0xA5;
+
+void* pool_alloc(ormi_b200_ctx* ctx, size_t asked) {
+    if (asked == 0) asked = 4;
+    const bool canary = ctx->pool_canary;
+    const size_t bytes = asked + (canary ? kCanaryBytes : 0);
+    void* p = nullptr;
     {
         std::lock_guard<std::mutex> lock(ctx->pool_mutex);
         auto it = ctx->free_blocks.find(bytes);
         if (it != ctx->free_blocks.end() && !it->second.empty()) {
-            void* p = it->second.back();
+            p = it->second.back();
             it->second.pop_back();
             ctx->pooled.erase(p);
             ctx->counters["pool_hits"]++;
-            return p;
         }
     }
-    void* p = nullptr;
-    auto over_limit = [&]() { return ctx->pool_limit_bytes > 0 && ctx->pool_held_bytes + (long long)bytes > ctx->pool_limit_bytes; };
-    cudaError_t e = over_limit() ? cudaErrorMemoryAllocation : cudaMalloc(&p, bytes);
-    if (e == cudaErrorMemoryAllocation) {   // give cached blocks back and try once more
-        cudaGetLastError();
-        {
-            std::lock_guard<std::mutex> lock(ctx->pool_mutex);
-            cudaStreamSynchronize(ctx->stream);
-            for (auto& kv : ctx->free_blocks) for (void* q : kv.second) { cudaFree(q); ctx->pool_held_bytes -= (long long)kv.first; }
-            ctx->free_blocks.clear();
-            ctx->pooled.clear();
-            ctx->counters["pool_trims"]++;
+    if (!p) {
+        auto over_limit = [&]() { return ctx->pool_limit_bytes > 0 && ctx->pool_held_bytes + (long long)bytes > ctx->pool_limit_bytes; };
+        cudaError_t e = over_limit() ? cudaErrorMemoryAllocation : cudaMalloc(&p, bytes);
+        if (e == cudaErrorMemoryAllocation) {   // give cached blocks back and try once more
+            cudaGetLastError();
+            {
+                std::lock_guard<std::mutex> lock(ctx->pool_mutex);
+                cudaStreamSynchronize(ctx->stream);
+                for (auto& kv : ctx->free_blocks) for (void* q : kv.second) { cudaFree(q); ctx->pool_held_bytes -= (long long)kv.first; }
+                ctx->free_blocks.clear();
+                ctx->pooled.clear();
+                ctx->counters["pool_trims"]++;
+            }
+            e = over_limit() ? cudaErrorMemoryAllocation : cudaMalloc(&p, bytes);
         }
-        e = over_limit() ? cudaErrorMemoryAllocation : cudaMalloc(&p, bytes);
+        if (e != cudaSuccess) throw Error(std::string("CUDA Error: ") + cudaGetErrorString(e) + " (allocating " + std::to_string(bytes) + " bytes)");
+        ctx->counters["bytes_allocated"] += (int64_t)bytes;
+        ctx->pool_held_bytes += (long long)bytes;
     }
-    if (e != cudaSuccess) throw Error(std::string("CUDA Error: ") + cudaGetErrorString(e) + " (allocating " + std::to_string(bytes) + " bytes)");
-    ctx->counters["bytes_allocated"] += (int64_t)bytes;
-    ctx->pool_held_bytes += (long long)bytes;
+    if (canary) {
+        const cudaError_t e = cudaMemsetAsync((char*)p + asked, kCanaryByte, kCanaryBytes, ctx->stream);
+        if (e != cudaSuccess) { pool_free(ctx, p, bytes); throw Error(std::string("CUDA Error: ") + cudaGetErrorString(e) + " (filling a guard zone)"); }
+        std::lock_guard<std::mutex> lock(ctx->pool_mutex);
+        ctx->canaries[p] = asked;
+    }
     return p;
 }
 
@@ -84,9 +99,28 @@ void pool_free(ormi_b200_ctx* ctx, void* ptr, size_t bytes) {
     if (!ptr) return;
     if (bytes == 0) bytes = 4;
     shadow_drop(ctx, ptr, bytes);      // a bf16 twin of this buffer goes back to the pool with it
-    std::lock_guard<std::mutex> lock(ctx->pool_mutex);
-    if (!ctx->pooled.insert(ptr).second) throw Error("internal: a pool block was returned twice (" + std::to_string(bytes) + " bytes)");
-    ctx->free_blocks[bytes].push_back(ptr);
+    bool guarded_block = false;
+    {
+        std::lock_guard<std::mutex> lock(ctx->pool_mutex);
+        auto it = ctx->canaries.find(ptr);
+        if (it != ctx->canaries.end()) { guarded_block = true; bytes = it->second; ctx->canaries.erase(it); }
+    }
+    std::string damage;
+    if (guarded_block) {
+        unsigned char zone[kCanaryBytes];
+        cudaError_t e = cudaMemcpyAsync(zone, (const char*)ptr + bytes, kCanaryBytes, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) damage = std::string("CUDA Error: ") + cudaGetErrorString(e) + " (reading a guard zone)";
+        else for (size_t i = 0; i < kCanaryBytes; ++i)
+            if (zone[i] != kCanaryByte) { damage = "guard zone behind a " + std::to_string(bytes) + "-byte block overwritten at byte +" + std::to_string(i); break; }
+        bytes += kCanaryBytes;
+    }
+    {
+        std::lock_guard<std::mutex> lock(ctx->pool_mutex);
+        if (!ctx->pooled.insert(ptr).second) throw Error("internal: a pool block was returned twice (" + std::to_string(bytes) + " bytes)");
+        ctx->free_blocks[bytes].push_back(ptr);
+    }
+    if (!damage.empty()) { ctx->counters["canary_hits"]++; throw Error(damage); }
 }
 
 // ------------------------------------------------------------------------------------------------ NVRTC

@@ -35,7 +35,7 @@ class Device:
 
     def free(self, ptr: int, nbytes: int):
         if self.handle:
-            lib.ormi_b200_free(self.handle, ctypes.c_void_p(ptr), nbytes)
+            check(lib.ormi_b200_free(self.handle, ctypes.c_void_p(ptr), nbytes))
 
     def h2d(self, ptr: int, array: np.ndarray):
         check(lib.ormi_b200_memcpy_h2d(self.handle, ctypes.c_void_p(ptr), array.ctypes.data_as(ctypes.c_void_p), array.nbytes))

@@ -515,3 +515,39 @@ def test_intermediates_free_reuses_blocks_inside_the_call():
     np.testing.assert_array_equal(got["keep"][0], got["free"][0])
     assert got["keep"][2] == [True, True, True] and got["free"][2] == [False, False, False]
     assert got["keep"][1] == 4 << 20 and got["free"][1] == 2 << 20      # the block of p1 serves p2, that of e1 the root
+
+
+def test_pool_canary_reports_a_write_past_the_end_of_a_block():
+    """"pool_canary": every block carries a guard zone that is read back when the block returns.  Odd-shaped graphs leave
+    the zones alone (the generated kernels' bounds predicates hold); a write past the end of a block — made here through
+    the ABI, inside the block's own allocation, so nothing faults — is reported by the call that returns the block."""
+    import gc
+    from ormi_b200.runtime import Device
+    dev = Device(0)
+    try:
+        dev.set_option("pool_canary", "on")
+        for shape in ((5, 33), (7, 1001), (3, 4097), (130, 250)):
+            x = dev.leaf(W.normal(0, shape), True)
+            g, b = dev.leaf(W.normal(1, shape[-1:]), True), dev.leaf(W.normal(2, shape[-1:]), True)
+            y = W.layernorm(x, g, b)
+            y.grad = dev.leaf(W.normal(3, shape))
+            G.compute_gradients(y)
+            s = G.sum_(G.mul(x, x), [0], False)
+            m = G.matmul(G.transpose(x, [1, 0]), y)
+            dev.realize([y, x.grad, g.grad, b.grad, s, m])
+            ref = W.normal(0, shape).astype(np.float64)
+            np.testing.assert_allclose(dev.numpy(s), (ref * ref).sum(0), rtol=1e-5)
+            del x, g, b, y, s, m
+            gc.collect()
+        dev.sync()
+        assert dev.counter("canary_hits") == 0
+        p = dev.alloc(1000)
+        check_bytes = np.zeros(2, np.float32)
+        dev.h2d(p + 1000, check_bytes)                          # 8 bytes past the end: inside the guard zone
+        with pytest.raises(RuntimeError, match="guard zone behind a 1000-byte block"):
+            dev.free(p, 1000)
+        assert dev.counter("canary_hits") == 1
+        q = dev.alloc(1000)                                     # the block is back in the pool and usable
+        dev.free(q, 1000)
+    finally:
+        dev.close()
