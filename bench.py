@@ -503,6 +503,7 @@ def main():
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--no-extras", action="store_true", help="skip the matmul sweep and the MLP training steps")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--e2e-chunk", type=int, default=1024, help="rows per chunk of the pipelined end-to-end step (a divisor of 16384)")
     ap.add_argument("--set", default="", help="with --only mlp_sharded: backend options for the run, key=value,key=value")
     args = ap.parse_args()
     # Libraries (NCCL's version banner, for one) print to stdout; the contract is ONE JSON line there.  Everything but
@@ -620,7 +621,7 @@ def main():
     # runs in chunks of E2E_CHUNK rows — uploads on the upload stream, the kernels of chunk k as soon as its rows have
     # arrived, its results back on the download stream while later chunks upload and compute.  dg, db come back as one
     # partial per chunk and are added on the host (and, with N > 1, summed over the ranks on the device first).
-    E2E_CHUNK = 1024
+    E2E_CHUNK = args.e2e_chunk
     n_chunks = R // E2E_CHUNK
     host_in = {k: torch.from_numpy(np.ascontiguousarray(v.data.host if v.data.host is not None else dev.download(v.data))).pin_memory()
                for k, v in inputs.items()}
