@@ -557,10 +557,9 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     } else {
         if (dyn_rows) {
             s << "    __shared__ int nextrb[2];\n    int* const rowctr = err + " << kRowCounterWord << ";\n";
-            // the first rows of a block are its own index (no round trip to the counter before the first load); the counter
-            // hands out what lies behind the grid's first pass
-            s << "    for (int it = 0;; ++it) {\n        const int rb = it == 0 ? (int)blockIdx.x * " << G << " : nextrb[it & 1];\n        if (rb >= " << R << ") break;\n";
-            s << "        if (threadIdx.x == 0) nextrb[(it + 1) & 1] = (int)gridDim.x * " << G << " + atomicAdd(rowctr, " << G << ");     // visible after this row's barriers\n";
+            s << "    if (threadIdx.x == 0) nextrb[0] = atomicAdd(rowctr, " << G << ");\n    __syncthreads();\n";
+            s << "    for (int it = 0;; ++it) {\n        const int rb = nextrb[it & 1];\n        if (rb >= " << R << ") break;\n";
+            s << "        if (threadIdx.x == 0) nextrb[(it + 1) & 1] = atomicAdd(rowctr, " << G << ");     // visible after this row's barriers\n";
         } else {
             s << "    for (int rb = blockIdx.x * " << G << "; rb < " << R << "; rb += gridDim.x * " << G << ") {\n";
         }
