@@ -274,7 +274,7 @@ int ormi_b200_selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms);
  *              single SMs, and a pair needs both SMs of a TPC — measured 5 % slower than "on" on 2 and on 4 GPUs).
  *   "tune.rows_vpt", "tune.rows_minb", "tune.rows_grid", "tune.rows_stage", "tune.rows_nstage", "tune.rows_dynamic",
  *   "tune.flat_unroll", "tune.rows_hoist", "tune.epi_unroll", "tune.epi_wpq", "tune.gemm_bn" (128 / 256 columns per
- *   tensor-core GEMM tile): integer overrides of the code generator's measured defaults, for
+ *   tensor-core GEMM tile), "tune.epi_node_major" (1: GEMM epilogue text column by column instead of node by node): integer overrides of the code generator's measured defaults, for
  *              experiments ("0" = default; for the on/off ones 1 = off, 2 = on). */
 int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value);
 

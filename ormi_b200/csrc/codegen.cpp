@@ -65,6 +65,16 @@ __device__ __forceinline__ float ormi_pow(float x, float y) {
     if (y == -1.0f) return __fdiv_rn(1.0f, x);
     return ormi_pow_general(x, y);
 }
+// The same for four values and one exponent: one chain of comparisons for the four, and the four results of the branch
+// taken are independent instruction streams (GEMM epilogues, where every branch splits what the compiler may interleave).
+__device__ __forceinline__ void ormi_pow4(const float* x, float y, float* out) {
+    if (y == 0.5f) { for (int j = 0; j < 4; ++j) out[j] = sqrtf(x[j]); }
+    else if (y == 2.0f) { for (int j = 0; j < 4; ++j) out[j] = __fmul_rn(x[j], x[j]); }
+    else if (y == 3.0f) { for (int j = 0; j < 4; ++j) out[j] = ormi_cube(x[j]); }
+    else if (y == 1.0f) { for (int j = 0; j < 4; ++j) out[j] = x[j]; }
+    else if (y == -1.0f) { for (int j = 0; j < 4; ++j) out[j] = __fdiv_rn(1.0f, x[j]); }
+    else { for (int j = 0; j < 4; ++j) out[j] = ormi_pow_general(x[j], y); }
+}
 // GEMM epilogue: sum over the four lanes that hold the same columns of a 32-row block (lanes l, l^8, l^16, l^24)
 #ifndef ORMI_EMULATE
 // ... and over all 32 lanes (a global sum: one value per 32-row block and 32-column chunk)
@@ -836,7 +846,22 @@ GeneratedEpilogue generate_gemm_epilogue(const KernelSpec& spec, bool store_c, b
     };
     body << "const float A[4] = {acc.x, acc.y, acc.z, acc.w}; ";
     for (const KNode& kn : spec.nodes) body << "float v" << kn.node << "[4]; ";
-    if (!spec.nodes.empty()) {
+    // Node by node over the four columns (not column by column over the nodes): the four chains are side by side in
+    // program order, and a POW by a per-kernel exponent decides its special case once for the four.
+    const bool node_major = spec.tune[TUNE_EPI_NODE_MAJOR] != 1;
+    if (!spec.nodes.empty() && node_major) {
+        auto at_j = [](std::string r, int j) { size_t p = r.find("[j]"); if (p != std::string::npos) r.replace(p, 3, "[" + std::to_string(j) + "]"); return r; };
+        for (const KNode& kn : spec.nodes) {
+            const std::string a = ref(kn.operands[0]);
+            const std::string b = kn.operands.size() > 1 ? ref(kn.operands[1]) : "";
+            const bool a_elem = a.find("[j]") != std::string::npos, b_elem = b.find("[j]") != std::string::npos;
+            if (kn.op == ORMI_OP_POW && a_elem && !b_elem && !lowering_for(ORMI_OP_POW, nullptr)) {
+                body << "ormi_pow4(" << a.substr(0, a.find("[j]")) << ", " << b << ", v" << kn.node << "); ";
+                continue;
+            }
+            for (int j = 0; j < 4; ++j) body << "v" << kn.node << "[" << j << "] = " << op_expr(kn.op, at_j(a, j), at_j(b, j)) << "; ";
+        }
+    } else if (!spec.nodes.empty()) {
         body << "_Pragma(\"unroll\") for (int j = 0; j < 4; ++j) { ";
         for (const KNode& kn : spec.nodes) {
             std::string a = ref(kn.operands[0]);

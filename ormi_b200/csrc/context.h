@@ -101,7 +101,7 @@ struct ormi_b200_ctx {
     std::unordered_map<std::string, ormi_b200::CompiledKernel> kernel_cache;   // source hash -> module
     std::unordered_map<std::string, std::unique_ptr<ormi_b200::CachedPlan>> plan_cache;   // by graph_key (runtime.cu)
     bool free_intermediates = false;   // option "intermediates": materialized nodes the caller does not hold are scratch
-    int tune[ormi_b200::kTuneKnobs] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};   // code-generator overrides (SchedOptions::tune), 0 = default
+    int tune[ormi_b200::kTuneKnobs] = {};   // code-generator overrides (SchedOptions::tune), 0 = default
 
     ormi_b200::MatmulMode matmul_mode = ormi_b200::MatmulMode::FP32;
     bool fusion = true;

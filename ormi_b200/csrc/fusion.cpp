@@ -964,7 +964,7 @@ std::string json_escape(const std::string& s) {
 
 int tune_knob_index(const std::string& name) {
     static const char* names[kTuneKnobs] = {"rows_vpt", "rows_minb", "rows_grid", "rows_stage", "rows_nstage", "rows_dynamic",
-                                            "flat_unroll", "rows_hoist", "epi_unroll", "epi_wpq", "gemm_bn"};
+                                            "flat_unroll", "rows_hoist", "epi_unroll", "epi_wpq", "gemm_bn", "epi_node_major"};
     for (int i = 0; i < kTuneKnobs; ++i) if (name == names[i]) return i;
     return -1;
 }

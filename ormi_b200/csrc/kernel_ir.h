@@ -50,7 +50,7 @@ struct KernelSpec {
     std::vector<KOutput> outputs;
     int num_sms = 148;
     bool aligned = true;        // every buffer starts on a 16-byte boundary (else scalar accesses only, no bulk copies)
-    int tune[kTuneKnobs] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};   // SchedOptions::tune
+    int tune[kTuneKnobs] = {};   // SchedOptions::tune
 };
 
 struct GeneratedKernel {

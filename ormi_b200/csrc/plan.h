@@ -85,8 +85,9 @@ struct Plan {
 enum TuneKnob { TUNE_ROWS_VPT = 0, TUNE_ROWS_MINB, TUNE_ROWS_GRID, TUNE_ROWS_STAGE /* 1 off, 2 on */, TUNE_ROWS_NSTAGE,
                 TUNE_ROWS_DYNAMIC /* 1 off, 2 on */, TUNE_FLAT_UNROLL, TUNE_ROWS_HOIST /* 1 off, 2 on */,
                 TUNE_EPI_UNROLL /* unrolled row steps of a GEMM epilogue chunk: 1, 2, 4, 8 */, TUNE_EPI_WPQ /* epilogue warps per quarter: 1, 2, 4 */,
-                TUNE_GEMM_BN /* columns per tensor-core GEMM tile: 128, 256 */ };
-constexpr int kTuneKnobs = 11;
+                TUNE_GEMM_BN /* columns per tensor-core GEMM tile: 128, 256 */,
+                TUNE_EPI_NODE_MAJOR /* GEMM epilogue text node by node over the four columns: 1 off, 2 on */ };
+constexpr int kTuneKnobs = 12;
 
 struct SchedOptions {
     int  num_sms = 148;
@@ -94,7 +95,7 @@ struct SchedOptions {
     bool bf16_matmul = false;   // matmuls run on the tensor-core kernel: fuse epilogues, let producers write bf16 twins
     bool aligned = true;        // every realized input starts on a 16-byte boundary (else: no 128-bit accesses, no bulk copies)
     bool free_intermediates = false;   // materialized nodes the caller does not hold (no root, no KEEP) are scratch of the call
-    int  tune[kTuneKnobs] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    int  tune[kTuneKnobs] = {};
 };
 
 Plan build_plan(const ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots, const SchedOptions& opt);
