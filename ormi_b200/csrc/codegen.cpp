@@ -34,7 +34,7 @@ std::string device_prelude() {
     return R"PRE(
 #ifndef ORMI_PRELUDE
 #define ORMI_PRELUDE
-// x ** y with the exponents the graphs actually use (0.5, 2, 3, 1, -1) evaluated the way a correctly
+// x ** y with the exponents the graphs actually use (0.5, 2, 3, 1, -1, -0.5) evaluated the way a correctly
 // rounded powf would come out; anything else is powf.  The rare paths are kept out of line: inlined at every use
 // they multiply the code size of an unrolled kernel body and push it out of the instruction cache.
 #ifndef ORMI_EMULATE
@@ -63,6 +63,7 @@ __device__ __forceinline__ float ormi_pow(float x, float y) {
     if (y == 3.0f) return ormi_cube(x);
     if (y == 1.0f) return x;
     if (y == -1.0f) return __fdiv_rn(1.0f, x);
+    if (y == -0.5f) return __frsqrt_rn(x);       // the derivative of a square root: sits on the per-row path of layernorm's backward
     return ormi_pow_general(x, y);
 }
 // The same for four values and one exponent: one chain of comparisons for the four, and the four results of the branch
@@ -73,6 +74,7 @@ __device__ __forceinline__ void ormi_pow4(const float* x, float y, float* out) {
     else if (y == 3.0f) { for (int j = 0; j < 4; ++j) out[j] = ormi_cube(x[j]); }
     else if (y == 1.0f) { for (int j = 0; j < 4; ++j) out[j] = x[j]; }
     else if (y == -1.0f) { for (int j = 0; j < 4; ++j) out[j] = __fdiv_rn(1.0f, x[j]); }
+    else if (y == -0.5f) { for (int j = 0; j < 4; ++j) out[j] = __frsqrt_rn(x[j]); }
     else { for (int j = 0; j < 4; ++j) out[j] = ormi_pow_general(x[j], y); }
 }
 // GEMM epilogue: sum over the four lanes that hold the same columns of a 32-row block (lanes l, l^8, l^16, l^24)

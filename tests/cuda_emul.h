@@ -36,6 +36,7 @@ struct uint2 { unsigned x, y; };
 static inline uint2 make_uint2(unsigned x, unsigned y) { uint2 r = {x, y}; return r; }
 static inline float __fdiv_rn(float a, float b) { return a / b; }
 static inline float __frcp_rn(float a) { return 1.0f / a; }
+static inline float __frsqrt_rn(float a) { return (float)(1.0 / sqrt((double)a)); }
 static inline void __syncthreads() { pthread_barrier_wait(&emul_barrier); }
 static inline float __shfl_xor_sync(unsigned, float v, int lane_mask) {
     unsigned t = threadIdx.x;
