@@ -268,7 +268,8 @@ int ormi_b200_selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms);
  *   "pool_canary": "on" / "off" (default).  A debugging aid in place of a memory checker: every block the pool hands out
  *              from then on carries a 256-byte guard zone behind it, read back (synchronously) when the block returns; an
  *              overwritten zone makes that call — ormi_b200_free, or the realize call that returns scratch — fail with
- *              the block's size in the message.
+ *              the block's size in the message.  The environment variable ORMI_B200_POOL_CANARY=1 starts every context
+ *              with it on.
  *   "tc_pair": "on" (default: one tcgen05.mma per pair of SMs, 256 x 256 tiles) / "off" (one per SM, 128 x 256) /
  *              "auto" (pairs, except for GEMMs queued while an overlapped all-reduce is in flight: a collective holds
  *              single SMs, and a pair needs both SMs of a TPC — measured 5 % slower than "on" on 2 and on 4 GPUs).

@@ -66,6 +66,8 @@ int ormi_b200_init(int device, ormi_b200_ctx** out_ctx) {
         ORMI_CUDA(cudaFree(0));
         ctx->drv.load();
         ORMI_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+        // ORMI_B200_POOL_CANARY=1: every context starts with the option "pool_canary" on (a whole test session under guard zones)
+        ctx->pool_canary = std::getenv("ORMI_B200_POOL_CANARY") != nullptr;
         *out_ctx = ctx.release();
     });
 }

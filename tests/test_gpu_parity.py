@@ -5,6 +5,7 @@ bf16 tensor-core matmul <= 2e-2 — all as max|gpu - cpu| / max|cpu| per tensor,
 serially in fp32 and an element-wise relative error is unbounded wherever a sum cancels.
 """
 import ctypes
+import os
 import math
 
 import numpy as np
@@ -352,6 +353,8 @@ def test_wide_hidden_layer_schedule(device):
 def test_scratch_buffers_are_reused_inside_one_realize():
     """Three column sums in a chain need three 1 MiB partial buffers with disjoint lifetimes: the executor takes each
     from the pool at its first step and returns it after its last, so a fresh context allocates that size once."""
+    if os.environ.get("ORMI_B200_POOL_CANARY"):
+        pytest.skip("counts bytes taken from the driver: guard zones add 256 to every block")
     from ormi_b200.runtime import Device
     dev = Device(0)
     try:
@@ -495,6 +498,8 @@ def test_pool_byte_cap_walks_the_out_of_memory_path():
 def test_intermediates_free_reuses_blocks_inside_the_call():
     """"intermediates=free": a materialized node the caller does not hold is scratch of the realize call — its block is
     back in the pool for a later step of the same call — and does not come back realized.  Values are unchanged."""
+    if os.environ.get("ORMI_B200_POOL_CANARY"):
+        pytest.skip("counts bytes taken from the driver: guard zones add 256 to every block")
     from ormi_b200.runtime import Device
     a_h, b_h = W.normal(0, (512, 512), 0.05), W.normal(1, (512, 512), 0.05)
     got = {}
