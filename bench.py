@@ -615,6 +615,15 @@ def main():
     settle()
     dev.sync()
     clocks = sampler.stop() if rank == 0 else None
+    # the same step recorded once (ormi_b200_capture_begin / _end) and replayed with one call per step
+    graph_ms = None
+    if dist is None and not args.no_extras:
+        with dev.capture() as captured:
+            runner.run()
+        for _ in range(3):
+            captured.launch()
+        graph_ms = timed(dev, torch, captured.launch, args.steps) / args.steps
+        captured.destroy()
 
     # ------------------------------------------------------------------------------------------------ end to end
     # Host buffers in, host buffers out, through the public Device API, pipelined: the step is row independent, so it
@@ -701,6 +710,9 @@ def main():
 
     # the other legs of the metric: configs[0], matmul TFLOP/s (configs[2]) and MLP training steps/s (configs[3], [4])
     extras = {}
+    if graph_ms is not None:
+        extras["step_graph_replay"] = {"ms_per_step": graph_ms, "gbps": BYTES_STEP / (graph_ms * 1e-3) / 1e9,
+                                       "note": "the headline step captured into a CUDA graph and replayed: one host call per step"}
     peak, peak_src = peaks()
     if not args.no_extras:
         del runner, host_in, host_out, host_part, np_in, np_out, np_part, chunk_sets

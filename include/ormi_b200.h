@@ -279,6 +279,20 @@ int ormi_b200_selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms);
  *              experiments ("0" = default; for the on/off ones 1 = off, 2 = on). */
 int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value);
 
+/* Step capture (additive; the reference launches every kernel from the host, ormi-core/csrc/backend/cuda/jit.cu:13-44).
+ * Between capture_begin and capture_end everything the context queues on its compute stream — ormi_b200_realize,
+ * ormi_b200_sum / _matmul / _gemm_bf16, device-to-device copies, fills — is recorded into a CUDA graph instead of run;
+ * ormi_b200_graph_launch replays the whole step with one call.  Rules: run the step once before capturing it (kernels
+ * compiled, every block it needs cached by the pool: nothing is taken from the driver inside a capture); calls that wait
+ * for the device, copy to or from the host, or use the second stream (collectives) fail while a capture is open; the
+ * replays read the inputs and write the results at the addresses the capture saw, so every pool block handed out during
+ * the capture — results included — belongs to the graph until ormi_b200_graph_destroy: ormi_b200_free of one of them is
+ * a no-op while the graph lives, and the results die with the graph.  Not with "pool_canary" on. */
+int ormi_b200_capture_begin(ormi_b200_ctx* ctx);
+int ormi_b200_capture_end(ormi_b200_ctx* ctx, void** out_graph);
+int ormi_b200_graph_launch(ormi_b200_ctx* ctx, void* graph);
+int ormi_b200_graph_destroy(ormi_b200_ctx* ctx, void* graph);
+
 /* Counters since init: "kernels_compiled", "kernel_cache_hits", "plan_cache_hits", "launches",
  * "gemm_launches", "bytes_allocated", "pool_hits". */
 int ormi_b200_get_counter(ormi_b200_ctx* ctx, const char* name, int64_t* out_value);

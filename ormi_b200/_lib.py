@@ -62,6 +62,10 @@ _SIGNATURES = {
     "ormi_b200_selftest_wait_timeout": (c_int, [c_void_p, c_int]),
     "ormi_b200_set_option": (c_int, [c_void_p, c_char_p, c_char_p]),
     "ormi_b200_get_counter": (c_int, [c_void_p, c_char_p, P(ctypes.c_int64)]),
+    "ormi_b200_capture_begin": (c_int, [c_void_p]),
+    "ormi_b200_capture_end": (c_int, [c_void_p, P(c_void_p)]),
+    "ormi_b200_graph_launch": (c_int, [c_void_p, c_void_p]),
+    "ormi_b200_graph_destroy": (c_int, [c_void_p, c_void_p]),
 }
 
 

@@ -1,4 +1,5 @@
 // extern "C" surface of the backend (include/ormi_b200.h): argument checking, exception -> error code.
+#include <algorithm>
 #include <cstring>
 
 #include "context.h"
@@ -19,9 +20,12 @@ static void need(bool cond, const char* msg) { if (!cond) throw Error(msg); }
 
 // Every entry point that takes a context makes the context's device current first: a process may hold contexts on
 // several devices, and stream operations fail when another device is current.
-static void bind(ormi_b200_ctx* ctx, const char* who) {
+static void bind(ormi_b200_ctx* ctx, const char* who, bool capturable = false) {
     if (!ctx) throw Error(std::string(who) + ": ctx is NULL");
     ORMI_CUDA(cudaSetDevice(ctx->device));
+    // while a step is being captured only calls that queue work on the compute stream (or touch the pool) may run:
+    // a host wait, a copy to or from the host or a collective would end the capture with an error of the driver's
+    if (ctx->capturing && !capturable) throw Error(std::string(who) + ": not allowed while a step is being captured");
     // An error that an earlier runtime call of this thread left behind and nobody consumed (another library in the
     // process, or a collective library called from here, may do that with a call it expected to fail) must not be
     // blamed on the next kernel this library launches: it is taken off here and counted.  Sticky errors stay and are
@@ -89,11 +93,11 @@ int ormi_b200_shutdown(ormi_b200_ctx* ctx) {
 }
 
 int ormi_b200_alloc(ormi_b200_ctx* ctx, size_t bytes, void** out_ptr) {
-    return guarded([&] { need(out_ptr != nullptr, "ormi_b200_alloc: NULL argument"); bind(ctx, "ormi_b200_alloc"); *out_ptr = pool_alloc(ctx, bytes); });
+    return guarded([&] { need(out_ptr != nullptr, "ormi_b200_alloc: NULL argument"); bind(ctx, "ormi_b200_alloc", true); *out_ptr = pool_alloc(ctx, bytes); });
 }
 
 int ormi_b200_free(ormi_b200_ctx* ctx, void* ptr, size_t bytes) {
-    return guarded([&] { bind(ctx, "ormi_b200_free"); pool_free(ctx, ptr, bytes); });
+    return guarded([&] { bind(ctx, "ormi_b200_free", true); pool_free(ctx, ptr, bytes); });
 }
 
 int ormi_b200_trim(ormi_b200_ctx* ctx) {
@@ -114,11 +118,11 @@ int ormi_b200_trim(ormi_b200_ctx* ctx) {
 }
 
 int ormi_b200_memset(ormi_b200_ctx* ctx, void* ptr, int value, size_t bytes) {
-    return guarded([&] { bind(ctx, "ormi_b200_memset"); shadow_drop(ctx, ptr, bytes); ORMI_CUDA(cudaMemsetAsync(ptr, value, bytes, ctx->stream)); });
+    return guarded([&] { bind(ctx, "ormi_b200_memset", true); shadow_drop(ctx, ptr, bytes); ORMI_CUDA(cudaMemsetAsync(ptr, value, bytes, ctx->stream)); });
 }
 
 int ormi_b200_memcpy_d2d(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes) {
-    return guarded([&] { bind(ctx, "ormi_b200_memcpy_d2d"); shadow_drop(ctx, dst, bytes); ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream)); });
+    return guarded([&] { bind(ctx, "ormi_b200_memcpy_d2d", true); shadow_drop(ctx, dst, bytes); ORMI_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream)); });
 }
 
 int ormi_b200_memcpy_h2d(ormi_b200_ctx* ctx, void* dst, const void* src, size_t bytes) {
@@ -211,7 +215,7 @@ __global__ void fill_u32_kernel(uint32_t* dst, uint32_t v, size_t n) {
 
 int ormi_b200_fill_u32(ormi_b200_ctx* ctx, void* dst, uint32_t pattern, size_t count) {
     return guarded([&] {
-        bind(ctx, "ormi_b200_fill_u32");
+        bind(ctx, "ormi_b200_fill_u32", true);
         if (count == 0) return;
         shadow_drop(ctx, dst, count * 4);
         int grid = (int)std::min<size_t>((count + 255) / 256, (size_t)ctx->num_sms * 8);
@@ -221,7 +225,7 @@ int ormi_b200_fill_u32(ormi_b200_ctx* ctx, void* dst, uint32_t pattern, size_t c
 }
 
 int ormi_b200_fill_u8(ormi_b200_ctx* ctx, void* dst, uint8_t pattern, size_t count) {
-    return guarded([&] { bind(ctx, "ormi_b200_fill_u8"); shadow_drop(ctx, dst, count); ORMI_CUDA(cudaMemsetAsync(dst, pattern, count, ctx->stream)); });
+    return guarded([&] { bind(ctx, "ormi_b200_fill_u8", true); shadow_drop(ctx, dst, count); ORMI_CUDA(cudaMemsetAsync(dst, pattern, count, ctx->stream)); });
 }
 
 int ormi_b200_sync(ormi_b200_ctx* ctx) {
@@ -233,7 +237,7 @@ void* ormi_b200_stream(ormi_b200_ctx* ctx) { return ctx ? (void*)ctx->stream : n
 int ormi_b200_realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots) {
     return guarded([&] {
         need(nodes && roots && n_nodes > 0 && n_roots > 0, "ormi_b200_realize: bad arguments");
-        bind(ctx, "ormi_b200_realize");
+        bind(ctx, "ormi_b200_realize", true);
         realize(ctx, nodes, n_nodes, roots, n_roots);
     });
 }
@@ -309,7 +313,7 @@ int ormi_b200_sum(ormi_b200_ctx* ctx, const float* in, int ndim, const int32_t* 
                   const int32_t* axes, int n_axes, float* out) {
     return guarded([&] {
         need(in && out && ndim >= 0 && ndim <= ORMI_B200_MAX_DIMS, "ormi_b200_sum: bad arguments");
-        bind(ctx, "ormi_b200_sum");
+        bind(ctx, "ormi_b200_sum", true);
         ormi_b200_node g[2];
         fill_node(g[0], ORMI_OP_LEAF, ndim, shape, strides, (void*)in);
         int32_t oshape[ORMI_B200_MAX_DIMS]; int ond = 0;
@@ -333,7 +337,7 @@ int ormi_b200_matmul(ormi_b200_ctx* ctx,
                      float* out, int ndim_out, const int32_t* shape_out) {
     return guarded([&] {
         need(A && B && out, "ormi_b200_matmul: NULL argument");
-        bind(ctx, "ormi_b200_matmul");
+        bind(ctx, "ormi_b200_matmul", true);
         need(ndim_a >= 2 && ndim_b >= 2 && ndim_a <= ORMI_B200_MAX_DIMS && ndim_b <= ORMI_B200_MAX_DIMS && ndim_out <= ORMI_B200_MAX_DIMS,
              "MATMUL requires operands to have at least 2 dimensions.");
         ormi_b200_node g[3];
@@ -352,7 +356,7 @@ int ormi_b200_matmul(ormi_b200_ctx* ctx,
 int ormi_b200_cvt_bf16_kmajor(ormi_b200_ctx* ctx, const float* src, int64_t row_stride, int64_t k_stride, int rows, int K, void* dst) {
     return guarded([&] {
         need(src && dst && rows > 0 && K > 0, "ormi_b200_cvt_bf16_kmajor: bad arguments");
-        bind(ctx, "ormi_b200_cvt_bf16_kmajor");
+        bind(ctx, "ormi_b200_cvt_bf16_kmajor", true);
         cvt_bf16_kmajor(ctx, src, row_stride, k_stride, rows, K, dst);
     });
 }
@@ -360,7 +364,7 @@ int ormi_b200_cvt_bf16_kmajor(ormi_b200_ctx* ctx, const float* src, int64_t row_
 int ormi_b200_gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* b16, float* C, int M, int N, int Kp) {
     return guarded([&] {
         need(a16 && b16 && C, "ormi_b200_gemm_bf16_kmajor: NULL argument");
-        bind(ctx, "ormi_b200_gemm_bf16_kmajor");
+        bind(ctx, "ormi_b200_gemm_bf16_kmajor", true);
         gemm_bf16_kmajor(ctx, a16, b16, C, M, N, Kp);
     });
 }
@@ -368,7 +372,7 @@ int ormi_b200_gemm_bf16_kmajor(ormi_b200_ctx* ctx, const void* a16, const void* 
 int ormi_b200_cvt_bf16(ormi_b200_ctx* ctx, const float* src, int64_t ld, int rows, int cols, void* dst) {
     return guarded([&] {
         need(src && dst, "ormi_b200_cvt_bf16: NULL argument");
-        bind(ctx, "ormi_b200_cvt_bf16");
+        bind(ctx, "ormi_b200_cvt_bf16", true);
         cvt_bf16(ctx, src, ld, rows, cols, dst);
     });
 }
@@ -377,7 +381,7 @@ int ormi_b200_gemm_bf16(ormi_b200_ctx* ctx, const void* a16, int a_transposed, c
                         float* C, int M, int N, int K) {
     return guarded([&] {
         need(a16 && b16 && C, "ormi_b200_gemm_bf16: NULL argument");
-        bind(ctx, "ormi_b200_gemm_bf16");
+        bind(ctx, "ormi_b200_gemm_bf16", true);
         shadow_drop(ctx, C, (size_t)M * N * 4);
         gemm_tc(ctx, a16, a_transposed ? 1 : 0, b16, b_transposed ? 0 : 1, C, M, N, K);
     });
@@ -422,7 +426,7 @@ int ormi_b200_selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms) {
 int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value) {
     return guarded([&] {
         need(key && value, "ormi_b200_set_option: NULL argument");
-        bind(ctx, "ormi_b200_set_option");
+        bind(ctx, "ormi_b200_set_option", true);
         std::string k = key, v = value;
         if (k == "matmul") {
             if (v == "fp32") ctx->matmul_mode = MatmulMode::FP32;
@@ -461,6 +465,91 @@ int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value)
             // "free": only roots and ORMI_NODE_KEEP nodes are; the other materialized nodes are scratch of the call.
             if (v == "keep") ctx->free_intermediates = false; else if (v == "free") ctx->free_intermediates = true; else throw Error("intermediates must be keep or free");
         } else throw Error("unknown option: " + k);
+    });
+}
+
+// ------------------------------------------------------------------------------------------------ step capture
+struct CapturedStep {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    std::vector<std::pair<void*, size_t>> blocks;      // every pool block the step touched: owned until the graph is destroyed
+};
+
+int ormi_b200_capture_begin(ormi_b200_ctx* ctx) {
+    return guarded([&] {
+        bind(ctx, "ormi_b200_capture_begin");
+        if (ctx->pool_canary) throw Error("ormi_b200_capture_begin: not with pool_canary on (its checks wait for the device)");
+        if (ctx->comm_inflight > 0) throw Error("ormi_b200_capture_begin: a collective is in flight on the second stream");
+        device_error_word(ctx);                         // exists before the capture: nothing is allocated inside it
+        check_gemm_error(ctx);
+        ORMI_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        ctx->capture_blocks.clear();
+        ctx->capturing = true;
+    });
+}
+
+int ormi_b200_capture_end(ormi_b200_ctx* ctx, void** out_graph) {
+    return guarded([&] {
+        if (!ctx || !out_graph) throw Error("ormi_b200_capture_end: NULL argument");
+        ORMI_CUDA(cudaSetDevice(ctx->device));
+        if (!ctx->capturing) throw Error("ormi_b200_capture_end: no capture is open");
+        ctx->capturing = false;
+        auto step = std::make_unique<CapturedStep>();
+        cudaError_t e = cudaStreamEndCapture(ctx->stream, &step->graph);
+        if (e == cudaSuccess) e = cudaGraphInstantiate(&step->exec, step->graph, 0);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            if (step->graph) cudaGraphDestroy(step->graph);
+            ctx->capture_blocks.clear();
+            throw Error(std::string("CUDA Error: ") + cudaGetErrorString(e) + " (ending the capture)");
+        }
+        // Every block the pool handed out during the capture is read or written by the replays: the graph owns them all
+        // from here on.  Those that went back to the pool in the meantime are taken out of it again; freeing one of
+        // the others (a result the caller holds) is a no-op while the graph lives.
+        std::lock_guard<std::mutex> lock(ctx->pool_mutex);
+        for (auto& kv : ctx->capture_blocks) {
+            step->blocks.push_back(kv);
+            ctx->graph_owned.insert(kv.first);
+            if (ctx->pooled.erase(kv.first)) {
+                auto& v = ctx->free_blocks[kv.second];
+                v.erase(std::remove(v.begin(), v.end(), kv.first), v.end());
+            }
+        }
+        ctx->capture_blocks.clear();
+        ctx->counters["captured_steps"]++;
+        *out_graph = step.release();
+    });
+}
+
+int ormi_b200_graph_launch(ormi_b200_ctx* ctx, void* graph) {
+    return guarded([&] {
+        bind(ctx, "ormi_b200_graph_launch");
+        if (!graph) throw Error("ormi_b200_graph_launch: NULL graph");
+        ORMI_CUDA(cudaGraphLaunch(((CapturedStep*)graph)->exec, ctx->stream));
+        ctx->gemm_err_pending = true;
+        ctx->counters["graph_launches"]++;
+    });
+}
+
+int ormi_b200_graph_destroy(ormi_b200_ctx* ctx, void* graph) {
+    return guarded([&] {
+        bind(ctx, "ormi_b200_graph_destroy");
+        if (!graph) return;
+        std::unique_ptr<CapturedStep> step((CapturedStep*)graph);
+        cudaGraphExecDestroy(step->exec);
+        cudaGraphDestroy(step->graph);
+        {
+            std::lock_guard<std::mutex> lock(ctx->pool_mutex);
+            for (auto& b : step->blocks) ctx->graph_owned.erase(b.first);
+        }
+        // bf16 twins that live in the graph's blocks go with them; the blocks return to the pool behind the replays
+        // already queued on the compute stream
+        for (auto it = ctx->shadows.begin(); it != ctx->shadows.end();) {
+            bool mine = false;
+            for (auto& b : step->blocks) if (b.first == it->second.ptr) mine = true;
+            it = mine ? ctx->shadows.erase(it) : std::next(it);
+        }
+        for (auto& b : step->blocks) pool_free(ctx, b.first, b.second);
     });
 }
 

@@ -94,6 +94,10 @@ struct ormi_b200_ctx {
     std::mutex pool_mutex;
     long long pool_limit_bytes = 0, pool_held_bytes = 0;   // option "pool_limit_bytes": simulated memory exhaustion
     std::unordered_map<size_t, std::vector<void*>> free_blocks;
+    // step capture (ormi_b200_capture_begin .. _end): blocks the pool hands out meanwhile, and the blocks live graphs own
+    bool capturing = false;
+    std::unordered_map<void*, size_t> capture_blocks;
+    std::unordered_set<void*> graph_owned;
     bool pool_canary = false;              // option "pool_canary": a guard zone behind every block, checked when the block comes back
     std::unordered_map<void*, size_t> canaries;   // block -> bytes asked for, of the blocks that carry a guard zone
     std::unordered_set<void*> pooled;      // every block that sits in free_blocks: a block returned twice is caught, not handed to two owners

@@ -67,6 +67,8 @@ void* pool_alloc(ormi_b200_ctx* ctx, size_t asked) {
             ctx->counters["pool_hits"]++;
         }
     }
+    if (!p && ctx->capturing)
+        throw Error("capture: the pool holds no free block of " + std::to_string(bytes) + " bytes (run the step once before capturing it: nothing may be taken from the driver while a step is captured)");
     if (!p) {
         auto over_limit = [&]() { return ctx->pool_limit_bytes > 0 && ctx->pool_held_bytes + (long long)bytes > ctx->pool_limit_bytes; };
         cudaError_t e = over_limit() ? cudaErrorMemoryAllocation : cudaMalloc(&p, bytes);
@@ -86,6 +88,7 @@ void* pool_alloc(ormi_b200_ctx* ctx, size_t asked) {
         ctx->counters["bytes_allocated"] += (int64_t)bytes;
         ctx->pool_held_bytes += (long long)bytes;
     }
+    if (ctx->capturing) { std::lock_guard<std::mutex> lock(ctx->pool_mutex); ctx->capture_blocks[p] = bytes; }
     if (canary) {
         const cudaError_t e = cudaMemsetAsync((char*)p + asked, kCanaryByte, kCanaryBytes, ctx->stream);
         if (e != cudaSuccess) { pool_free(ctx, p, bytes); throw Error(std::string("CUDA Error: ") + cudaGetErrorString(e) + " (filling a guard zone)"); }
@@ -98,6 +101,10 @@ void* pool_alloc(ormi_b200_ctx* ctx, size_t asked) {
 void pool_free(ormi_b200_ctx* ctx, void* ptr, size_t bytes) {
     if (!ptr) return;
     if (bytes == 0) bytes = 4;
+    {   // a block that a captured step reads or writes on every replay stays with that graph until the graph is destroyed
+        std::lock_guard<std::mutex> lock(ctx->pool_mutex);
+        if (ctx->graph_owned.count(ptr)) return;
+    }
     shadow_drop(ctx, ptr, bytes);      // a bf16 twin of this buffer goes back to the pool with it
     bool guarded_block = false;
     {

@@ -74,6 +74,13 @@ class Device:
         """The value last set through this object (the defaults: "matmul" "fp32", "fusion" "on", "tc_pair" "on", "intermediates" "keep")."""
         return self._options.get(key, {"matmul": "fp32", "fusion": "on", "tc_pair": "on", "intermediates": "keep"}.get(key, ""))
 
+    def capture(self):
+        """``with dev.capture() as step: ...`` records what the block queues on the compute stream (realize calls, raw
+        matmuls) instead of running it; afterwards ``step.launch()`` replays it with one call and ``step.destroy()`` gives
+        its buffers back.  Run the block once before capturing it.  Results obtained inside the block stay valid (and are
+        rewritten by every replay) until the step is destroyed."""
+        return CapturedStep(self)
+
     def counter(self, name: str) -> int:
         v = ctypes.c_int64()
         check(lib.ormi_b200_get_counter(self.handle, name.encode(), ctypes.byref(v)))
@@ -171,6 +178,35 @@ def _find_buffer(order, ptr):
         if n.data is not None and n.data.dev_ptr == ptr:
             return n.data
     raise RuntimeError("alias of an unknown buffer")
+
+
+class CapturedStep:
+    """A step recorded by ``Device.capture()`` (ormi_b200_capture_begin / _end / ormi_b200_graph_launch)."""
+
+    def __init__(self, dev: "Device"):
+        self.dev, self.handle = dev, None
+
+    def __enter__(self):
+        check(lib.ormi_b200_capture_begin(self.dev.handle))
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        g = ctypes.c_void_p()
+        rc = lib.ormi_b200_capture_end(self.dev.handle, ctypes.byref(g))
+        if exc_type is None:
+            check(rc)
+            self.handle = g
+        elif rc == 0:
+            lib.ormi_b200_graph_destroy(self.dev.handle, g)
+        return False
+
+    def launch(self):
+        check(lib.ormi_b200_graph_launch(self.dev.handle, self.handle))
+
+    def destroy(self):
+        if self.handle is not None and self.dev.handle:
+            check(lib.ormi_b200_graph_destroy(self.dev.handle, self.handle))
+        self.handle = None
 
 
 def plan(roots: Sequence[G.Node], host_pointers=True, options: str = "") -> dict:

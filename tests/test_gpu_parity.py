@@ -556,3 +556,73 @@ def test_pool_canary_reports_a_write_past_the_end_of_a_block():
         dev.free(q, 1000)
     finally:
         dev.close()
+
+
+def test_captured_step_replays_with_new_input_contents():
+    """Step capture: a softmax + layernorm forward/backward step and a matmul are recorded once and replayed with one call;
+    the replays read the input buffers at their addresses (new contents give new results), rewrite the results in place,
+    and keep every block they touch until the step is destroyed."""
+    from ormi_b200.runtime import Device
+    dev = Device(0)
+    try:
+        R, C = 96, 520
+
+        def graph(xn, gyn, gn, bn, an, wn):
+            y = W.layernorm(xn, gn, bn)
+            y.grad = gyn
+            G.compute_gradients(y)
+            return [y, xn.grad, gn.grad, bn.grad, G.matmul(an, wn)]
+
+        def inputs(seed):
+            return [W.normal(seed, (R, C), 1.5), W.normal(seed + 1, (R, C)), W.normal(seed + 2, (C,), 0.5, 1.0), W.normal(seed + 3, (C,)),
+                    W.normal(seed + 4, (64, 72)), W.normal(seed + 5, (72, 40))]
+
+        host = inputs(0)
+        leaves = [dev.leaf(h, i in (0, 2, 3)) for i, h in enumerate(host)]
+        roots = graph(*leaves)
+        arr, order, ridx = G.flatten(roots, host_pointers=False, stop_at_realized=True)
+        dev.ensure_on_device(order)
+        arr, order, ridx = G.flatten(roots, host_pointers=False, stop_at_realized=True)
+        template = bytes(arr)
+        cridx = (ctypes.c_int * len(ridx))(*ridx)
+        from ormi_b200._lib import lib, check
+
+        def run():
+            ctypes.memmove(arr, template, len(template))
+            check(lib.ormi_b200_realize(dev.handle, arr, len(order), cridx, len(ridx)))
+            return [(arr[i].data, arr[i].data_bytes) for i in ridx]
+
+        for ptr, nbytes in run():                     # warm-up: kernels compiled, blocks cached by the pool
+            dev.free(ptr, nbytes)
+        dev.sync()
+        held = dev.counter("bytes_allocated")
+        with dev.capture() as step:
+            outs = run()
+            with pytest.raises(RuntimeError, match="not allowed while a step is being captured"):
+                dev.sync()
+        assert dev.counter("bytes_allocated") == held               # nothing was taken from the driver inside the capture
+        launches = dev.counter("launches")
+
+        def expect(hs):
+            ref_leaves = [G.leaf(h, i in (0, 2, 3)) for i, h in enumerate(hs)]
+            want, _ = O.port_run(graph(*ref_leaves))
+            return want
+
+        for seed in (0, 100, 200):
+            hs = inputs(seed)
+            for leaf, h in zip(leaves, hs):
+                dev.h2d(leaf.data.dev_ptr, np.ascontiguousarray(h))
+            step.launch()
+            dev.sync()
+            for (ptr, nbytes), want in zip(outs, expect(hs)):
+                got = np.empty(want.size, np.float32)
+                dev.d2h(got, ptr)
+                assert np.abs(got - want.reshape(-1)).max() <= 2e-5 * max(1e-30, np.abs(want).max())
+        assert dev.counter("launches") == launches                   # the replays went through the graph, not through realize
+        assert dev.counter("graph_launches") == 3
+        dev.free(*outs[0])                                           # a no-op while the step lives
+        step.launch()
+        dev.sync()
+        step.destroy()
+    finally:
+        dev.close()
