@@ -443,6 +443,9 @@ int ormi_b200_set_option(ormi_b200_ctx* ctx, const char* key, const char* value)
             // refuse allocations that would take the pool past this many bytes, as the driver does when memory is
             // exhausted (0 = no limit): lets a host test walk the out-of-memory path without exhausting a GPU
             ctx->pool_limit_bytes = std::atoll(v.c_str());
+        } else if (k == "auto_graph") {
+            // realize replays the launches of a plan as a CUDA graph once the same buffer addresses come round again
+            if (v == "on") ctx->auto_graph = true; else if (v == "off") ctx->auto_graph = false; else throw Error("auto_graph must be on or off");
         } else if (k == "pool_canary") {
             // debugging aid: a 256-byte guard zone behind every block taken from now on, checked when the block comes back
             if (v == "on") ctx->pool_canary = true; else if (v == "off") ctx->pool_canary = false; else throw Error("pool_canary must be on or off");

@@ -46,7 +46,19 @@ struct CompiledKernel {
     CUfunction func = nullptr;
 };
 
+// The launches of a plan for one set of buffer addresses, as an instantiated CUDA graph (runtime.cu, realize).
+struct StepGraph {
+    std::vector<void*> at;     // what every step saw: steps x buffers
+    void* exec = nullptr;      // cudaGraphExec_t
+    int launches = 0;
+    uint64_t stamp = 0;
+};
+
 struct CachedPlan {
+    ~CachedPlan();
+    std::vector<StepGraph> graphs;                 // most recently used address sets
+    std::vector<std::vector<void*>> seen;          // address sets met once: the second meeting records a graph
+    uint64_t graph_clock = 0;
     Plan plan;
     std::vector<CompiledKernel*> kernels;   // per step (nullptr for GEMM steps)
     // liveness of the scratch (Temp) buffers: the step that first touches buffer b and the step after which nothing
@@ -95,6 +107,7 @@ struct ormi_b200_ctx {
     long long pool_limit_bytes = 0, pool_held_bytes = 0;   // option "pool_limit_bytes": simulated memory exhaustion
     std::unordered_map<size_t, std::vector<void*>> free_blocks;
     // step capture (ormi_b200_capture_begin .. _end): blocks the pool hands out meanwhile, and the blocks live graphs own
+    bool auto_graph = true;                // option "auto_graph": realize replays a plan's launches as a CUDA graph when the addresses repeat
     bool capturing = false;
     std::unordered_map<void*, size_t> capture_blocks;
     std::unordered_set<void*> graph_owned;

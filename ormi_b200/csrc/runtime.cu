@@ -8,6 +8,7 @@
 // (the reference uses the legacy default stream and re-initialises the driver on every call), compiled
 // kernels are cached by source hash and whole schedules by graph structure, so a training loop that
 // rebuilds the same graph every step pays for scheduling, code generation and NVRTC once.
+#include <algorithm>
 #include <nvrtc.h>
 
 #include <cstdio>
@@ -277,6 +278,8 @@ static std::string graph_key(const ormi_b200_ctx* ctx, const ormi_b200_node* nod
     return key;
 }
 
+CachedPlan::~CachedPlan() { for (auto& g : graphs) if (g.exec) cudaGraphExecDestroy((cudaGraphExec_t)g.exec); }
+
 void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* roots, int n_roots,
              const std::vector<std::pair<int, void*>>* preassigned) {
     ORMI_CUDA(cudaSetDevice(ctx->device));
@@ -349,37 +352,95 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
                 if (!bufs[b] && cp->first_use[b] < 0) bufs[b] = pool_alloc(ctx, (size_t)pb.bytes);   // scratch comes later
             }
         }
+        // Pass 1, the pool only: every buffer gets its block in the order the steps need them — scratch is taken right
+        // before its first step and goes back right after its last one, so a later step of this call may get the same
+        // block (the stream orders the kernels that use it).  `at[s]` is what step s sees.
+        const size_t nb = plan.buffers.size();
+        std::vector<void*> at(plan.steps.size() * nb, nullptr);
         for (size_t s = 0; s < plan.steps.size(); ++s) {
-            const Step& st = plan.steps[s];
-            for (size_t b = 0; b < plan.buffers.size(); ++b)
+            for (size_t b = 0; b < nb; ++b)
                 if (cp->first_use[b] == (int)s && !bufs[b]) bufs[b] = pool_alloc(ctx, (size_t)plan.buffers[b].bytes);
-            if (st.type == Step::Kernel) {
-                std::vector<void*> args;
-                for (int a : st.k.args) args.push_back(bufs[a]);
-                launch_kernel(ctx, cp->kernels[s], st.k.grid, st.k.block, args, st.k.dyn_smem);
-                if (st.k.err_arg) ctx->gemm_err_pending = true;
-            } else {
-                GemmArgs g;
-                g.A = (const float*)bufs[st.g.a]; g.B = (const float*)bufs[st.g.b]; g.C = (float*)bufs[st.g.c];
-                g.M = st.g.M; g.N = st.g.N; g.K = st.g.K;
-                g.trans_a = st.g.trans_a; g.trans_b = st.g.trans_b; g.lda = st.g.lda; g.ldb = st.g.ldb;
-                g.batch = st.g.batch; g.nbatch = st.g.nbatch;
-                std::memcpy(g.bshape, st.g.bshape, sizeof g.bshape);
-                std::memcpy(g.astride, st.g.astride, sizeof g.astride);
-                std::memcpy(g.bstride, st.g.bstride, sizeof g.bstride);
-                if (st.g.tc) {
-                    TcEpilogue epi;
-                    if (st.g.has_epi) {
-                        epi.prelude = st.g.epi_prelude; epi.params = st.g.epi_params; epi.init = st.g.epi_init;
-                        epi.cols = st.g.epi_cols; epi.pre = st.g.epi_pre; epi.body = st.g.epi_body; epi.end = st.g.epi_end; epi.wpq = st.g.epi_wpq; epi.unroll = st.g.epi_unroll;
-                        for (int a : st.g.epi_args) epi.args.push_back(bufs[a]);
-                    }
-                    gemm_tc_from_fp32(ctx, g, st.g.a16 >= 0 ? bufs[st.g.a16] : nullptr, st.g.b16 >= 0 ? bufs[st.g.b16] : nullptr,
-                                      st.g.has_epi ? &epi : nullptr);
-                } else gemm_dispatch(ctx, g);
-            }
-            for (size_t b = 0; b < plan.buffers.size(); ++b)
+            std::copy(bufs.begin(), bufs.end(), at.begin() + s * nb);
+            for (size_t b = 0; b < nb; ++b)
                 if (cp->last_use[b] == (int)s && bufs[b]) { pool_free(ctx, bufs[b], (size_t)plan.buffers[b].bytes); bufs[b] = nullptr; handed[b] = true; }
+        }
+        // Pass 2, the launches.  A plan of several launches whose buffers come out at the same addresses as in an
+        // earlier call (a loop in its steady state: the pool hands the same blocks out in the same order) is replayed
+        // as a CUDA graph recorded at the second such call: one submission instead of one per kernel, and no gaps
+        // between the kernels.  The graph holds nothing but launches and their arguments: the blocks are owned as ever.
+        auto launch_steps = [&]() {
+            for (size_t s = 0; s < plan.steps.size(); ++s) {
+                const Step& st = plan.steps[s];
+                void* const* bp = at.data() + s * nb;
+                if (st.type == Step::Kernel) {
+                    std::vector<void*> args;
+                    for (int a : st.k.args) args.push_back(bp[a]);
+                    launch_kernel(ctx, cp->kernels[s], st.k.grid, st.k.block, args, st.k.dyn_smem);
+                    if (st.k.err_arg) ctx->gemm_err_pending = true;
+                } else {
+                    GemmArgs g;
+                    g.A = (const float*)bp[st.g.a]; g.B = (const float*)bp[st.g.b]; g.C = (float*)bp[st.g.c];
+                    g.M = st.g.M; g.N = st.g.N; g.K = st.g.K;
+                    g.trans_a = st.g.trans_a; g.trans_b = st.g.trans_b; g.lda = st.g.lda; g.ldb = st.g.ldb;
+                    g.batch = st.g.batch; g.nbatch = st.g.nbatch;
+                    std::memcpy(g.bshape, st.g.bshape, sizeof g.bshape);
+                    std::memcpy(g.astride, st.g.astride, sizeof g.astride);
+                    std::memcpy(g.bstride, st.g.bstride, sizeof g.bstride);
+                    if (st.g.tc) {
+                        TcEpilogue epi;
+                        if (st.g.has_epi) {
+                            epi.prelude = st.g.epi_prelude; epi.params = st.g.epi_params; epi.init = st.g.epi_init;
+                            epi.cols = st.g.epi_cols; epi.pre = st.g.epi_pre; epi.body = st.g.epi_body; epi.end = st.g.epi_end; epi.wpq = st.g.epi_wpq; epi.unroll = st.g.epi_unroll;
+                            for (int a : st.g.epi_args) epi.args.push_back(bp[a]);
+                        }
+                        gemm_tc_from_fp32(ctx, g, st.g.a16 >= 0 ? bp[st.g.a16] : nullptr, st.g.b16 >= 0 ? bp[st.g.b16] : nullptr,
+                                          st.g.has_epi ? &epi : nullptr);
+                    } else gemm_dispatch(ctx, g);
+                }
+            }
+        };
+        bool replayable = ctx->auto_graph && !ctx->capturing && !ctx->pool_canary && plan.steps.size() >= 2;
+        for (const Step& st : plan.steps)
+            if (st.type != Step::Kernel && (st.g.tc || ctx->matmul_mode != MatmulMode::FP32)) replayable = false;   // those matmuls look up or make operand copies as they go
+        if (!replayable) launch_steps();
+        else {
+            StepGraph* hit = nullptr;
+            for (auto& sg : cp->graphs) if (sg.at == at) hit = &sg;
+            if (hit) {
+                ORMI_CUDA(cudaGraphLaunch((cudaGraphExec_t)hit->exec, ctx->stream));
+                hit->stamp = ++cp->graph_clock;
+                ctx->counters["launches"] += hit->launches;
+                ctx->counters["graph_replays"]++;
+                for (const Step& st : plan.steps) if (st.type == Step::Kernel && st.k.err_arg) ctx->gemm_err_pending = true;
+            } else if (std::find(cp->seen.begin(), cp->seen.end(), at) == cp->seen.end()) {
+                launch_steps();                                  // first sighting of these addresses: remember them
+                if (cp->seen.size() >= 32) cp->seen.erase(cp->seen.begin());
+                cp->seen.push_back(at);
+            } else {
+                // second sighting: record the launches and run them as a graph from now on
+                const int64_t before = ctx->counters["launches"];
+                cudaGraph_t graph = nullptr;
+                ORMI_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+                try { launch_steps(); }
+                catch (...) { cudaStreamEndCapture(ctx->stream, &graph); if (graph) cudaGraphDestroy(graph); cudaGetLastError(); throw; }
+                ORMI_CUDA(cudaStreamEndCapture(ctx->stream, &graph));
+                cudaGraphExec_t exec = nullptr;
+                const cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+                cudaGraphDestroy(graph);
+                if (e != cudaSuccess) throw Error(std::string("CUDA Error: ") + cudaGetErrorString(e) + " (instantiating a step graph)");
+                if (cp->graphs.size() >= 32) {                   // keep the 32 most recently used address sets
+                    size_t oldest = 0;
+                    for (size_t i = 1; i < cp->graphs.size(); ++i) if (cp->graphs[i].stamp < cp->graphs[oldest].stamp) oldest = i;
+                    cudaGraphExecDestroy((cudaGraphExec_t)cp->graphs[oldest].exec);
+                    cp->graphs.erase(cp->graphs.begin() + oldest);
+                }
+                StepGraph sg;
+                sg.at = at; sg.exec = exec; sg.launches = (int)(ctx->counters["launches"] - before); sg.stamp = ++cp->graph_clock;
+                cp->graphs.push_back(std::move(sg));
+                cp->seen.erase(std::find(cp->seen.begin(), cp->seen.end(), at));
+                ORMI_CUDA(cudaGraphLaunch(exec, ctx->stream));
+                ctx->counters["graphs_recorded"]++;
+            }
         }
     } catch (...) {
         for (size_t b = 0; b < plan.buffers.size(); ++b)
