@@ -35,11 +35,16 @@ WORKLOAD = "configs[1]: row softmax + layernorm, forward + autograd backward, x[
 BYTES_SOFTMAX = 4 * R * C * 4
 BYTES_LAYERNORM = 4 * R * C * 4 + 4 * C * 4
 BYTES_STEP = BYTES_SOFTMAX + BYTES_LAYERNORM
-# DRAM traffic of the dominant kernel from its ncu capture (profiles/rows_layernorm_fwd_bwd_8192x4096.md): 268.5 MB read +
-# 231.5 MB written per launch over 8192 rows; the traffic is proportional to the rows, the bench launch covers 16384.
-LN_TRAFFIC_BYTES = 2 * (268_529_664 + 231_505_920)
-LN_TRAFFIC_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 8192 rows (500.0 MB), times 2 for 16384 rows"
-LN_KERNEL = "fused layernorm forward+backward (rows template) + its finalize launch (partials of dg and db)"
+# The two graphs read the same x and gy.  Realized in ONE call they become one kernel that reads each once: what that
+# kernel must move is x, gy in and y, dx of both graphs out (plus g, b, dg, db).
+BYTES_FUSED_KERNEL = 6 * R * C * 4 + 4 * C * 4
+# DRAM traffic of the dominant kernel from its ncu capture (profiles/rows_softmax_layernorm_one_call_8192x4096.md), per
+# launch over 8192 rows; the traffic is proportional to the rows, the bench launch covers 16384.
+FUSED_READ_8192, FUSED_WRITE_8192 = 273_184_256, 502_176_512
+STEP_TRAFFIC_BYTES = 2 * (FUSED_READ_8192 + FUSED_WRITE_8192)
+STEP_TRAFFIC_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 8192 rows (775.4 MB), times 2 for 16384 rows"
+STEP_KERNEL = ("one fused kernel for both graphs (rows template: softmax and layernorm forward+backward of the same x and gy, "
+               "each read once) + its finalize launch (partials of dg and db)")
 
 
 _REAL_STDOUT = None
@@ -481,8 +486,8 @@ def run_only(args):
         roots, nbytes = [y, x.grad], 4 * args.rows * C * 4
     else:
         sm, ln, _ = build_graphs(G, W, lambda a, rg=False: dev.leaf(a, rg), rows=args.rows)
-        roots = sm if args.only == "softmax" else ln
-        nbytes = 4 * args.rows * C * 4
+        roots = sm if args.only == "softmax" else (ln if args.only == "layernorm" else sm + ln)
+        nbytes = (6 if args.only == "fused_step" else 4) * args.rows * C * 4
     runner = StepRunner(dev, G, [roots])
     for _ in range(args.warmup):
         runner.run()
@@ -498,7 +503,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default=None, choices=["softmax", "softmax_stable", "layernorm", "rowsum", "gemm_bf16", "gemm_fp32", "gemm_tf32", "gemm_3xtf32", "mlp_bf16", "mlp_fp32", "mlp_sharded"],
+    ap.add_argument("--only", default=None, choices=["softmax", "softmax_stable", "layernorm", "fused_step", "rowsum", "gemm_bf16", "gemm_fp32", "gemm_tf32", "gemm_3xtf32", "mlp_bf16", "mlp_fp32", "mlp_sharded"],
                     help="profiling aid: run just this graph --steps times on --rows rows and exit")
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--no-extras", action="store_true", help="skip the matmul sweep and the MLP training steps")
@@ -550,7 +555,8 @@ def main():
 
     # inputs resident in HBM; each rank draws its own shard (seed offset by rank)
     sm_roots, ln_roots, inputs = build_graphs(G, W, lambda a, rg=False: dev.leaf(a, rg), shard=rank)
-    runner = StepRunner(dev, G, [sm_roots, ln_roots])
+    runner = StepRunner(dev, G, [sm_roots, ln_roots])            # the two graphs in separate calls (kernels timed alone)
+    fused = StepRunner(dev, G, [sm_roots + ln_roots])           # the step: one realize call for all six results
 
     if dist is not None:
         from ormi_b200.train_step import init_comm
@@ -573,15 +579,14 @@ def main():
 
     def step():
         if dist is None:
-            runner.run()
+            fused.run()
             return
-        # cross-shard combine: dg, db (the last two roots of the layernorm graph) are summed over the ranks, in place,
-        # by NCCL on the second stream.  Nothing of the next step reads them, so the all-reduce (a latency of some
-        # 25 us for 2 x 16 KB) runs beside the next step's softmax kernel; the compute stream waits for it after that
-        # kernel has been queued.  No host synchronisation inside a step.
-        outs = runner.run(which=0, keep=True)
+        # cross-shard combine: dg, db (the last two roots) are summed over the ranks, in place, by NCCL on the second
+        # stream.  Nothing of the next step reads them; the compute stream waits for the all-reduce (a latency of some
+        # 25 us for 2 x 16 KB) before the next step's kernel, whose blocks have fixed row shares and must not find SMs
+        # taken.  No host synchronisation inside a step.
         settle()
-        outs += runner.run(which=1, keep=True)
+        outs = fused.run(keep=True)
         bufs = (ctypes.c_void_p * 2)(outs[-2][0], outs[-1][0])
         counts = (ctypes.c_size_t * 2)(C, C)
         check(lib.ormi_b200_allreduce_sum_f32(dev.handle, bufs, counts, 2, 1))
@@ -593,7 +598,7 @@ def main():
     # The dominant kernel alone right after the warm-up, before the GPU has been under load for a second: the state the
     # copy-bandwidth peak was measured in (a burst).  `roofline.achieved` is the same measurement taken after the timed
     # region, under the power cap the long run settles into; both are reported.
-    ms_ln_burst = timed(dev, torch, lambda: runner.run(which=1), args.steps, dist)
+    ms_fused_burst = timed(dev, torch, lambda: fused.run(), args.steps, dist)
     # nvidia-smi samples every 100 ms and the timed region lasts milliseconds, so the same step keeps the GPU under
     # load for about a second before and after the timed region: the clock samples bracket it.
     sampler = ClockSampler(local_rank)
@@ -607,7 +612,8 @@ def main():
     launches0 = dev.counter("launches")
     ms_total = timed(dev, torch, step, args.steps, dist, after=settle)
     launches = dev.counter("launches") - launches0
-    # dominant kernel alone (the fused layernorm forward+backward kernel)
+    # the dominant kernel (with its finalize launch) alone, and the two graphs in calls of their own
+    ms_fused = timed(dev, torch, lambda: fused.run(), args.steps, dist)
     ms_ln = timed(dev, torch, lambda: runner.run(which=1), args.steps, dist)
     ms_sm = timed(dev, torch, lambda: runner.run(which=0), args.steps, dist)
     for _ in range(300):
@@ -619,7 +625,7 @@ def main():
     graph_ms = None
     if dist is None and not args.no_extras:
         with dev.capture() as captured:
-            runner.run()
+            fused.run()
         for _ in range(3):
             captured.launch()
         graph_ms = timed(dev, torch, captured.launch, args.steps) / args.steps
@@ -643,7 +649,7 @@ def main():
     chunk_sets = []
     for _ in range(n_chunks):
         csm, cln, cin = build_graphs(G, W, lambda a, rg=False: dev.leaf(a, rg), rows=E2E_CHUNK, shard=rank)
-        chunk_sets.append((StepRunner(dev, G, [csm, cln]), cin))
+        chunk_sets.append((StepRunner(dev, G, [csm + cln]), cin))
     np_in = {k: t.numpy() for k, t in host_in.items()}
     np_out = [t.numpy() for t in host_out]
     np_part = host_part.numpy()
@@ -715,7 +721,7 @@ def main():
                                        "note": "the headline step captured into a CUDA graph and replayed: one host call per step"}
     peak, peak_src = peaks()
     if not args.no_extras:
-        del runner, host_in, host_out, host_part, np_in, np_out, np_part, chunk_sets
+        del runner, fused, host_in, host_out, host_part, np_in, np_out, np_part, chunk_sets
         for node in inputs.values():
             node.data = None
         inputs.clear()
@@ -751,13 +757,16 @@ def main():
         ms_step = ms_total / args.steps
         value = world * BYTES_STEP / (ms_step * 1e-3) / 1e9
         ln_gbps = BYTES_LAYERNORM / (ms_ln / args.steps * 1e-3) / 1e9
+        fused_gbps = BYTES_FUSED_KERNEL / (ms_fused / args.steps * 1e-3) / 1e9
         sm_gbps = BYTES_SOFTMAX / (ms_sm / args.steps * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "rows_per_gpu": R, "cols": C,
-                       "l2": "inputs larger than L2: every kernel reads 537 MB and writes 537 MB",
+                       "l2": "inputs larger than L2: x and gy are 268 MB each, the four results 268 MB each",
+                       "step": "both graphs in one realize call: one fused kernel reads x and gy once (1.61 GB moved per step); "
+                               "value counts the algorithmic bytes of the two graphs as separate fused passes (2.15 GB), as the reference arm does",
                        "exchange": "all-reduce of dg, db (2 x 4096 fp32) per step" if world > 1 else "none",
                        "cpu_sample": f"the reference arm and cpu_baseline step over workers x {CPU_ROWS_PER_WORKER} rows of the same workload"},
             "clocks": clocks,
@@ -765,14 +774,17 @@ def main():
                     "ms_per_step": e2e_ms, "pipeline": f"{n_chunks} chunks of {E2E_CHUNK} rows: all uploads queued first | kernels k after upload k | download k behind kernels k",
                     "pinned_h2d_gbps": h2d_gbps, "pinned_d2h_gbps": d2h_gbps},
             "gpu_launches": launches,
-            "roofline": {"bound": "hbm", "kernel": LN_KERNEL,
-                         "achieved": ln_gbps, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": ln_gbps / peak,
-                         "traffic": LN_TRAFFIC_BYTES, "traffic_unit": "bytes per launch",
-                         "traffic_source": LN_TRAFFIC_SOURCE,
-                         "algorithmic_bytes": BYTES_LAYERNORM, "softmax_kernel_gbps": sm_gbps,
-                         "burst": {"achieved": BYTES_LAYERNORM / (ms_ln_burst / args.steps * 1e-3) / 1e9,
-                                   "frac": BYTES_LAYERNORM / (ms_ln_burst / args.steps * 1e-3) / 1e9 / peak,
-                                   "note": "the same kernel timed right after the warm-up steps, before the sustained load"}},
+            "roofline": {"bound": "hbm", "kernel": STEP_KERNEL,
+                         "achieved": fused_gbps, "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": fused_gbps / peak,
+                         "traffic": STEP_TRAFFIC_BYTES, "traffic_unit": "bytes per launch",
+                         "traffic_source": STEP_TRAFFIC_SOURCE,
+                         "algorithmic_bytes": BYTES_FUSED_KERNEL,
+                         "burst": {"achieved": BYTES_FUSED_KERNEL / (ms_fused_burst / args.steps * 1e-3) / 1e9,
+                                   "frac": BYTES_FUSED_KERNEL / (ms_fused_burst / args.steps * 1e-3) / 1e9 / peak,
+                                   "note": "the same kernel timed right after the warm-up steps, before the sustained load"},
+                         "graphs_in_calls_of_their_own": {
+                             "softmax_kernel_gbps": sm_gbps, "layernorm_kernel_gbps": ln_gbps, "layernorm_frac": ln_gbps / peak,
+                             "note": "each graph realized alone reads x and gy itself: 1 073.7 MB of algorithmic bytes per kernel"}},
         }
         if cpu_rec is not None:
             line["cpu_baseline"] = cpu_rec

@@ -43,8 +43,8 @@ def test_gpu_arm_line(tmp_path):
     assert len(lines) == 1
     line = json.loads(lines[0])
     assert COMMON | {"clocks", "gpu_launches", "roofline"} <= set(line)
-    # per step: the softmax kernel, the layernorm kernel, one finalize launch for dg and db
-    assert line["gpu_launches"] == 5 * 3 and line["n_gpus"] == 1 and line["dtype"] == "f32"
+    # per step: one fused kernel for both graphs, one finalize launch for dg and db
+    assert line["gpu_launches"] == 5 * 2 and line["n_gpus"] == 1 and line["dtype"] == "f32"
     r = line["roofline"]
     assert r["bound"] == "hbm" and r["unit"] == "GB/s" and abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-9 and r["traffic"] > 0
     assert line["e2e"]["h2d_bytes_per_step"] > 0 and line["e2e"]["d2h_bytes_per_step"] > 0 and line["e2e"]["value"] < line["value"]

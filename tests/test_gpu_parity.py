@@ -626,3 +626,25 @@ def test_captured_step_replays_with_new_input_contents():
         step.destroy()
     finally:
         dev.close()
+
+
+def test_softmax_and_layernorm_in_one_realize_call_match_the_separate_calls(device):
+    """The benchmark step as one realize call (one fused kernel for both graphs + one finalize launch) against the two
+    graphs realized in calls of their own: y and dx of both graphs bit for bit (the arithmetic of a row does not depend on
+    what else the kernel computes), dg and db within the reduction tolerance (the blocks' row shares may differ)."""
+    import bench as B
+    R = 2048
+    sm, ln, inputs = B.build_graphs(G, W, lambda a, rg=False: device.leaf(a, rg), rows=R)
+    before = device.counter("launches")
+    device.realize(sm + ln)
+    assert device.counter("launches") == before + 2
+    together = [device.numpy(n) for n in sm + ln]
+    for n in sm + ln:
+        n.data = None
+    device.realize(sm)
+    device.realize(ln)
+    apart = [device.numpy(n) for n in sm + ln]
+    for a, b in zip(together[:4], apart[:4]):
+        np.testing.assert_array_equal(a, b)
+    for a, b in zip(together[4:], apart[4:]):
+        assert np.abs(a - b).max() <= REDUCE_TOL * np.abs(b).max()

@@ -55,6 +55,29 @@ def test_softmax_forward_backward_is_one_kernel():
     assert kinds(plan) == ["rows"]
 
 
+@pytest.mark.parametrize("shape", [(12, 256), (7, 100), (3, 4096)])
+def test_softmax_and_layernorm_realized_together_are_one_kernel(shape):
+    """Both graphs of the benchmark step handed to ONE realize call: they share x, gy and the [rows, columns] domain, so
+    the scheduler puts all six results (y, dx of the softmax; y, dx, dg, db of the layernorm) into one rows kernel that
+    reads the inputs once, plus the finalize launch of the column partials."""
+    R, C = shape
+    x = G.leaf(W.normal(0, (R, C), math.sqrt(2.0)), True)
+    gy = G.leaf(W.normal(1, (R, C)))
+    y1 = W.softmax(x)
+    y1.grad = gy
+    G.compute_gradients(y1)
+    dx1 = x.grad
+    x.grad = None
+    g, b = G.leaf(W.uniform(3, (C,), 0.5, 1.5), True), G.leaf(W.normal(4, (C,), 0.1), True)
+    y2 = W.layernorm(x, g, b)
+    y2.grad = gy
+    G.compute_gradients(y2)
+    plan = compare([y1, dx1, y2, x.grad, g.grad, b.grad], 2 * REDUCE_TOL)
+    assert kinds(plan) == ["rows", "finalize"]
+    assert "outs=FFFFCC" in plan["steps"][0]["what"]
+    assert plan["steps"][0]["bytes_read"] <= 2 * R * C * 4 + 2 * C * 4 + 64    # x and gy once (not once per graph), g, b, constants
+
+
 @pytest.mark.parametrize("shape", [(12, 256), (7, 100), (5, 37), (3, 1024), (2, 4096)])
 def test_layernorm_forward_backward(shape):
     R, C = shape
