@@ -434,6 +434,35 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
             depth = std::max(depth, lv);
         }
     }
+    // Register demand of the row body: per-element values that must survive a block barrier (defined at or before a
+    // reduction level and still read after it) stay in registers across it, next to the vectors that are always live
+    // (row-invariant operands held for every row, the column accumulators).  Counted in vectors of VPT elements.
+    int live_vectors = 0;
+    {
+        std::map<int, int> lvl, last;                     // node -> level it is computed at / last level that reads it
+        std::vector<int> load_last(spec.loads.size(), 0);
+        auto use = [&](const KRef& r, int at) {
+            if (r.t == KRef::NODE) last[r.id] = std::max(last[r.id], at);
+            else load_last[r.id] = std::max(load_last[r.id], at);
+        };
+        for (const KNode& kn : spec.nodes) {
+            int lv = 0;
+            for (auto& r : kn.operands) if (r.t == KRef::NODE) lv = std::max(lv, lvl[r.id]);
+            for (auto& r : kn.operands) use(r, lv);       // a row sum reads its operand at the level below its own
+            if (kn.op == KNode::OP_ROWSUM) lv += 1;
+            lvl[kn.node] = lv;
+        }
+        for (auto& o : spec.outputs) use(o.value, o.value.t == KRef::NODE ? lvl[o.value.id] : 0);
+        int always = 0;
+        for (auto& o : spec.outputs) if (o.kind == KOutput::COLSUM) ++always;
+        for (size_t l = 0; l < spec.loads.size(); ++l) if (li[l].elem && !li[l].row_var) ++always;
+        for (int b = 0; b < depth; ++b) {                 // the barrier between level b and level b + 1
+            int live = 0;
+            for (const KNode& kn : spec.nodes) if (!(kn.row || kn.scalar) && lvl[kn.node] <= b && last[kn.node] > b) ++live;
+            for (size_t l = 0; l < spec.loads.size(); ++l) if (li[l].elem && li[l].row_var && load_last[l] > b) ++live;
+            live_vectors = std::max(live_vectors, live + always);
+        }
+    }
     //   depth <= 1 with no column / global partials, re-measured with three rotated input sets (no operand left in
     //            L2): 8 elements/thread, 4 blocks/SM, grid 4/SM, direct loads -> 5275; 2 blocks/SM staged -> 4880.
     bool pure_rows = true;
@@ -441,11 +470,16 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     const bool shallow = depth <= 1 && pure_rows;
     const int target = knob(TUNE_ROWS_VPT, (V == 4 && depth >= 2) ? 16 : 8);
     const bool hoist = toggle(TUNE_ROWS_HOIST, true);
-    int minb = knob(TUNE_ROWS_MINB, shallow ? 4 : (depth == 2 ? 3 : 2));
-    const int grid_mult = knob(TUNE_ROWS_GRID, shallow ? 4 : (depth == 2 ? 3 : 2));
     int T = std::min(1024, std::max(32, ceil_pow2((C + target - 1) / target)));
     int64_t VPT = (C + T - 1) / T;
     VPT = (VPT + V - 1) / V * V;
+    //   depth 4 with more live values than two blocks per SM leave registers for (both graphs of the benchmark step in
+    //            one kernel: 9 vectors of 16 across a barrier = 144 registers; the 128-register cap spilled 116 bytes per
+    //            thread): one block per SM, uncapped, with a 3-stage ring -> 5950; 2 blocks/SM -> 5370.  The layernorm
+    //            kernel alone (7 vectors = 112 registers) keeps two blocks: 6000 against 5560.
+    const bool heavy = depth >= 3 && live_vectors * VPT > 120;
+    int minb = knob(TUNE_ROWS_MINB, shallow ? 4 : (depth == 2 ? 3 : (heavy ? 1 : 2)));
+    const int grid_mult = knob(TUNE_ROWS_GRID, shallow ? 4 : (depth == 2 ? 3 : (heavy ? 1 : 2)));
     if (VPT > 32) return unsupported("row of " + std::to_string(C) + " elements does not fit in registers");
     const int NT = std::max(T, 256), G = NT / T, NV = (int)VPT / V, NW = T / 32;
     if (NT * minb > 1024) minb = 0;     // never squeeze a block below 64 registers per thread
@@ -472,7 +506,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
         if (can && !staged.empty()) {
             const int64_t per_stage = (int64_t)staged.size() * C * 4;
             const int64_t budget = (int64_t)(minb >= 3 ? 70 : (minb == 2 ? 100 : 200)) * 1024;
-            stages = (int)std::min<int64_t>(knob(TUNE_ROWS_NSTAGE, 2), budget / per_stage);
+            stages = (int)std::min<int64_t>(knob(TUNE_ROWS_NSTAGE, heavy ? 3 : 2), budget / per_stage);
             if (stages < 2) stages = 0;
         }
         if (!stages) staged.clear();
@@ -763,7 +797,7 @@ GeneratedKernel generate_rows(const KernelSpec& spec, const std::string& name) {
     out.step.err_arg = stages > 0 || dyn_rows;
     out.cols = C;
     std::ostringstream w;
-    w << "rows[R=" << R << ",C=" << C << ",T=" << T << ",G=" << G << ",VPT=" << VPT << ",V=" << V << ",levels=" << max_level << ",stages=" << stages << (dyn_rows ? ",dyn" : "") << "] nodes=" << spec.nodes.size()
+    w << "rows[R=" << R << ",C=" << C << ",T=" << T << ",G=" << G << ",VPT=" << VPT << ",V=" << V << ",levels=" << max_level << ",stages=" << stages << (dyn_rows ? ",dyn" : "") << ",live=" << live_vectors << "] nodes=" << spec.nodes.size()
       << " loads=" << spec.loads.size() << " outs=";
     for (auto& o : spec.outputs) w << (o.kind == KOutput::FULL ? "F" : o.kind == KOutput::ROW ? "R" : o.kind == KOutput::COLSUM ? "C" : "G");
     out.step.what = w.str();

@@ -9,6 +9,7 @@
 // kernels are cached by source hash and whole schedules by graph structure, so a training loop that
 // rebuilds the same graph every step pays for scheduling, code generation and NVRTC once.
 #include <algorithm>
+#include <map>
 #include <nvrtc.h>
 
 #include <cstdio>
@@ -355,14 +356,26 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
         // Pass 1, the pool only: every buffer gets its block in the order the steps need them — scratch is taken right
         // before its first step and goes back right after its last one, so a later step of this call may get the same
         // block (the stream orders the kernels that use it).  `at[s]` is what step s sees.
+        // Scratch that a step gives back can serve a later step of this call, but it returns to the pool itself only
+        // when every launch of the call has been queued: something that takes a block from the pool while the launches
+        // are being queued (a bf16 copy of an operand, say) must not get one that a kernel not yet queued will write.
         const size_t nb = plan.buffers.size();
         std::vector<void*> at(plan.steps.size() * nb, nullptr);
+        struct Returned {
+            ormi_b200_ctx* ctx;
+            std::multimap<size_t, void*> blocks;
+            ~Returned() { for (auto& kv : blocks) { try { pool_free(ctx, kv.second, kv.first); } catch (...) { } } }
+        } returned{ctx, {}};
         for (size_t s = 0; s < plan.steps.size(); ++s) {
-            for (size_t b = 0; b < nb; ++b)
-                if (cp->first_use[b] == (int)s && !bufs[b]) bufs[b] = pool_alloc(ctx, (size_t)plan.buffers[b].bytes);
+            for (size_t b = 0; b < nb; ++b) {
+                if (cp->first_use[b] != (int)s || bufs[b]) continue;
+                auto again = returned.blocks.find((size_t)plan.buffers[b].bytes);
+                if (again != returned.blocks.end()) { bufs[b] = again->second; returned.blocks.erase(again); }
+                else bufs[b] = pool_alloc(ctx, (size_t)plan.buffers[b].bytes);
+            }
             std::copy(bufs.begin(), bufs.end(), at.begin() + s * nb);
             for (size_t b = 0; b < nb; ++b)
-                if (cp->last_use[b] == (int)s && bufs[b]) { pool_free(ctx, bufs[b], (size_t)plan.buffers[b].bytes); bufs[b] = nullptr; handed[b] = true; }
+                if (cp->last_use[b] == (int)s && bufs[b]) { returned.blocks.insert({(size_t)plan.buffers[b].bytes, bufs[b]}); bufs[b] = nullptr; handed[b] = true; }
         }
         // Pass 2, the launches.  A plan of several launches whose buffers come out at the same addresses as in an
         // earlier call (a loop in its steady state: the pool hands the same blocks out in the same order) is replayed
