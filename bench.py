@@ -40,9 +40,9 @@ BYTES_STEP = BYTES_SOFTMAX + BYTES_LAYERNORM
 BYTES_FUSED_KERNEL = 6 * R * C * 4 + 4 * C * 4
 # DRAM traffic of the dominant kernel from its ncu capture (profiles/rows_softmax_layernorm_one_call_8192x4096.md), per
 # launch over 8192 rows; the traffic is proportional to the rows, the bench launch covers 16384.
-FUSED_READ_8192, FUSED_WRITE_8192 = 273_184_256, 502_176_512
+FUSED_READ_8192, FUSED_WRITE_8192 = 268_499_712, 482_261_760
 STEP_TRAFFIC_BYTES = 2 * (FUSED_READ_8192 + FUSED_WRITE_8192)
-STEP_TRAFFIC_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 8192 rows (775.4 MB), times 2 for 16384 rows"
+STEP_TRAFFIC_SOURCE = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 8192 rows (750.8 MB), times 2 for 16384 rows"
 STEP_KERNEL = ("one fused kernel for both graphs (rows template: softmax and layernorm forward+backward of the same x and gy, "
                "each read once) + its finalize launch (partials of dg and db)")
 
