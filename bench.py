@@ -599,6 +599,9 @@ def main():
     # The dominant kernel alone right after the warm-up, before the GPU has been under load for a second: the state the
     # copy-bandwidth peak was measured in (a burst).  `roofline.achieved` is the same measurement taken after the timed
     # region, under the power cap the long run settles into; both are reported.
+    settle()
+    fused.run()
+    dev.sync()
     ms_fused_burst = timed(dev, torch, lambda: fused.run(), args.steps, dist)
     # nvidia-smi samples every 100 ms and the timed region lasts milliseconds, so the same step keeps the GPU under
     # load for about a second before and after the timed region: the clock samples bracket it.

@@ -330,7 +330,9 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
         for (size_t b = 0; b < p.buffers.size(); ++b) {
             if (p.buffers[b].kind != BufKind::Twin16) continue;
             for (const NodeResult& r : p.results)
-                if (!r.alias && r.node == p.buffers[b].node) { fresh->twin_result[b] = r.buffer; fresh->last_use[b] = -1; }
+                // (a node handed out as bf16 ONLY is its twin: that result's buffer is b itself, and registering a buffer as
+                // its own twin would make freeing it free it twice)
+                if (!r.alias && !r.bf16 && r.node == p.buffers[b].node) { fresh->twin_result[b] = r.buffer; fresh->last_use[b] = -1; }
         }
         cp = fresh.get();
         ctx->plan_cache[key] = std::move(fresh);

@@ -648,3 +648,28 @@ def test_softmax_and_layernorm_in_one_realize_call_match_the_separate_calls(devi
         np.testing.assert_array_equal(a, b)
     for a, b in zip(together[4:], apart[4:]):
         assert np.abs(a - b).max() <= REDUCE_TOL * np.abs(b).max()
+
+
+def test_a_bf16_only_result_is_freed_once():
+    """A root handed back as bf16 ONLY (ORMI_NODE_BF16) is an ordinary pool block for its owner: freeing it returns it once
+    (it used to be registered as its own bf16 copy, so that freeing it freed it twice: two later allocations then shared
+    one block)."""
+    from ormi_b200.runtime import Device
+    dev = Device(0)
+    try:
+        dev.set_option("matmul", "bf16")
+        B, D, H = 256, 128, 512
+        x, w1, b1 = W.normal(0, (B, D)), W.kaiming_uniform(2, D, (D, H)), W.normal(4, (H,), 0.1)
+        h = W.gelu_tanh(G.add(G.matmul(dev.leaf(x), dev.leaf(w1)), dev.leaf(b1)))
+        h.bf16 = True
+        dev.realize([h])
+        assert h.bf16 and h.data.nbytes == B * H * 2
+        ptr, nbytes = h.data.dev_ptr, h.data.nbytes
+        h.data._release = None                      # freed by hand below
+        dev.free(ptr, nbytes)                       # raised "returned twice" before the fix
+        p1, p2 = dev.alloc(nbytes), dev.alloc(nbytes)
+        assert p1 != p2
+        dev.free(p1, nbytes)
+        dev.free(p2, nbytes)
+    finally:
+        dev.close()
