@@ -265,6 +265,10 @@ int ormi_b200_selftest_wait_timeout(ormi_b200_ctx* ctx, int limit_ms);
  *              every node it executes (runtime.cpp:13-39).  "free": only roots and ORMI_NODE_KEEP nodes come back; a
  *              materialized node nobody outside the call holds is scratch, returned to the pool after the last step
  *              that reads it (a later call that reaches it again recomputes it).
+ *   "auto_graph": "on" (default) / "off".  ormi_b200_realize replays the launches of a plan with two or more of them as a
+ *              CUDA graph when the buffers of the call come out at the same addresses as in an earlier call (a loop in its
+ *              steady state); recorded at the second such call, up to 32 address sets per plan.  Plans with tensor-core
+ *              matmuls are left out (they look up or make bf16 operand copies as they go).
  *   "pool_canary": "on" / "off" (default).  A debugging aid in place of a memory checker: every block the pool hands out
  *              from then on carries a 256-byte guard zone behind it, read back (synchronously) when the block returns; an
  *              overwritten zone makes that call — ormi_b200_free, or the realize call that returns scratch — fail with
