@@ -722,7 +722,7 @@ def main():
     extras = {}
     if graph_ms is not None:
         extras["step_graph_replay"] = {"ms_per_step": graph_ms, "gbps": BYTES_STEP / (graph_ms * 1e-3) / 1e9,
-                                       "note": "the headline step captured into a CUDA graph and replayed: one host call per step; the replays rewrite the same result buffers, so part of the gain is write hits in L2"}
+                                       "note": "the headline step captured into a CUDA graph and replayed: one host call per step (timed after a pause of the sustained load: compare with roofline.burst, not with value)"}
     peak, peak_src = peaks()
     if not args.no_extras:
         del runner, fused, host_in, host_out, host_part, np_in, np_out, np_part, chunk_sets
