@@ -562,6 +562,8 @@ def test_captured_step_replays_with_new_input_contents():
     """Step capture: a softmax + layernorm forward/backward step and a matmul are recorded once and replayed with one call;
     the replays read the input buffers at their addresses (new contents give new results), rewrite the results in place,
     and keep every block they touch until the step is destroyed."""
+    if os.environ.get("ORMI_B200_POOL_CANARY"):
+        pytest.skip("a capture is refused while guard zones are on: their checks wait for the device")
     from ormi_b200.runtime import Device
     dev = Device(0)
     try:
