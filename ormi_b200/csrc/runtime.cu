@@ -366,7 +366,14 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
         struct Returned {
             ormi_b200_ctx* ctx;
             std::multimap<size_t, void*> blocks;
-            ~Returned() { for (auto& kv : blocks) { try { pool_free(ctx, kv.second, kv.first); } catch (...) { } } }
+            // every block goes back; the first complaint of the pool (an overwritten guard zone) is reported afterwards
+            void release(bool report) {
+                std::string first;
+                for (auto& kv : blocks) { try { pool_free(ctx, kv.second, kv.first); } catch (const std::exception& e) { if (first.empty()) first = e.what(); } }
+                blocks.clear();
+                if (report && !first.empty()) throw Error(first);
+            }
+            ~Returned() { release(false); }          // the call is failing for another reason
         } returned{ctx, {}};
         for (size_t s = 0; s < plan.steps.size(); ++s) {
             for (size_t b = 0; b < nb; ++b) {
@@ -457,6 +464,7 @@ void realize(ormi_b200_ctx* ctx, ormi_b200_node* nodes, int n_nodes, const int* 
                 ctx->counters["graphs_recorded"]++;
             }
         }
+        returned.release(true);
     } catch (...) {
         for (size_t b = 0; b < plan.buffers.size(); ++b)
             if (plan.buffers[b].kind != BufKind::External && bufs[b] && !handed[b]) pool_free(ctx, bufs[b], (size_t)plan.buffers[b].bytes);
